@@ -1,0 +1,181 @@
+"""The Python entry point: a model folder (or random weights) to generated tokens.
+
+The reference has no offline entry point; its de-facto API is the benchmark
+script ``test/generate_token.py:24-67`` (config, runner, ``init_model``, a batch,
+a loop of forwards) and the HTTP manager ``litelang/apis/http_server_manager.py:
+12-63``.  ``Engine`` does what those do between a prompt's tokens and its new
+tokens: it builds the model chosen by config.json, sizes the cache from free
+memory (``mem_usage``, as ``litelang/models/cache.py:218-223``) or from an
+explicit page count, and ``generate`` drives the scheduler to completion.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from .. import models as _models  # noqa: F401  (registers the architectures)
+from ..cache.manager import CacheManager
+from ..config.base import ModelConfig, load_config
+from ..config.engine import EngineConfig
+from ..sampling.sampler import Sampler, SamplingParams, uniform_for
+from ..weights.loader import load_weights
+from ..weights.random_init import random_fetch
+from .batch import StepEntry
+from .model import CausalLM
+from .runner import ModelRunner
+from .scheduler import PlannedEntry, Request, Scheduler
+
+_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+def cache_bytes_per_page(model: CausalLM, page_size: int, elt: int) -> int:
+    n = 0
+    for g in model.cache_groups:
+        if g.kind == "paged":
+            n += g.planes * 2 * g.num_kv_heads * page_size * g.head_dim * elt
+    return n
+
+
+class Engine:
+    def __init__(self, model_path: Optional[str] = None, engine_config: Optional[EngineConfig] = None, *,
+                 config: Optional[ModelConfig] = None, random_seed: Optional[int] = None,
+                 device: str = "cuda:0"):
+        """Load ``model_path`` (config.json + safetensors), or build ``config`` with random
+        weights drawn on the device from ``random_seed`` (no folder is written)."""
+        self.cfg = engine_config or EngineConfig()
+        if not torch.cuda.is_available():
+            raise RuntimeError("lite_lang_b200 needs a CUDA device (B200, sm_100a); none is visible")
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        if model_path is not None:
+            self.model_config = load_config(model_path)
+        elif config is not None:
+            self.model_config = config
+        else:
+            raise ValueError("give a model_path or a config")
+        self.model_path = model_path
+        self.dtype = _TORCH_DTYPE[self.cfg.dtype]
+        spec = self.model_config.model_spec()
+        self.model = CausalLM(spec)
+        if model_path is not None and random_seed is None:
+            load_weights(self.model, model_path, self.dtype, self.device)
+        else:
+            seed = 0 if random_seed is None else random_seed
+            fetch = random_fetch(self.model, seed, self.model_config.init_scales(), torch.bfloat16,
+                                 device=str(self.device))
+            self.model.load(fetch, self.dtype, self.device)
+        self.max_model_len = min(self.cfg.model_len, spec.max_positions)
+        num_pages = self.cfg.num_pages
+        if num_pages is None:
+            torch.cuda.synchronize(self.device)
+            free, _total = torch.cuda.mem_get_info(self.device)
+            per_page = cache_bytes_per_page(self.model, self.cfg.page_size, 2 if self.dtype == torch.bfloat16 else 4)
+            num_pages = max(1, int(free * self.cfg.mem_usage) // max(1, per_page))
+            # no more than every request slot could ever use
+            most = self.cfg.max_batch_size * ((self.max_model_len + self.cfg.page_size - 1) // self.cfg.page_size)
+            num_pages = min(num_pages, most)
+        n_paged = sum(1 for g in self.model.cache_groups if g.kind == "paged")
+        self.manager = CacheManager(self.model.cache_groups, [num_pages] * n_paged, self.cfg.page_size,
+                                    self.cfg.max_batch_size, self.max_model_len)
+        self.runner = ModelRunner(self.model, self.manager, self.device, self.cfg.max_tokens_per_step,
+                                  self.cfg.cuda_graphs)
+        self.sampler = Sampler(self.device, self.cfg.max_batch_size, out=self.runner.result_buf)
+        self.scheduler = Scheduler(self.manager, self.cfg.max_tokens_per_step, self.cfg.max_reqs,
+                                   self.cfg.busy_scale, self.cfg.preempt_strategy, self.cfg.max_output_length)
+        self._next_id = 0
+        self._tokenizer = None
+        pinned = True
+        self._result_host = torch.zeros(self.cfg.max_batch_size + 1, dtype=torch.int32, pin_memory=pinned)
+
+    # ------------------------------------------------------------------
+    def tokenizer(self):
+        """The folder's tokenizer (only needed when prompts are text)."""
+        if self._tokenizer is None:
+            if self.model_path is None:
+                raise RuntimeError("text prompts need a model folder with a tokenizer")
+            from transformers import AutoTokenizer
+            self._tokenizer = AutoTokenizer.from_pretrained(self.model_path)
+        return self._tokenizer
+
+    def add_request(self, prompt: Union[str, Sequence[int]], params: Optional[SamplingParams] = None) -> Request:
+        params = params or SamplingParams()
+        if isinstance(prompt, str):
+            prompt = self.tokenizer().encode(prompt)
+        prompt = [int(t) for t in prompt]
+        if len(prompt) > self.cfg.max_input_length:
+            raise ValueError(f"a prompt of {len(prompt)} tokens exceeds max_input_length {self.cfg.max_input_length}")
+        vocab = self.model.spec.vocab_size
+        if any(t < 0 or t >= vocab for t in prompt):
+            raise ValueError("a prompt token lies outside the vocabulary")
+        max_new = params.max_new_tokens if params.max_new_tokens is not None else self.cfg.max_output_length
+        req = Request(self._next_id, prompt, params, max_new, tuple(self.model.spec.eos_token_ids))
+        self._next_id += 1
+        if not self.scheduler.add(req):
+            raise RuntimeError(f"the waiting queue is full (max_reqs = {self.cfg.max_reqs})")
+        return req
+
+    def step(self) -> List[Request]:
+        """One scheduler step: plan, run, sample, commit.  Returns the requests that finished."""
+        plan = self.scheduler.plan()
+        if not plan:
+            if self.scheduler.has_work():
+                raise RuntimeError("the scheduler has work but could plan nothing")
+            return []
+        entries = []
+        for p in plan:
+            toks = p.request.tokens[p.start:p.start + p.count]
+            entries.append(StepEntry(p.request.slot, toks, (p.count - 1,) if p.samples else ()))
+        logits = self.runner.step(entries)
+        sampled: List[Optional[int]] = [None] * len(plan)
+        rows = [i for i, p in enumerate(plan) if p.samples]
+        if rows:
+            temps, unis = [], []
+            for i in rows:
+                r = plan[i].request
+                greedy = r.params.greedy
+                temps.append(0.0 if greedy else float(r.params.temperature))
+                seed = r.params.seed if r.params.seed is not None else self.cfg.seed
+                unis.append(0.0 if greedy else uniform_for(seed, r.id, len(r.output)))
+            self.sampler.sample(logits, temps, unis)
+        # one copy brings the sampled tokens and the kernels' status word
+        self._result_host.copy_(self.runner.result_buf, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        host = self._result_host.numpy()
+        if host[-1] != 0:
+            self.runner.check_status()
+        for k, i in enumerate(rows):
+            sampled[i] = int(host[k])
+        return self.scheduler.commit(plan, sampled)
+
+    def generate(self, prompts: Sequence[Union[str, Sequence[int]]],
+                 params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:
+        """New tokens for each prompt (token ids in, token ids out), in the order given."""
+        if params is None or isinstance(params, SamplingParams):
+            plist = [params or SamplingParams()] * len(prompts)
+        else:
+            plist = list(params)
+            if len(plist) != len(prompts):
+                raise ValueError("one SamplingParams per prompt is needed")
+        reqs = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        while self.scheduler.has_work():
+            self.step()
+        return [list(r.output) for r in reqs]
+
+    def generate_text(self, prompts: Sequence[str], params=None) -> List[str]:
+        outs = self.generate(prompts, params)
+        tok = self.tokenizer()
+        return [tok.decode(o) for o in outs]
+
+    def stats(self) -> Dict[str, int]:
+        d = dict(self.scheduler.counters)
+        d.update(pages_handed_out=self.manager.pages_handed_out, pages_reused=self.manager.pages_reused,
+                 graph_replays=self.runner.graph_replays, steps_run=self.runner.steps_run)
+        return d
+
+
+def generate(model_path: str, prompts, params=None, engine_config: Optional[EngineConfig] = None):
+    """One-call form: build an engine for ``model_path`` and generate."""
+    return Engine(model_path, engine_config).generate(prompts, params)

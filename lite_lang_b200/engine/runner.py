@@ -1,0 +1,156 @@
+"""The step function: runs a batch of (request, next tokens) from the cache.
+
+It takes the place of the reference's ``Qwen2ModelRunner.forward`` together
+with the cache allocation that the reference does inside layer 0
+(``litelang/models/qwen2/model.py:123-126``, ``qwen2/layer/transformer_layer.py:
+53-60``).  Differences: the pages of a step are reserved *before* it is launched
+(by the scheduler or the replay tool, through the cache manager), a step may mix
+portions of prompts with single decoded tokens, nothing between the upload of
+the index arrays and the logits waits for the host, and the result is the
+float32 logits at the wanted places, not token ids.
+
+Steps made of single-token entries only are captured in CUDA graphs, one per
+batch-size bucket, and replayed; everything a captured step reads (index
+arrays, block tables, cache) sits at fixed addresses.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+from ..csrc.build import load_library
+from .batch import BatchBuilder, StepBatch, StepEntry
+from .model import CausalLM
+
+_STATUS_TEXT = {
+    1: "a token id outside the vocabulary",
+    2: "a cache slot outside the pool",
+    3: "a block-table entry outside the pool",
+    4: "a position outside the position table",
+}
+
+
+class KernelStatusError(RuntimeError):
+    pass
+
+
+def _buckets(limit: int) -> List[int]:
+    out, b = [], 1
+    while b < limit:
+        out.append(b)
+        b *= 2
+    out.append(limit)
+    return out
+
+
+class ModelRunner:
+    def __init__(self, model: CausalLM, manager: CacheManager, device: torch.device, max_tokens_per_step: int,
+                 cuda_graphs: bool = True):
+        if device.type != "cuda":
+            raise RuntimeError("lite_lang_b200 runs on a CUDA device only; there is no CPU path")
+        self.model = model
+        self.manager = manager
+        self.device = device
+        ops.configure_matmul_precision()
+        for lib in model.kernel_libraries():
+            load_library(lib)
+        self.storage = CacheStorage(manager, model.dtype, device)
+        # last element: the kernels' status word; the rest: sampled tokens (see sampling/)
+        self.result_buf = torch.zeros(manager.max_requests + 1, dtype=torch.int32, device=device)
+        self.status = self.result_buf[manager.max_requests:]
+        self.builder = BatchBuilder(manager, max_tokens_per_step, manager.max_requests, device, self.status)
+        self.single_builder = BatchBuilder(manager, manager.max_requests, manager.max_requests, device, self.status)
+        self.use_graphs = bool(cuda_graphs)
+        self._graphs: Dict[int, tuple] = {}
+        self._graph_pool = None
+        self._bucket_list = _buckets(manager.max_requests)
+        self.steps_run = 0
+        self.graph_replays = 0
+
+    # ------------------------------------------------------------------
+    def reserve(self, slot: int, new_tokens: int) -> bool:
+        """Make room for ``new_tokens`` more tokens of the request in ``slot``."""
+        return self.manager.reserve(slot, self.manager.length(slot) + new_tokens)
+
+    def step(self, entries: Sequence[StepEntry], allow_graph: bool = True) -> Optional[torch.Tensor]:
+        """Run one step.  Pages must have been reserved.  Returns float32 logits
+        [wanted, vocab] in the order of the entries and of their ``want`` lists (None if
+        nothing is wanted).  The tensor is valid until the next step."""
+        entries = list(entries)
+        m = self.manager
+        for e in entries:
+            c = m.length(e.slot)
+            for g in m.paged_ids:
+                if (c + len(e.tokens) + m.page_size - 1) // m.page_size > len(m._requests[e.slot].pages[g]):
+                    raise RuntimeError(f"step without reserved pages for slot {e.slot}")
+        self.storage.sync()
+        single = all(len(e.tokens) == 1 for e in entries)
+        if single and self.use_graphs and allow_graph:
+            logits = self._step_graph(entries)
+        else:
+            batch = self.builder.build(entries)
+            logits = self.model.forward(batch, self.storage)
+        for e in entries:
+            m.advance(e.slot, m.length(e.slot) + len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    # ------------------------------------------------------------------
+    def _bucket(self, n: int) -> int:
+        for b in self._bucket_list:
+            if b >= n:
+                return b
+        return self._bucket_list[-1]
+
+    def _capture(self, bucket: int):
+        batch = self.single_builder.build([], pad_entries=bucket)
+        batch.max_kv_len = self.manager.max_model_len
+        batch.captured = True
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.model.forward(batch, self.storage)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(batch, self.storage)
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        self._graphs[bucket] = (graph, logits)
+        return self._graphs[bucket]
+
+    def capture_all(self) -> None:
+        """Capture every bucket now (largest first, so that the pool is sized once)."""
+        if not self.use_graphs:
+            return
+        for b in sorted(self._bucket_list, reverse=True):
+            if b not in self._graphs:
+                self._capture(b)
+
+    def _step_graph(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
+        bucket = self._bucket(len(entries))
+        got = self._graphs.get(bucket)
+        if got is None:
+            got = self._capture(bucket)
+        graph, logits = got
+        batch = self.single_builder.build(entries, pad_entries=bucket)
+        graph.replay()
+        self.graph_replays += 1
+        if batch.real_logits == 0:
+            return None
+        return logits[:batch.real_logits]
+
+    # ------------------------------------------------------------------
+    def check_status(self) -> None:
+        """Raise if a kernel met an index out of range (synchronises)."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise KernelStatusError(f"a kernel reported {_STATUS_TEXT.get(code, code)}")

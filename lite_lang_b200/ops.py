@@ -1,0 +1,227 @@
+"""Typed Python entry points of the hand-written CUDA kernels.
+
+Every function takes torch CUDA tensors, checks what the kernel assumes
+(device, dtype, contiguity, sizes) and launches on torch's current stream.
+There is no CPU or library fallback: a tensor that is not on a CUDA device, or
+a missing kernel library, raises.
+
+Matrix products are the exception: like the reference, which calls cuBLAS
+through ``torch.mm`` / ``torch.addmm`` (``litelang/models/qwen2/layer/
+transformer_layer.py:79-109,193``), ``linear`` is a library product.  On the
+float32 path TF32 is switched off so that it is a true 32-bit product.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc.build import load_library
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"kernels take float32 or bfloat16 tensors, not {t.dtype}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("lite_lang_b200 kernels run on CUDA tensors only; there is no CPU path")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise ValueError(msg)
+
+
+def _i32(t: Optional[torch.Tensor], name: str) -> None:
+    if t is not None:
+        _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
+
+
+def _f32(t: Optional[torch.Tensor], name: str) -> None:
+    if t is not None:
+        _need(t.dtype == torch.float32 and t.is_contiguous(), f"{name} must be a contiguous float32 tensor")
+
+
+def core():
+    return load_library("core")
+
+
+def configure_matmul_precision() -> None:
+    """True float32 products (no TF32) and float32 accumulation for bfloat16 ones."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    try:
+        torch.set_float32_matmul_precision("highest")
+    except Exception:  # pragma: no cover
+        pass
+
+
+# --------------------------------------------------------------------------
+def embed_gather(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+    _need_cuda(out, table, ids)
+    _i32(ids, "ids")
+    _need(out.dtype == table.dtype and out.is_contiguous() and table.is_contiguous(), "embed: dtype/contiguity")
+    n, hidden = ids.numel(), table.shape[1]
+    _need(out.shape[0] >= n and out.shape[1] == hidden, "embed: out has the wrong shape")
+    core().call("ll_embed_gather", c_int(_dtype_code(out)), _ptr(out), _ptr(table), _ptr(ids), c_int(n),
+                c_int(hidden), c_int(table.shape[0]), _ptr(status), _stream())
+
+
+def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    _need_cuda(out, x, weight)
+    _f32(weight, "norm weight")
+    _need(x.dim() == 2 and out.shape == x.shape and out.dtype == x.dtype, "rmsnorm: shapes")
+    _need(x.stride(1) == 1 and out.stride(1) == 1, "rmsnorm: rows must be contiguous")
+    _need(weight.numel() == x.shape[1], "rmsnorm: weight size")
+    core().call("ll_rmsnorm", c_int(_dtype_code(x)), _ptr(out), _ptr(x), _ptr(weight), c_float(eps),
+                c_int(x.shape[0]), c_int(x.shape[1]), c_long(x.stride(0)), c_long(out.stride(0)), _stream())
+
+
+def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                eps: float, rows: Optional[torch.Tensor] = None, write_residual: bool = True) -> None:
+    """out[i] = norm(residual[r] + delta[r]); r = rows[i] if rows is given, else i.
+
+    Without ``rows`` the rounded sum is written back into ``residual``.
+    """
+    _need_cuda(out, residual, delta, weight, rows)
+    _f32(weight, "norm weight")
+    _i32(rows, "rows")
+    hidden = residual.shape[1]
+    _need(residual.is_contiguous() and out.is_contiguous() and out.dtype == residual.dtype, "add_rmsnorm: layout")
+    if delta is not None:
+        _need(delta.is_contiguous() and delta.dtype == residual.dtype and delta.shape[1] == hidden,
+              "add_rmsnorm: delta layout")
+    n_out = rows.numel() if rows is not None else residual.shape[0]
+    _need(out.shape[0] >= n_out and out.shape[1] == hidden, "add_rmsnorm: out shape")
+    wr = 1 if (write_residual and rows is None and delta is not None) else 0
+    core().call("ll_add_rmsnorm", c_int(_dtype_code(residual)), _ptr(out), _ptr(residual), _ptr(delta), _ptr(weight),
+                c_float(eps), c_int(n_out), c_int(hidden), _ptr(rows), c_int(wr), _stream())
+
+
+def bias_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: Optional[torch.Tensor],
+                    cos_sin: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                    slot_map: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                    v_cache: Optional[torch.Tensor], page_size: int, status: Optional[torch.Tensor],
+                    num_tokens: Optional[int] = None) -> None:
+    """Bias, half-split rotation of q and k, and the store of k and v into a cache plane.
+
+    Each of the three is skipped when its argument is None.  ``cos_sin`` is the
+    float32 table [max_positions, rot_dim] (cos half, then sin half).
+    """
+    _need_cuda(qkv, bias, positions, cos_sin, slot_map, k_cache, v_cache)
+    _f32(bias, "bias")
+    _f32(cos_sin, "cos_sin")
+    _i32(positions, "positions")
+    _i32(slot_map, "slot_map")
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    _need(qkv.dim() == 2 and qkv.shape[1] == width and qkv.stride(1) == 1, "qkv must be [tokens, (nh+2nkv)*hd]")
+    n = qkv.shape[0] if num_tokens is None else num_tokens
+    if bias is not None:
+        _need(bias.numel() == width, "bias size")
+    rot_dim, max_pos = 0, 0
+    if cos_sin is not None:
+        _need(positions is not None, "rotation needs positions")
+        max_pos, rot_dim = cos_sin.shape
+    num_slots = 0
+    if slot_map is not None:
+        _need(k_cache is not None and v_cache is not None, "store needs the cache plane")
+        _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache dtype differs from activations")
+        _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache plane must be contiguous")
+        _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache plane shape")
+        num_slots = k_cache.shape[0] * page_size
+    core().call("ll_bias_rope_store", c_int(_dtype_code(qkv)), _ptr(qkv), c_long(qkv.stride(0)), _ptr(bias),
+                _ptr(positions), _ptr(cos_sin), c_int(max_pos), c_int(rot_dim), c_int(num_heads),
+                c_int(num_kv_heads), c_int(head_dim), _ptr(slot_map), _ptr(k_cache), _ptr(v_cache),
+                c_int(page_size), c_long(num_slots), c_int(n), _ptr(status), _stream())
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
+    _need_cuda(out, gate_up)
+    _need(gate_up.is_contiguous() and out.is_contiguous() and out.dtype == gate_up.dtype, "silu_mul: layout")
+    n, two_i = gate_up.shape
+    _need(two_i % 2 == 0 and out.shape[0] == n and out.shape[1] == two_i // 2, "silu_mul: shapes")
+    core().call("ll_silu_mul", c_int(_dtype_code(out)), _ptr(out), _ptr(gate_up), c_int(n), c_int(two_i // 2),
+                _stream())
+
+
+def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor,
+                            v_cache: torch.Tensor, block_table: torch.Tensor, token_req: torch.Tensor,
+                            req_slot: torch.Tensor, positions: torch.Tensor, num_tokens: int, num_heads: int,
+                            num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int], scale: float,
+                            status: Optional[torch.Tensor]) -> None:
+    """Attention of every new token over its request's cached keys (any sizes, both dtypes).
+
+    ``q`` points at the first query head of the first token; head h of token t
+    is at ``q + t*q_stride + h*head_dim`` (elements).
+    """
+    _need_cuda(out, q, k_cache, v_cache, block_table, token_req, req_slot, positions)
+    for t, nm in ((block_table, "block_table"), (token_req, "token_req"), (req_slot, "req_slot"),
+                  (positions, "positions")):
+        _i32(t, nm)
+    _need(head_dim <= 256, f"head_dim {head_dim} is larger than the generic attention kernel takes (256)")
+    _need(num_heads % num_kv_heads == 0, "num_heads must be a multiple of num_kv_heads")
+    _need(out.dtype == q.dtype == k_cache.dtype == v_cache.dtype, "attention: dtypes differ")
+    _need(out.stride(1) == 1 and out.shape[1] == num_heads * head_dim, "attention: out shape")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache plane must be contiguous")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache plane shape")
+    core().call("ll_paged_attention_generic", c_int(_dtype_code(out)), _ptr(out), c_long(out.stride(0)), _ptr(q),
+                c_long(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.stride(0)),
+                _ptr(token_req), _ptr(req_slot), _ptr(positions), c_int(num_tokens), c_int(num_heads),
+                c_int(num_kv_heads), c_int(head_dim), c_int(page_size), c_int(k_cache.shape[0]),
+                c_int(window or 0), c_float(scale), _ptr(status), _stream())
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           uniform: Optional[torch.Tensor] = None, rows: Optional[int] = None) -> None:
+    """Greedy (temperature None or <= 0) or temperature sampling of each row of float32 logits."""
+    _need_cuda(logits, out, temperature, uniform)
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "logits must be float32 2-D")
+    _i32(out, "out")
+    _f32(temperature, "temperature")
+    _f32(uniform, "uniform")
+    n = logits.shape[0] if rows is None else rows
+    _need(out.numel() >= n, "sample: out too small")
+    core().call("ll_sample", _ptr(logits), c_long(logits.stride(0)), _ptr(temperature), _ptr(uniform), _ptr(out),
+                c_int(n), c_int(logits.shape[1]), _stream())
+
+
+# --------------------------------------------------------------------------
+def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [n, in] times weight [out, in] transposed: a library (cuBLAS) product.
+
+    float32 operands give a true float32 product (TF32 is off); bfloat16
+    operands accumulate in float32.  ``out_dtype=torch.float32`` with bfloat16
+    operands keeps the float32 accumulator as the result (the logits).
+    """
+    _need_cuda(x, weight)
+    if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise RuntimeError("TF32 is on; call ops.configure_matmul_precision() before a float32 product")
+    if out_dtype is not None and out_dtype != x.dtype:
+        res = torch.mm(x, weight.t(), out_dtype=out_dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    if out is not None:
+        return torch.mm(x, weight.t(), out=out)
+    return torch.mm(x, weight.t())

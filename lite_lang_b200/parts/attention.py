@@ -1,0 +1,115 @@
+"""Grouped-query attention over the paged cache, with q/k/v bias.
+
+Per layer (``litelang/models/qwen2/layer/transformer_layer.py:94-194``):
+q|k|v projection with bias, rotation of q and k, k and v written to the
+request's cache, attention of each new token over the request's cached keys
+(query head a uses kv head a // group, scores scaled by head_dim^-1/2, causal),
+output projection without bias.  The reference fuses k and v only
+(``layer_weights/load_weights.py:110-116``); here q, k and v are one projection.
+
+Differences that come with this engine: any number of new tokens per request in
+one step (portions of prompts beside decoded tokens), pages of ``page_size``
+tokens instead of one token (``litelang/models/cache.py:138``), bias added and
+rotation done in float32 in one kernel that also writes the cache, and an
+optional window of the last ``window`` positions.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import ops
+from ..config.spec import PartSpec
+from .base import Mixer, PagedKVNeed, TensorDecl, build_part, register_part
+
+
+class GQAttention(Mixer):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.num_heads = int(p["num_heads"])
+        self.num_kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.qkv_bias = bool(p.get("qkv_bias", False))
+        self.out_bias = bool(p.get("out_bias", False))
+        self.scale = float(p.get("scale", self.head_dim ** -0.5))
+        self.window = p.get("window")
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("gqa_attention: num_heads must be a multiple of num_kv_heads")
+        if self.out_bias:
+            raise ValueError("gqa_attention: a bias on the output projection is not built")
+        pos = p.get("position")
+        self.position = build_part("position", pos) if pos is not None else None
+        self.q_width = self.num_heads * self.head_dim
+        self.kv_width = self.num_kv_heads * self.head_dim
+        self.w_qkv = None
+        self.b_qkv = None
+        self.w_o = None
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        h = self.hidden_size
+        d = {
+            "q_proj.weight": TensorDecl((self.q_width, h)),
+            "k_proj.weight": TensorDecl((self.kv_width, h)),
+            "v_proj.weight": TensorDecl((self.kv_width, h)),
+            "o_proj.weight": TensorDecl((h, self.q_width)),
+        }
+        if self.qkv_bias:
+            d["q_proj.bias"] = TensorDecl((self.q_width,), "bias")
+            d["k_proj.bias"] = TensorDecl((self.kv_width,), "bias")
+            d["v_proj.bias"] = TensorDecl((self.kv_width,), "bias")
+        return d
+
+    def load(self, fetch, dtype, device) -> None:
+        w = [fetch(n).to(dtype) for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight")]
+        self.w_qkv = torch.cat(w, dim=0).to(device).contiguous()
+        if self.qkv_bias:
+            b = [fetch(n).to(torch.float32) for n in ("q_proj.bias", "k_proj.bias", "v_proj.bias")]
+            self.b_qkv = torch.cat(b, dim=0).to(device).contiguous()
+        self.w_o = fetch("o_proj.weight").to(dtype).to(device).contiguous()
+
+    def weight_bytes(self) -> int:
+        n = self.w_qkv.numel() * self.w_qkv.element_size() + self.w_o.numel() * self.w_o.element_size()
+        if self.b_qkv is not None:
+            n += self.b_qkv.numel() * 4
+        return n
+
+    def cache_need(self):
+        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    def prepare(self, device, dtype) -> None:
+        if self.position is not None:
+            self.position.prepare(device)
+
+    # ------------------------------------------------------------------
+    def forward(self, x, step, cache):
+        n = x.shape[0]
+        qkv = ops.linear(x, self.w_qkv)
+        slot_map = cache.slot_map if cache.writable else None
+        if self.position is None or self.position.fuses_with_store:
+            table = self.position.fused_table() if self.position is not None else None
+            ops.bias_rope_store(qkv, self.b_qkv, step.positions, table, self.num_heads, self.num_kv_heads,
+                                self.head_dim, slot_map, cache.k, cache.v, cache.page_size, step.status, n)
+        else:
+            if self.b_qkv is not None:
+                ops.bias_rope_store(qkv, self.b_qkv, None, None, self.num_heads, self.num_kv_heads, self.head_dim,
+                                    None, None, None, cache.page_size, step.status, n)
+            self.position.apply(qkv, step.positions, self.num_heads, self.num_kv_heads, self.head_dim, n)
+            if slot_map is not None:
+                ops.bias_rope_store(qkv, None, None, None, self.num_heads, self.num_kv_heads, self.head_dim,
+                                    slot_map, cache.k, cache.v, cache.page_size, step.status, n)
+        attn = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
+        self.attend(attn, qkv, step, cache)
+        return ops.linear(attn, self.w_o)
+
+    def attend(self, out, qkv, step, cache) -> None:
+        """Attention of the step's tokens over the cache plane; picks the kernel by shape."""
+        ops.paged_attention_generic(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.token_req,
+                                    step.req_slot, step.positions, qkv.shape[0], self.num_heads, self.num_kv_heads,
+                                    self.head_dim, cache.page_size, self.window, self.scale, step.status)
+
+
+register_part("mixer", "gqa_attention", GQAttention)

@@ -1,0 +1,22 @@
+"""Pre-norm arrangement: h += mixer(norm(h)); h += feed_forward(norm(h)).
+
+``litelang/models/qwen2/layer/transformer_layer.py:46-77``.  The residual sums
+are folded into the norm that follows them (one pass over the row instead of
+two), which is why a block hands its last, not yet added, output on as ``delta``.
+"""
+
+from __future__ import annotations
+
+from .base import Block, register_part
+
+
+class PreNormBlock(Block):
+    def forward(self, h, delta, step, cache):
+        x = self.mixer_norm.add_forward(h, delta)
+        a = self.mixer.forward(x, step, cache)
+        x = self.feed_forward_norm.add_forward(h, a)
+        f = self.feed_forward.forward(x, step)
+        return h, f
+
+
+register_part("block", "pre_norm", PreNormBlock)
