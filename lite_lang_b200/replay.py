@@ -104,6 +104,8 @@ def main(argv=None) -> int:
             if rid in slots:
                 manager.close(slots.pop(rid))
         print(f"done {step}", flush=True)
+    print(f"trace_run: {runner.steps_run} steps, {runner.graph_replays} graph replays, "
+          f"pages handed out {manager.pages_handed_out}, pages reused {manager.pages_reused}", file=sys.stderr)
     return 0
 
 

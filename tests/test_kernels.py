@@ -1,0 +1,293 @@
+"""Each CUDA kernel alone against its plain float32 formula, at sizes other than the engine tests' (GPU)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen2_plain as P
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def tol(dtype):
+    return 2e-6 if dtype == torch.float32 else 1.6e-2     # bfloat16: two roundings of 2^-8 relative
+
+
+def assert_close(got, ref, dtype, what=""):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    scale = float(ref.abs().max()) or 1.0
+    err = float((got - ref).abs().max()) / scale
+    assert err <= tol(dtype), f"{what}: {err:.3e} > {tol(dtype):.1e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(72, 101), (1536, 333), (50, 7)])
+def test_embedding(dtype, hidden, vocab):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, hidden, generator=g).to(dtype).to(dev())
+    ids = torch.randint(0, vocab, (37,), generator=g, dtype=torch.int32).to(dev())
+    out = torch.empty(37, hidden, dtype=dtype, device=dev())
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    ops.embed_gather(out, table, ids, status)
+    assert torch.equal(out.cpu(), P.embedding(table.cpu(), ids.cpu()))
+    assert status.item() == 0
+    bad = ids.clone()
+    bad[3] = vocab
+    ops.embed_gather(out, table, bad, status)
+    assert status.item() == 1 and float(out[3].float().abs().max()) == 0.0     # refused, not read out of bounds
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden,eps", [(5, 96, 1e-5), (33, 1536, 1e-6), (2, 250, 1e-3), (1, 8192, 1e-6)])
+def test_rmsnorm_alone_and_fused(dtype, rows, hidden, eps):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    x = (3 * torch.randn(rows, hidden, generator=g)).to(dtype)
+    d = torch.randn(rows, hidden, generator=g).to(dtype)
+    w = (1 + 0.2 * torch.randn(hidden, generator=g))
+    xd, dd, wd = x.to(dev()), d.to(dev()), w.to(dev())
+    out = torch.empty_like(xd)
+    ops.rmsnorm(out, xd, wd, eps)
+    assert_close(out, P.rms_norm(x.float(), w, eps), dtype, "rmsnorm")
+    # fused with the residual sum: the residual is replaced by the rounded sum
+    res = xd.clone()
+    ops.add_rmsnorm(out, res, dd, wd, eps)
+    s = (x.float() + d.float()).to(dtype)
+    assert torch.equal(res.cpu(), s)
+    assert_close(out, P.rms_norm(s.float(), w, eps), dtype, "add_rmsnorm")
+    # selected rows only, nothing written back
+    rows_idx = torch.tensor([rows - 1, 0], dtype=torch.int32, device=dev())
+    res2 = xd.clone()
+    out2 = torch.empty(2, hidden, dtype=dtype, device=dev())
+    ops.add_rmsnorm(out2, res2, dd, wd, eps, rows_idx)
+    assert torch.equal(res2, xd)
+    assert_close(out2, P.rms_norm(s.float(), w, eps)[[rows - 1, 0]], dtype, "add_rmsnorm rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [8, 40, 203, 8960])
+def test_silu_mul(dtype, inter):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    gu = (2 * torch.randn(7, 2 * inter, generator=g)).to(dtype)
+    out = torch.empty(7, inter, dtype=dtype, device=dev())
+    ops.silu_mul(out, gu.to(dev()))
+    assert_close(out, P.silu_and_mul(gu[:, :inter].float(), gu[:, inter:].float()), dtype, "silu_mul")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rot,ps", [(6, 2, 48, 48, 4), (3, 1, 128, 128, 16), (4, 4, 80, 32, 8)])
+def test_bias_rope_store(dtype, nh, nkv, hd, rot, ps):
+    from lite_lang_b200 import ops
+    from lite_lang_b200.parts.rope import rope_table
+    g = torch.Generator().manual_seed(3)
+    T, max_pos, num_pages = 11, 300, 9
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width, generator=g).to(dtype)
+    bias = 0.5 * torch.randn(width, generator=g)
+    pos = torch.randint(0, max_pos, (T,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(num_pages * ps, generator=g)[:T].to(torch.int32)
+    slots[4] = -1                                             # a token whose k/v are not stored
+    table = rope_table(rot, 12345.0, max_pos)
+    kc = torch.zeros(num_pages, nkv, ps, hd, dtype=dtype, device=dev())
+    vc = torch.zeros_like(kc)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    q_dev = qkv.to(dev()).clone()
+    ops.bias_rope_store(q_dev, bias.to(dev()), pos.to(dev()), table.to(dev()), nh, nkv, hd, slots.to(dev()), kc, vc,
+                        ps, status)
+    assert status.item() == 0
+    x = qkv.float() + bias
+    q = x[:, :nh * hd].view(T, nh, hd)
+    k = x[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
+    v = x[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    cos, sin = P.rope_tables(rot, 12345.0, pos)
+    q_ref = torch.cat((P.apply_rope(q[..., :rot], cos, sin), q[..., rot:]), dim=-1)
+    k_ref = torch.cat((P.apply_rope(k[..., :rot], cos, sin), k[..., rot:]), dim=-1)
+    assert_close(q_dev[:, :nh * hd].view(T, nh, hd), q_ref, dtype, "q")
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        page, off = divmod(s, ps)
+        assert_close(kc[page, :, off, :], k_ref[t], dtype, f"k of token {t}")
+        assert_close(vc[page, :, off, :], v[t], dtype, f"v of token {t}")
+    used = {int(s) for s in slots if s >= 0}
+    for s in range(num_pages * ps):                            # nothing else was touched
+        if s not in used:
+            page, off = divmod(s, ps)
+            assert float(kc[page, :, off, :].float().abs().max()) == 0.0
+
+
+def _paged_case(dtype, nh, nkv, hd, ps, lens, q_lens, window, seed, peak=None):
+    """Requests with `lens` cached tokens each, the last `q_lens` of which are this step's queries.
+    Pages are scattered over the pool in a random order.  Returns kernel inputs and the plain result."""
+    g = torch.Generator().manual_seed(seed)
+    n = len(lens)
+    max_blocks = max((l + ps - 1) // ps for l in lens) + 1
+    num_pages = sum((l + ps - 1) // ps for l in lens) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    bt = torch.full((n + 2, max_blocks), -1, dtype=torch.int32)
+    kc = torch.zeros(num_pages, nkv, ps, hd)
+    vc = torch.zeros(num_pages, nkv, ps, hd)
+    slots_of_req = [1 + i for i in range(n)]                   # request slots differ from entry indices
+    q_rows, token_req, positions, ref_rows = [], [], [], []
+    for i, (l, ql) in enumerate(zip(lens, q_lens)):
+        k = torch.randn(l, nkv, hd, generator=g)
+        v = torch.randn(l, nkv, hd, generator=g)
+        q = torch.randn(l, nh, hd, generator=g)
+        if peak is not None:                                   # one far key dominates the last query
+            far = peak(l)
+            k[far] *= 0.0
+            k[far, :, 0] = 30.0
+            q[l - 1] *= 0.1
+            q[l - 1, :, 0] = 30.0 / math.sqrt(hd) * 4
+            v[far] = 5.0
+        k, v, q = k.to(dtype).float(), v.to(dtype).float(), q.to(dtype).float()
+        for lp in range((l + ps - 1) // ps):
+            page = perm.pop()
+            bt[slots_of_req[i], lp] = page
+            m = min(ps, l - lp * ps)
+            kc[page, :, :m] = k[lp * ps:lp * ps + m].transpose(0, 1)
+            vc[page, :, :m] = v[lp * ps:lp * ps + m].transpose(0, 1)
+        o = P.attention(q, k, v, window)
+        for t in range(l - ql, l):
+            q_rows.append(q[t].reshape(-1))
+            token_req.append(i)
+            positions.append(t)
+            ref_rows.append(o[t].reshape(-1))
+    d = dev()
+    return dict(q=torch.stack(q_rows).to(dtype).to(d), kc=kc.to(dtype).to(d), vc=vc.to(dtype).to(d), bt=bt.to(d),
+                token_req=torch.tensor(token_req, dtype=torch.int32, device=d),
+                req_slot=torch.tensor(slots_of_req, dtype=torch.int32, device=d),
+                positions=torch.tensor(positions, dtype=torch.int32, device=d),
+                ref=torch.stack(ref_rows), lens=lens, q_lens=q_lens)
+
+
+GENERIC_SHAPES = [
+    # nh, nkv, hd, page, lens, q_lens, window
+    (6, 2, 48, 4, [70, 1, 33], [70, 1, 5], None),
+    (10, 1, 80, 16, [300, 45], [1, 45], None),             # group 10 > 8 heads a block
+    (3, 3, 256, 8, [40, 129], [3, 1], None),
+    (4, 2, 32, 32, [200, 64, 65], [10, 64, 1], 33),
+    (8, 2, 128, 16, [700], [1], None),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,ps,lens,q_lens,window", GENERIC_SHAPES)
+def test_paged_attention_generic(dtype, nh, nkv, hd, ps, lens, q_lens, window):
+    from lite_lang_b200 import ops
+    c = _paged_case(dtype, nh, nkv, hd, ps, lens, q_lens, window, seed=5)
+    out = torch.empty_like(c["q"])
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    ops.paged_attention_generic(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], c["token_req"],
+                                c["req_slot"], c["positions"], c["q"].shape[0], nh, nkv, hd, ps, window,
+                                hd ** -0.5, status)
+    assert status.item() == 0
+    assert_close(out, c["ref"], dtype, "generic attention")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("where", ["first", "page_edge", "window_in", "window_out"])
+def test_generic_attention_finds_one_far_key(dtype, where):
+    """A single key carries nearly all the weight: a kernel that misses it (a page's first slot, the
+    window's first position) or reads it although the window excludes it gives a very different row."""
+    from lite_lang_b200 import ops
+    nh, nkv, hd, ps, L, window = 4, 2, 64, 16, 400, None
+    if where == "first":
+        peak = lambda l: 0
+    elif where == "page_edge":
+        peak = lambda l: 16 * 7
+    else:
+        window = 100
+        peak = (lambda l: l - 100) if where == "window_in" else (lambda l: l - 101)
+    c = _paged_case(dtype, nh, nkv, hd, ps, [L], [1], window, seed=6, peak=peak)
+    out = torch.empty_like(c["q"])
+    ops.paged_attention_generic(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], c["token_req"],
+                                c["req_slot"], c["positions"], 1, nh, nkv, hd, ps, window, hd ** -0.5, None)
+    assert_close(out, c["ref"], dtype, where)
+    mean_v = float(c["ref"].mean())
+    assert (mean_v > 4.5) == (where != "window_out")          # the case does what it is meant to do
+
+
+def test_padding_entries_write_zeros_and_read_nothing():
+    from lite_lang_b200 import ops
+    c = _paged_case(torch.float32, 4, 2, 32, 8, [20], [1], None, seed=8)
+    q = torch.cat([c["q"], c["q"]])
+    token_req = torch.tensor([0, 1], dtype=torch.int32, device=dev())
+    req_slot = torch.tensor([int(c["req_slot"][0]), -1], dtype=torch.int32, device=dev())
+    positions = torch.tensor([19, 0], dtype=torch.int32, device=dev())
+    out = torch.full_like(q, 7.0)
+    ops.paged_attention_generic(out, q, q.stride(0), c["kc"], c["vc"], c["bt"], token_req, req_slot, positions, 2,
+                                4, 2, 32, 8, None, 32 ** -0.5, None)
+    assert_close(out[:1], c["ref"], torch.float32)
+    assert float(out[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("vocab", [7, 1000, 151936, 50257])
+def test_greedy_is_argmax_with_lowest_index_on_ties(vocab):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(4)
+    logits = torch.randn(5, vocab, generator=g)
+    logits[1, vocab // 2] = logits[1, vocab - 1] = 50.0        # a tie
+    logits[2, 0] = 60.0
+    logits[3, vocab - 1] = 60.0
+    out = torch.zeros(5, dtype=torch.int32, device=dev())
+    ops.sample(logits.to(dev()), out)
+    assert out.cpu().tolist() == torch.argmax(logits, dim=-1).tolist()
+    assert out[1].item() == vocab // 2
+
+
+@pytest.mark.parametrize("vocab", [13, 2048, 151936])
+def test_temperature_sampling_walks_the_cdf(vocab):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    rows = 40
+    logits = 3 * torch.randn(rows, vocab, generator=g)
+    temps = torch.tensor([0.7, 1.0, 0.3, 1.5] * (rows // 4))
+    temps[5] = 0.0                                             # greedy row among sampled ones
+    u = torch.rand(rows, generator=g)
+    out = torch.zeros(rows, dtype=torch.int32, device=dev())
+    ops.sample(logits.to(dev()), out, temps.to(dev()), u.to(dev()))
+    got = out.cpu().tolist()
+    for r in range(rows):
+        if temps[r] == 0:
+            assert got[r] == int(torch.argmax(logits[r]))
+            continue
+        p = P.temperature_probs(logits[r], float(temps[r]))
+        cdf = torch.cumsum(p, 0)
+        i = got[r]
+        lo = float(cdf[i - 1]) if i > 0 else 0.0
+        hi = float(cdf[i])
+        # the token's CDF interval holds u, up to float32 rounding of the sums
+        assert lo - 1e-4 <= float(u[r]) <= hi + 1e-4, (r, i, lo, float(u[r]), hi)
+    # the distribution is right: many draws of one row
+    row = torch.tensor([2.0, 1.0, 0.0, -1.0, 1.5]).repeat(4000, 1)
+    uu = torch.rand(4000, generator=g)
+    out = torch.zeros(4000, dtype=torch.int32, device=dev())
+    ops.sample(row.to(dev()), out, torch.full((4000,), 0.8).to(dev()), uu.to(dev()))
+    freq = torch.bincount(out.cpu().long(), minlength=5).double() / 4000
+    assert float((freq - P.temperature_probs(row[0], 0.8)).abs().max()) < 0.03
+
+
+def test_kernels_refuse_what_they_do_not_take():
+    from lite_lang_b200 import ops
+    x = torch.zeros(2, 8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.rmsnorm(torch.empty_like(x), x, torch.ones(8), 1e-6)       # CPU tensors: no fallback
+    d = dev()
+    with pytest.raises(TypeError):
+        ops.rmsnorm(torch.empty(2, 8, dtype=torch.float16, device=d), torch.zeros(2, 8, dtype=torch.float16, device=d),
+                    torch.ones(8, device=d), 1e-6)
+    with pytest.raises(ValueError, match="head_dim"):
+        c = _paged_case(torch.float32, 2, 1, 32, 8, [9], [1], None, seed=1)
+        ops.paged_attention_generic(torch.empty(1, 2 * 320, device=d), c["q"], 640, c["kc"], c["vc"], c["bt"],
+                                    c["token_req"], c["req_slot"], c["positions"], 1, 2, 1, 320, 8, None, 1.0, None)

@@ -1,0 +1,219 @@
+"""The scheduler's decisions, with a stand-in for the step function (no GPU)."""
+import random
+
+import pytest
+
+from lite_lang_b200.cache import CacheManager, PagedGroupSpec
+from lite_lang_b200.engine.scheduler import (STRATEGIES, Request, Scheduler, peak_token_estimate)
+from lite_lang_b200.sampling import SamplingParams
+
+
+def make(num_pages=16, page_size=4, max_requests=4, max_len=64, budget=8, strategy="LIFOStrategy", window=None):
+    m = CacheManager([PagedGroupSpec(1, 16, window, 1)], [num_pages], page_size, max_requests, max_len)
+    return m, Scheduler(m, budget, max_reqs=100, busy_scale=0.6, strategy=strategy)
+
+
+def req(i, n_prompt, max_new, eos=()):
+    return Request(i, list(range(1, n_prompt + 1)), SamplingParams(), max_new, tuple(eos))
+
+
+def run_step(m, s, token=7):
+    """What the engine does around a step: run the plan, advance the cache, commit."""
+    plan = s.plan()
+    for p in plan:
+        assert p.request.slot is not None and p.count >= 1
+        m.advance(p.request.slot, m.length(p.request.slot) + p.count)
+    done = s.commit(plan, [token if p.samples else None for p in plan])
+    m.check_invariants()
+    return plan, done
+
+
+def test_prompts_are_cut_under_the_token_budget():
+    m, s = make(budget=8)
+    a = req(0, 19, 2)
+    s.add(a)
+    counts = []
+    while s.has_work():
+        plan, _ = run_step(m, s)
+        counts.append([(p.request.id, p.start, p.count, p.samples) for p in plan])
+    assert counts[0] == [(0, 0, 8, False)]
+    assert counts[1] == [(0, 8, 8, False)]
+    assert counts[2] == [(0, 16, 3, True)]        # the last portion gives the first new token
+    assert counts[3] == [(0, 19, 1, True)]        # then one token a step
+    assert a.output == [7, 7] and a.finish_reason == "length"
+    assert m.num_free_pages() == 16
+
+
+def test_decode_tokens_come_first_and_share_the_step_with_portions():
+    m, s = make(budget=8)
+    a, b = req(0, 3, 5), req(1, 20, 2)
+    s.add(a)
+    run_step(m, s)                 # a prefilled, first token
+    s.add(b)
+    plan, _ = run_step(m, s)
+    assert [(p.request.id, p.count) for p in plan] == [(0, 1), (1, 7)]   # 1 + 7 = budget
+    plan, _ = run_step(m, s)
+    assert [(p.request.id, p.count) for p in plan] == [(0, 1), (1, 7)]
+    plan, _ = run_step(m, s)
+    assert [(p.request.id, p.count, p.samples) for p in plan] == [(0, 1, True), (1, 6, True)]
+
+
+def test_finish_rules():
+    m, s = make(budget=16)
+    a, b, c = req(0, 3, 10, eos=(7,)), req(1, 3, 10, eos=(9,)), req(2, 3, 2)
+    a.params = SamplingParams(ignore_eos=False)
+    b.params = SamplingParams()
+    for r in (a, b, c):
+        s.add(r)
+    _, done = run_step(m, s, token=7)
+    assert [r.id for r in done] == [0] and a.finish_reason == "eos"
+    _, done = run_step(m, s, token=7)
+    assert [r.id for r in done] == [2] and c.finish_reason == "length"
+    assert b.status == "running"
+    d = req(3, 3, 10, eos=(7,))
+    d.params = SamplingParams(ignore_eos=True)
+    s.add(d)
+    run_step(m, s, token=7)
+    assert d.status == "running" and d.output == [7]
+
+
+def test_model_length_ends_a_request():
+    m, s = make(max_len=8, num_pages=16)
+    a = req(0, 5, 100)
+    s.add(a)
+    while s.has_work():
+        run_step(m, s)
+    assert a.finish_reason == "model_len" and a.length == 8
+    b = req(1, 8, 4)        # prompt + 1 > max_model_len
+    s.add(b)
+    assert b.finish_reason == "too_long" and not s.has_work()
+
+
+def test_peak_estimate_is_the_references_formula():
+    # litelang/scheduler/req_queue.py:219-232 on [(held, expected)]
+    rows = [(10, 5), (3, 20), (7, 1)]
+    # sorted by expected desc: (3,20),(10,5),(7,1): cumsum held 3,13,20; + expected*k: 23, 23, 23
+    assert peak_token_estimate(rows) == 23
+    assert peak_token_estimate([(4, 6)]) == 10
+    assert peak_token_estimate([]) == 0
+
+
+def test_admission_waits_for_room_in_the_estimate():
+    m, s = make(num_pages=8, page_size=4, budget=32)      # 32 tokens of cache
+    a, b = req(0, 8, 10), req(1, 8, 10)
+    s.add(a)
+    s.add(b)
+    plan, _ = run_step(m, s)
+    # alone a always runs; with a running, b's estimate: not busy -> 6 expected each:
+    # sorted equal: cumsum 8,16 ; 8+6*1=14, 16+6*2=28 <= 32 -> admitted in the same step
+    assert [p.request.id for p in plan] == [0, 1]
+    c = req(2, 8, 10)
+    s.add(c)
+    plan, _ = run_step(m, s)
+    assert 2 not in [p.request.id for p in plan]           # 3 requests would peak above 32
+    assert s.waiting[0] is c
+
+
+def test_out_of_pages_at_decode_preempts_the_latest_arrival():
+    m, s = make(num_pages=4, page_size=4, budget=16, strategy="LIFOStrategy")
+    a, b = req(0, 7, 6), req(1, 7, 6)
+    s.add(a)
+    run_step(m, s)
+    # force b in although the estimate would refuse it: admit by hand
+    slot = m.open()
+    b.slot, b.status, b.arrival = slot, "running", 5
+    assert m.reserve(slot, 7)
+    m.advance(slot, 7)
+    b.computed, b.output = 7, [7]
+    b.prompt = list(range(1, 8))
+    s.running.append(b)
+    assert m.num_free_pages() == 0
+    a.computed, b.computed = a.length - 1, b.length - 1
+    # both sit at 8 tokens after this step; the step after needs a third page for each
+    run_step(m, s)
+    plan, _ = run_step(m, s)
+    assert [p.request.id for p in plan] == [0]             # b (latest) left, a went on
+    assert b.status == "waiting" and b.slot is None and b.computed == 0 and b.preemptions == 1
+    assert s.waiting[0] is b                               # at the front of the queue
+    assert s.counters["preemptions"] == 1
+    kept = list(b.output)
+    # b comes back later and is recomputed from prompt + produced tokens, producing nothing twice
+    while s.has_work():
+        run_step(m, s)
+    assert b.output[:len(kept)] == kept and len(b.output) == 6 and len(a.output) == 6
+    assert a.finish_reason == b.finish_reason == "length"
+    assert m.num_free_pages() == 4
+
+
+def test_a_request_that_cannot_fit_alone_ends_with_cache_full():
+    m, s = make(num_pages=2, page_size=4, budget=16, max_len=64)
+    a = req(0, 6, 50)
+    s.add(a)
+    while s.has_work():
+        run_step(m, s)
+    assert a.finish_reason == "cache_full" and a.length == 9      # 8 cached tokens and the one drawn from them
+    assert m.num_free_pages() == 2 and m.num_free_slots == 4
+    b = req(1, 12, 5)           # the prompt alone needs 3 pages
+    s.add(b)
+    while s.has_work():
+        run_step(m, s)
+    assert b.finish_reason == "cache_full" and b.output == []
+
+
+def test_portion_shrinks_to_the_free_pages():
+    m, s = make(num_pages=4, page_size=4, budget=64)
+    a = req(0, 6, 30)
+    s.add(a)
+    run_step(m, s)                         # a holds 2 pages
+    b = req(1, 14, 2)
+    s.add(b)
+    s._fits = lambda cand: True            # take the estimate out of the picture
+    plan, _ = run_step(m, s)
+    got = {p.request.id: p.count for p in plan}
+    assert got[1] == 8                     # two free pages -> 8 tokens of b's 14
+    assert m.num_free_pages() == 0
+
+
+def test_strategies_order_as_their_names_say():
+    rs = [req(0, 5, 1), req(1, 9, 1), req(2, 2, 1)]
+    for i, r in enumerate(rs):
+        r.arrival = i
+    assert [r.id for r in STRATEGIES["FIFOStrategy"](rs)] == [0, 1, 2]
+    assert [r.id for r in STRATEGIES["LIFOStrategy"](rs)] == [2, 1, 0]
+    assert [r.id for r in STRATEGIES["ShortestLeavesFirstStrategy"](rs)] == [2, 0, 1]
+    assert [r.id for r in STRATEGIES["LongestLeavesFirstStrategy"](rs)] == [1, 0, 2]
+    with pytest.raises(ValueError):
+        make(strategy="NoSuchStrategy")
+
+
+def test_waiting_queue_is_bounded():
+    m, s = make()
+    s.max_reqs = 2
+    assert s.add(req(0, 3, 1)) and s.add(req(1, 3, 1))
+    assert not s.add(req(2, 3, 1))
+
+
+@pytest.mark.parametrize("seed", range(8))
+@pytest.mark.parametrize("strategy", sorted(STRATEGIES))
+def test_random_load_always_drains(seed, strategy):
+    rng = random.Random(seed)
+    m, s = make(num_pages=rng.randint(3, 10), page_size=4, max_requests=3, max_len=48,
+                budget=rng.choice([2, 5, 16]), strategy=strategy, window=rng.choice([None, 6]))
+    reqs = [req(i, rng.randint(1, 20), rng.randint(1, 12)) for i in range(10)]
+    pending = list(reqs)
+    steps = 0
+    while pending or s.has_work():
+        if pending and rng.random() < 0.4:
+            s.add(pending.pop(0))
+        if s.has_work():
+            plan, _ = run_step(m, s, token=rng.randint(0, 50))
+            assert sum(p.count for p in plan) <= s.budget
+            assert len({p.request.id for p in plan}) == len(plan)
+        steps += 1
+        assert steps < 5000, "the scheduler does not make progress"
+    for r in reqs:
+        assert r.status == "finished" and r.slot is None
+        assert r.finish_reason in ("length", "cache_full", "model_len")
+        if r.finish_reason == "length":
+            assert len(r.output) == r.max_new_tokens
+    assert m.num_free_pages() == m.total_pages() and m.num_free_slots == 3
