@@ -1,0 +1,341 @@
+#!/usr/bin/env python3
+"""Measurement of the engine on one B200: decode tokens a second and a 2,048-token prefill.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The model has the layer sizes of Qwen2-1.5B (28 layers, hidden 1536, 12/2 heads of
+128, intermediate 8960, vocabulary 151936, tied embeddings) with random bfloat16
+weights; prompts are seeded uniform-random token ids.  A *step* is one decode step
+of a batch of 8 requests that each hold a 2,048-token prompt and decode towards a
+context of 4,096.  One JSON line is printed:
+
+  value      decoded tokens a second, timed on the device with CUDA events around K
+             steps (index arrays are uploaded every step, tokens are not read back);
+  e2e        the same through the Python entry point (scheduler, sampling, token ids
+             from the host and back to it every step);
+  prefill    one request of 2,048 tokens in one step, logits of its last token;
+  roofline   bytes a decode step has to read (every weight once, the cache of the live
+             requests) over its time, against the measured copy bandwidth;
+  points     decode at batch 1 and 64.
+
+A decode step reads about 3.1 GB of weights, far more than the 126 MB L2, so
+iterations need no L2 flush.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN2_1P5B = dict(architectures=["Qwen2ForCausalLM"], hidden_size=1536, num_hidden_layers=28,
+                  num_attention_heads=12, num_key_value_heads=2, intermediate_size=8960, vocab_size=151936,
+                  rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+                  max_position_embeddings=32768, use_sliding_window=False, torch_dtype="bfloat16")
+PROMPT_LEN = 2048
+CONTEXT = 4096
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as fh:
+                d = json.load(fh)
+            out = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in d:
+                out["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
+            return out
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs (read-only queries)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = os.path.join(ROOT, "gpurun_out", "bench_clocks.csv")
+
+    def start(self):
+        try:
+            os.makedirs(os.path.dirname(self.path), exist_ok=True)
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.fh,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.fh.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def build_engine(layers, max_batch, dtype="bfloat16"):
+    import torch
+    from lite_lang_b200 import Engine, EngineConfig
+    from lite_lang_b200.config import config_from_dict
+
+    cfg = config_from_dict(dict(QWEN2_1P5B, num_hidden_layers=layers))
+    pages_per_req = (CONTEXT + 15) // 16
+    ecfg = EngineConfig(dtype=dtype, page_size=16, num_pages=max_batch * pages_per_req + 8,
+                        max_batch_size=max_batch, max_input_length=PROMPT_LEN, max_output_length=CONTEXT - PROMPT_LEN,
+                        max_model_len=CONTEXT, max_tokens_per_step=2048, cuda_graphs=True, seed=0)
+    return Engine(config=cfg, engine_config=ecfg, random_seed=1234)
+
+
+def random_prompts(n, length, vocab, seed):
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    return [[int(t) for t in rng.integers(0, vocab, size=length)] for _ in range(n)]
+
+
+def kv_bytes_per_token(engine):
+    n = 0
+    for g in engine.model.cache_groups:
+        if g.kind == "paged":
+            n += g.planes * 2 * g.num_kv_heads * g.head_dim * 2
+    return n
+
+
+def prefill_flops(cfg, tokens):
+    qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    per_layer = cfg.hidden_size * qkv + cfg.num_attention_heads * cfg.head_dim * cfg.hidden_size \
+        + 3 * cfg.hidden_size * cfg.intermediate_size
+    linear = 2 * tokens * cfg.num_hidden_layers * per_layer
+    attn = 2 * tokens * tokens * cfg.num_attention_heads * cfg.head_dim * cfg.num_hidden_layers   # causal: half of 4 T^2
+    head = 2 * cfg.hidden_size * cfg.vocab_size
+    return linear + attn + head
+
+
+def device_decode(engine, batch, steps, warmup, sampler_on=True):
+    """K decode steps of `batch` requests, timed on the device.  Returns (ms per step, mean context)."""
+    import torch
+    from lite_lang_b200.engine.batch import StepEntry
+
+    m, runner = engine.manager, engine.runner
+    vocab = engine.model.spec.vocab_size
+    prompts = random_prompts(batch, PROMPT_LEN, vocab, 7)
+    slots = []
+    for p in prompts:                                   # prefill, untimed
+        s = m.open()
+        assert s is not None and runner.reserve(s, PROMPT_LEN)
+        runner.step([StepEntry(s, p, ())])
+        slots.append(s)
+    torch.cuda.synchronize()
+    toks = random_prompts(1, steps + warmup, vocab, 9)[0]
+
+    def one(i):
+        entries = []
+        for s in slots:
+            assert runner.reserve(s, 1)
+            entries.append(StepEntry(s, [toks[i]], (0,)))
+        logits = runner.step(entries)
+        if sampler_on:
+            engine.sampler.sample(logits, [0.0] * batch, [0.0] * batch)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    ctx0 = m.length(slots[0])
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    ctx1 = m.length(slots[0])
+    runner.check_status()
+    for s in slots:
+        m.close(s)
+    return ms, (ctx0 + ctx1) / 2.0
+
+
+def e2e_decode(engine, batch, steps, warmup):
+    """The same through Engine.step(): scheduler, sampling, tokens to the host every step."""
+    import torch
+    from lite_lang_b200 import SamplingParams
+
+    vocab = engine.model.spec.vocab_size
+    prompts = random_prompts(batch, PROMPT_LEN, vocab, 7)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=steps + warmup + 8, ignore_eos=True)
+    reqs = [engine.add_request(p, sp) for p in prompts]
+    while any(len(r.output) < 1 + warmup for r in reqs):    # prefill and warm-up decode steps
+        engine.step()
+    torch.cuda.synchronize()
+    n0 = sum(len(r.output) for r in reqs)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    n1 = sum(len(r.output) for r in reqs)
+    while engine.scheduler.has_work():                      # drain: give the cache back
+        for r in list(engine.scheduler.running):
+            r.max_new_tokens = len(r.output) + 1
+        engine.step()
+    h2d = engine.runner.single_builder.total * 4
+    d2h = engine._result_host.numel() * 4
+    return (n1 - n0) / dt, h2d, d2h, dt / steps * 1e3
+
+
+def prefill_once(engine, repeats=3):
+    import torch
+    from lite_lang_b200.engine.batch import StepEntry
+
+    m, runner = engine.manager, engine.runner
+    prompt = random_prompts(1, PROMPT_LEN, engine.model.spec.vocab_size, 11)[0]
+    best = None
+    for _ in range(repeats + 2):
+        s = m.open()
+        assert runner.reserve(s, PROMPT_LEN)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step([StepEntry(s, prompt, (PROMPT_LEN - 1,))])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        m.close(s)
+        best = ms if best is None else min(best, ms)
+    return best
+
+
+def run_ours(args):
+    import torch
+    from lite_lang_b200.csrc import build as kbuild
+
+    pk = peaks()
+    layers_full = QWEN2_1P5B["num_hidden_layers"]
+    layers = args.layers or layers_full
+    batch = args.batch
+    engine = build_engine(layers, max(64, batch))
+    cfg = engine.model_config
+    weight_bytes = engine.model.weight_bytes_per_step()
+    kvb = kv_bytes_per_token(engine)
+
+    points = {}
+    for b in (1, 64):
+        ms, _ = device_decode(engine, b, max(16, args.steps // 4), max(3, args.warmup))
+        points[f"decode_b{b}"] = round(b / ms * 1e3, 1)
+
+    prefill_ms = prefill_once(engine)
+    pf = prefill_flops(cfg, PROMPT_LEN)
+
+    clocks = ClockSampler()
+    clocks.start()
+    launches0 = kbuild.LAUNCHES
+    ms, ctx = device_decode(engine, batch, args.steps, args.warmup)
+    clk = clocks.stop()
+    bucket = engine.runner._bucket(batch)
+    per_step_kernels = engine.runner.graph_kernel_launches.get(bucket, 0) + 1        # + the sampling kernel
+    value = batch / ms * 1e3
+    step_bytes = weight_bytes + batch * ctx * kvb
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    e2e_value, h2d, d2h, e2e_ms = e2e_decode(engine, batch, args.steps, args.warmup)
+
+    out = {
+        "metric": "decode tok/s (Qwen2-1.5B shape, 1xB200)", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "Qwen2-1.5B-shaped, random weights", "layers": layers, "layers_full": layers_full,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "tied_embeddings": cfg.tie_word_embeddings, "global_batch": batch, "seq_len": CONTEXT,
+                   "prompt_len": PROMPT_LEN, "mean_context_timed": round(ctx, 1), "page_size": 16,
+                   "parallelism": "single GPU", "l2": "step inputs (3.1 GB of weights) exceed L2; no flush",
+                   "peaks": pk["source"]},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4)},
+        "gpu_launches": per_step_kernels * args.steps,
+        "gpu_launches_per_step": per_step_kernels,
+        "prefill": {"value": round(PROMPT_LEN / prefill_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(prefill_ms, 3),
+                    "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "step_bytes": int(step_bytes)},
+        "points": points,
+        "clocks": clk,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+def run_reference(args):
+    """The unmodified reference from baseline/_ref through its own runner API, if it is installed."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref, "litelang")):
+        why = "the reference is not installed under baseline/_ref"
+    if why is None:
+        try:
+            from baseline.reference_arm import run as run_ref   # noqa
+            return run_ref(args)
+        except Exception as exc:  # the reference could not run here: say why in one line
+            why = f"{type(exc).__name__}: {str(exc).splitlines()[0] if str(exc) else ''}"[:300]
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (reported in config)")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {args.gpus} is not built (this engine has no multi-GPU path)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

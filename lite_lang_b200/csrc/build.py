@@ -37,6 +37,7 @@ LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
 }
 
 _HEADERS = ("common.cuh",)
+LAUNCHES = 0   # launcher calls so far (each launches one kernel unless its docstring says otherwise)
 _lock = threading.Lock()
 _loaded: Dict[str, "Library"] = {}
 
@@ -152,7 +153,8 @@ def build_library(name: str, verbose: bool = True) -> str:
     os.replace(tmp, target)
     prefix = f"liblitelang_{name}_"
     for old in os.listdir(bdir):  # shared objects of this library built from older sources
-        if old.startswith(prefix) and old.endswith(".so") and os.path.join(bdir, old) != target:
+        if (old.startswith(prefix) and old.endswith(".so") and len(old) == len(prefix) + 16 + 3
+                and os.path.join(bdir, old) != target):
             try:
                 os.remove(os.path.join(bdir, old))
             except OSError:
@@ -188,6 +190,8 @@ class Library:
         return f
 
     def call(self, symbol: str, *args) -> None:
+        global LAUNCHES
+        LAUNCHES += 1
         err = self.fn(symbol)(*args)
         if err != 0:
             raise RuntimeError(f"{symbol} failed with CUDA error {err} "

@@ -68,6 +68,7 @@ class ModelRunner:
         self.use_graphs = bool(cuda_graphs)
         self._graphs: Dict[int, tuple] = {}
         self._graph_pool = None
+        self.graph_kernel_launches: Dict[int, int] = {}   # hand-written kernels inside each captured step
         self._bucket_list = _buckets(manager.max_requests)
         self.steps_run = 0
         self.graph_replays = 0
@@ -119,8 +120,11 @@ class ModelRunner:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
+        from ..csrc import build as _build
+        before = _build.LAUNCHES
         with torch.cuda.graph(graph, pool=self._graph_pool):
             logits = self.model.forward(batch, self.storage)
+        self.graph_kernel_launches[bucket] = _build.LAUNCHES - before
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
         self._graphs[bucket] = (graph, logits)
