@@ -1,0 +1,448 @@
+// Paged attention on tensor cores for bfloat16: decode (split over the keys) and prompt
+// portions with one kernel.
+//
+// Work item = (block of 16 query rows, kv head, split of the keys).  A query row is a
+// (new token, query head of the kv head's group) pair of one entry of the step, rows
+// ordered token-major, so the 16 rows of a block share the kv head's keys and values:
+// they are read once per group, not once per query head as in the reference's decode
+// kernel (litelang/kernel/develop_flash_attn/flash_decoding.py:7-114).  For a decoded
+// token the block holds the group's heads (the rest of the 16 rows is padding); for a
+// portion of a prompt it holds consecutive tokens' heads with a causal limit per row.
+//
+// The four warps of a CTA take the 16-key tiles of the work item's key range in turn.
+// Each warp keeps its own running maximum, sum and accumulator (online softmax,
+// float32) and the warps are merged through shared memory at the end.  With more than
+// one split the CTA's result goes to scratch memory and the CTA that arrives last
+// (a counter per row block and kv head) merges the splits; nothing spins.
+//
+// Data path: keys and values go from global memory straight into the registers that
+// mma.sync.m16n8k16 wants, in 16-byte loads.  That works because a dot product does
+// not care about the order of its terms: the contraction index of an MMA step is
+// mapped onto head dimensions (for Q K^T) so that each thread's four B values are 8
+// contiguous bytes... concretely thread (g = lane / 4, c = lane % 4) loads dims
+// [32 s + 8 c, 32 s + 8 c + 8) of key g of the tile and uses them for MMA steps 2 s
+// and 2 s + 1; Q is loaded with the same mapping.  For P V each thread loads, for its
+// four keys (2c, 2c+1, 2c+8, 2c+9), dims [64 h + 8 g, 64 h + 8 g + 8) and pairs the
+// values of two keys with a byte permute; output column n of MMA tile (h, j) is then
+// head dimension 64 h + 8 n + j.
+//
+// Takes head sizes 64 and 128, page sizes that are multiples of 16, any group size and
+// any number of heads.  Other shapes, and float32, go to the generic kernel.
+#include "common.cuh"
+
+#define AM_THREADS 128
+#define AM_WARPS 4
+#define AM_ROWS 16
+#define AM_TILE 16
+
+struct AttnMmaParams {
+  const bf16* q;
+  long q_stride;
+  bf16* out;
+  long out_stride;
+  const bf16* k_cache;
+  const bf16* v_cache;
+  const int* block_table;
+  int bt_stride;
+  const int* cu_q;
+  const int* ctx_len;
+  const int* req_slot;
+  int n_entries;
+  int nh, nkv, group;
+  int page_size, num_pages;
+  int window;
+  float scale_log2;  // softmax scale times log2(e)
+  int nsplit;
+  float* scratch_o;   // [row blocks * nkv * nsplit][16][HD]
+  float* scratch_ml;  // [row blocks * nkv * nsplit][16][2]
+  int* counters;      // [row blocks * nkv], zero before and after every launch
+  int* status;
+};
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                               unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+__device__ __forceinline__ uint4 ldg16(const bf16* p) { return *reinterpret_cast<const uint4*>(p); }
+
+template <int HD>
+__global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParams p) {
+  constexpr int KS = HD / 32;  // 16-byte key loads per thread and key row
+  constexpr int VS = HD / 64;  // 16-byte value loads per thread and key row
+  constexpr int NT = HD / 8;   // MMA column tiles of the output
+  __shared__ float sm_o[AM_WARPS][AM_ROWS][HD + 4];
+  __shared__ float sm_m[AM_WARPS][AM_ROWS];
+  __shared__ float sm_l[AM_WARPS][AM_ROWS];
+  __shared__ int sm_last;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const int kvh = blockIdx.y, split = blockIdx.z;
+
+  // ---- which entry does this row block belong to ----
+  int e = 0, base = 0, ql = 0;
+  for (; e < p.n_entries; ++e) {
+    ql = p.cu_q[e + 1] - p.cu_q[e];
+    const int nb = (ql * p.group + AM_ROWS - 1) / AM_ROWS;
+    if ((int)blockIdx.x < base + nb) break;
+    base += nb;
+  }
+  if (e >= p.n_entries) return;
+  const int r0 = ((int)blockIdx.x - base) * AM_ROWS;
+  const int tok0 = p.cu_q[e];
+  const int slot = p.req_slot[e];
+  const int total_rows = ql * p.group;
+
+  // rows of this thread: g and g + 8
+  int tokr[2], headr[2];
+  bool validr[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = r0 + g + 8 * i;
+    validr[i] = r < total_rows;
+    const int rr = validr[i] ? r : r0;
+    tokr[i] = rr / p.group;
+    headr[i] = kvh * p.group + (rr - tokr[i] * p.group);
+  }
+  if (slot < 0) {  // padding entry of a captured step: zeros, no reads, counters untouched
+    if (split == 0 && warp == 0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        if (validr[i]) {
+          bf16* o = p.out + (size_t)(tok0 + tokr[i]) * p.out_stride + (size_t)headr[i] * HD;
+          for (int d = c; d < HD; d += 4) o[d] = __float2bfloat16_rn(0.f);
+        }
+    }
+    return;
+  }
+  const int ctx = p.ctx_len[e];
+  int posr[2], lor[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    posr[i] = ctx + tokr[i];
+    lor[i] = p.window > 0 ? max(0, posr[i] - p.window + 1) : 0;
+  }
+  // key range of the whole block: from the first row's lower limit to the last valid row's position
+  const int first_tok = r0 / p.group;
+  const int last_row = min(total_rows, r0 + AM_ROWS) - 1;
+  const int last_tok = last_row / p.group;
+  const int j_lo = p.window > 0 ? max(0, ctx + first_tok - p.window + 1) : 0;
+  const int j_hi = ctx + last_tok;
+  const int lo_max = p.window > 0 ? max(0, ctx + last_tok - p.window + 1) : 0;  // largest lower limit of a row
+  const int p_min = ctx + first_tok;                                            // smallest position of a row
+  const int t_first = j_lo / AM_TILE, t_last = j_hi / AM_TILE;
+  const int ntiles = t_last - t_first + 1;
+  const int tps = (ntiles + p.nsplit - 1) / p.nsplit;
+  const int t_begin = t_first + split * tps;
+  const int t_end = min(t_last + 1, t_begin + tps);
+
+  // ---- Q fragments ----
+  uint4 qa[KS], qb[KS];
+  {
+    const bf16* qra = p.q + (size_t)(tok0 + tokr[0]) * p.q_stride + (size_t)headr[0] * HD + 8 * c;
+    const bf16* qrb = p.q + (size_t)(tok0 + tokr[1]) * p.q_stride + (size_t)headr[1] * HD + 8 * c;
+#pragma unroll
+    for (int s = 0; s < KS; ++s) {
+      qa[s] = validr[0] ? ldg16(qra + 32 * s) : make_uint4(0, 0, 0, 0);
+      qb[s] = validr[1] ? ldg16(qrb + 32 * s) : make_uint4(0, 0, 0, 0);
+    }
+  }
+
+  float o_acc[NT][4];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) o_acc[t][0] = o_acc[t][1] = o_acc[t][2] = o_acc[t][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  const int* bt = p.block_table + (size_t)slot * p.bt_stride;
+  uint4 kk[2][KS], vv[VS][4];
+
+  auto tile_base = [&](int t) -> long {  // element offset of key 0 of tile t for this kv head, or -1
+    const int key0 = t * AM_TILE;
+    const int page = bt[key0 / p.page_size];
+    if (page < 0 || page >= p.num_pages) {
+      if (lane == 0) set_status(p.status, LL_ERR_PAGE_RANGE);
+      return -1;
+    }
+    return (((long)page * p.nkv + kvh) * p.page_size + (key0 % p.page_size)) * HD;
+  };
+  auto load_k = [&](long tb) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int s = 0; s < KS; ++s) kk[u][s] = ldg16(p.k_cache + tb + (long)(8 * u + g) * HD + 32 * s + 8 * c);
+  };
+  auto load_v = [&](long tb) {
+#pragma unroll
+    for (int h = 0; h < VS; ++h) {
+      vv[h][0] = ldg16(p.v_cache + tb + (long)(2 * c) * HD + 64 * h + 8 * g);
+      vv[h][1] = ldg16(p.v_cache + tb + (long)(2 * c + 1) * HD + 64 * h + 8 * g);
+      vv[h][2] = ldg16(p.v_cache + tb + (long)(2 * c + 8) * HD + 64 * h + 8 * g);
+      vv[h][3] = ldg16(p.v_cache + tb + (long)(2 * c + 9) * HD + 64 * h + 8 * g);
+    }
+  };
+
+  int t = t_begin + warp;
+  long tb = (t < t_end) ? tile_base(t) : -1;
+  if (t < t_end && tb >= 0) {
+    load_k(tb);
+    load_v(tb);
+  }
+  for (; t < t_end; t += AM_WARPS) {
+    const int t_next = t + AM_WARPS;
+    const long tb_next = (t_next < t_end) ? tile_base(t_next) : -1;
+    if (tb < 0) {  // a page that is not there: nothing of this tile counts
+      tb = tb_next;
+      if (tb >= 0) {
+        load_k(tb);
+        load_v(tb);
+      }
+      continue;
+    }
+    // ---- S = Q K^T ----
+    float s_acc[2][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      s_acc[u][0] = s_acc[u][1] = s_acc[u][2] = s_acc[u][3] = 0.f;
+#pragma unroll
+      for (int s = 0; s < KS; ++s) {
+        mma_bf16_16816(s_acc[u], qa[s].x, qb[s].x, qa[s].y, qb[s].y, kk[u][s].x, kk[u][s].y);
+        mma_bf16_16816(s_acc[u], qa[s].z, qb[s].z, qa[s].w, qb[s].w, kk[u][s].z, kk[u][s].w);
+      }
+    }
+    if (tb_next >= 0) load_k(tb_next);  // the key registers are free again: fetch the next tile's keys
+    // ---- scale, mask, online softmax ----
+    const int key0 = t * AM_TILE;
+    const bool boundary = (key0 + AM_TILE - 1 > p_min) || (key0 < lo_max);
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const int i = x >> 1;  // 0: row g, 1: row g + 8
+        float v = s_acc[u][x] * p.scale_log2;
+        if (boundary) {
+          const int j = key0 + 8 * u + 2 * c + (x & 1);
+          if (j > posr[i] || j < lor[i]) v = -INFINITY;  // padding rows act as copies of the first row
+        }
+        s_acc[u][x] = v;
+        tmax[i] = fmaxf(tmax[i], v);
+      }
+    float alpha[2], msafe[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
+      tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
+      const float m_new = fmaxf(m_run[i], tmax[i]);
+      msafe[i] = (m_new == -INFINITY) ? 0.f : m_new;
+      alpha[i] = fast_exp2(m_run[i] - msafe[i]);
+      m_run[i] = m_new;
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const int i = x >> 1;
+        const float pv = fast_exp2(s_acc[u][x] - msafe[i]);
+        s_acc[u][x] = pv;
+        psum[i] += pv;
+      }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * alpha[i] + psum[i];
+    const unsigned pa0 = pack_bf16(s_acc[0][0], s_acc[0][1]);
+    const unsigned pa1 = pack_bf16(s_acc[0][2], s_acc[0][3]);
+    const unsigned pa2 = pack_bf16(s_acc[1][0], s_acc[1][1]);
+    const unsigned pa3 = pack_bf16(s_acc[1][2], s_acc[1][3]);
+    // ---- O = O * alpha + P V ----
+#pragma unroll
+    for (int h = 0; h < VS; ++h) {
+      const unsigned* w0 = reinterpret_cast<const unsigned*>(&vv[h][0]);
+      const unsigned* w1 = reinterpret_cast<const unsigned*>(&vv[h][1]);
+      const unsigned* w2 = reinterpret_cast<const unsigned*>(&vv[h][2]);
+      const unsigned* w3 = reinterpret_cast<const unsigned*>(&vv[h][3]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int T = h * 8 + j;
+        const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;
+        const unsigned b0 = __byte_perm(w0[j >> 1], w1[j >> 1], sel);
+        const unsigned b1 = __byte_perm(w2[j >> 1], w3[j >> 1], sel);
+        o_acc[T][0] *= alpha[0];
+        o_acc[T][1] *= alpha[0];
+        o_acc[T][2] *= alpha[1];
+        o_acc[T][3] *= alpha[1];
+        mma_bf16_16816(o_acc[T], pa0, pa1, pa2, pa3, b0, b1);
+      }
+    }
+    if (tb_next >= 0) load_v(tb_next);
+    tb = tb_next;
+  }
+
+  // ---- merge the four warps ----
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+  }
+  if (c == 0) {
+    sm_m[warp][g] = m_run[0];
+    sm_m[warp][g + 8] = m_run[1];
+    sm_l[warp][g] = l_run[0];
+    sm_l[warp][g + 8] = l_run[1];
+  }
+#pragma unroll
+  for (int T = 0; T < NT; ++T) {
+    const int h = T >> 3, j = T & 7;
+    const int d0 = 64 * h + 16 * c + j, d1 = d0 + 8;
+    sm_o[warp][g][d0] = o_acc[T][0];
+    sm_o[warp][g][d1] = o_acc[T][1];
+    sm_o[warp][g + 8][d0] = o_acc[T][2];
+    sm_o[warp][g + 8][d1] = o_acc[T][3];
+  }
+  __syncthreads();
+  // thread -> (row, HD/8 contiguous dims)
+  constexpr int DPT = HD / 8;
+  const int row = tid >> 3, dbase = (tid & 7) * DPT;
+  float M = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < AM_WARPS; ++w) M = fmaxf(M, sm_m[w][row]);
+  const float Ms = (M == -INFINITY) ? 0.f : M;
+  float L = 0.f, wgt[AM_WARPS];
+#pragma unroll
+  for (int w = 0; w < AM_WARPS; ++w) {
+    wgt[w] = fast_exp2(sm_m[w][row] - Ms);
+    L += sm_l[w][row] * wgt[w];
+  }
+  float acc[DPT];
+#pragma unroll
+  for (int d = 0; d < DPT; ++d) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < AM_WARPS; ++w) a += sm_o[w][row][dbase + d] * wgt[w];
+    acc[d] = a;
+  }
+  const int r = r0 + row;
+  const bool rvalid = r < total_rows;
+  const int rtok = rvalid ? r / p.group : 0;
+  const int rhead = kvh * p.group + (rvalid ? r - rtok * p.group : 0);
+  bf16* orow = p.out + (size_t)(tok0 + rtok) * p.out_stride + (size_t)rhead * HD + dbase;
+
+  if (p.nsplit == 1) {
+    if (rvalid) {
+      const float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+      for (int d = 0; d < DPT; d += 2)
+        *reinterpret_cast<unsigned*>(orow + d) = pack_bf16(acc[d] * inv, acc[d + 1] * inv);
+    }
+    return;
+  }
+  // ---- several splits: park the partial result, the last CTA to arrive merges ----
+  const size_t item = ((size_t)blockIdx.x * p.nkv + kvh);
+  float* so = p.scratch_o + ((item * p.nsplit + split) * AM_ROWS + row) * HD + dbase;
+#pragma unroll
+  for (int d = 0; d < DPT; ++d) so[d] = acc[d];
+  if ((tid & 7) == 0) {
+    float* sml = p.scratch_ml + ((item * p.nsplit + split) * AM_ROWS + row) * 2;
+    sml[0] = M;
+    sml[1] = L;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int arrived = atomicAdd(p.counters + item, 1);
+    sm_last = (arrived == p.nsplit - 1);
+  }
+  __syncthreads();
+  if (!sm_last) return;
+  __threadfence();
+  float Mg = -INFINITY;
+  for (int s = 0; s < p.nsplit; ++s)
+    Mg = fmaxf(Mg, __ldcg(p.scratch_ml + ((item * p.nsplit + s) * AM_ROWS + row) * 2));
+  const float Mgs = (Mg == -INFINITY) ? 0.f : Mg;
+  float Lg = 0.f;
+#pragma unroll
+  for (int d = 0; d < DPT; ++d) acc[d] = 0.f;
+  for (int s = 0; s < p.nsplit; ++s) {
+    const float* sml = p.scratch_ml + ((item * p.nsplit + s) * AM_ROWS + row) * 2;
+    const float ws = fast_exp2(__ldcg(sml) - Mgs);
+    Lg += __ldcg(sml + 1) * ws;
+    const float* po = p.scratch_o + ((item * p.nsplit + s) * AM_ROWS + row) * HD + dbase;
+#pragma unroll
+    for (int d = 0; d < DPT; ++d) acc[d] += __ldcg(po + d) * ws;
+  }
+  if (rvalid) {
+    const float inv = Lg > 0.f ? 1.0f / Lg : 0.f;
+#pragma unroll
+    for (int d = 0; d < DPT; d += 2)
+      *reinterpret_cast<unsigned*>(orow + d) = pack_bf16(acc[d] * inv, acc[d + 1] * inv);
+  }
+  if (tid == 0) p.counters[item] = 0;  // ready for the next launch
+}
+
+// Sizes of the scratch memory for a launch with `row_blocks` row blocks.
+extern "C" long ll_attn_mma_scratch_floats(int row_blocks, int nkv, int nsplit, int hd) {
+  return (long)row_blocks * nkv * nsplit * AM_ROWS * (hd + 2);
+}
+
+// q: query rows, head h of token t at q + t*q_stride + h*hd (bfloat16); out likewise.
+// cu_q / ctx_len / req_slot describe the entries; row_blocks = sum over entries of
+// ceil(q_len * group / 16), counted by the caller.  scratch: float32, at least
+// ll_attn_mma_scratch_floats() elements (unused when nsplit == 1); counters: int32
+// [row_blocks * nkv], zero at the first launch (the kernel leaves them zero).
+extern "C" int ll_attn_mma(void* out, long out_stride, const void* q, long q_stride, const void* k_cache,
+                           const void* v_cache, const int* block_table, int bt_stride, const int* cu_q,
+                           const int* ctx_len, const int* req_slot, int n_entries, int row_blocks, int nh, int nkv,
+                           int hd, int page_size, int num_pages, int window, float scale, int nsplit, float* scratch,
+                           int* counters, int* status, cudaStream_t stream) {
+  if (row_blocks <= 0 || n_entries <= 0) return 0;
+  if ((hd != 64 && hd != 128) || page_size % AM_TILE != 0 || nkv <= 0 || nh % nkv != 0 || nsplit < 1 ||
+      nsplit > 65535 || nkv > 65535)
+    return (int)cudaErrorInvalidValue;
+  if ((q_stride % 8) != 0 || (out_stride % 2) != 0) return (int)cudaErrorInvalidValue;
+  AttnMmaParams p;
+  p.q = (const bf16*)q;
+  p.q_stride = q_stride;
+  p.out = (bf16*)out;
+  p.out_stride = out_stride;
+  p.k_cache = (const bf16*)k_cache;
+  p.v_cache = (const bf16*)v_cache;
+  p.block_table = block_table;
+  p.bt_stride = bt_stride;
+  p.cu_q = cu_q;
+  p.ctx_len = ctx_len;
+  p.req_slot = req_slot;
+  p.n_entries = n_entries;
+  p.nh = nh;
+  p.nkv = nkv;
+  p.group = nh / nkv;
+  p.page_size = page_size;
+  p.num_pages = num_pages;
+  p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.nsplit = nsplit;
+  p.scratch_o = scratch;
+  p.scratch_ml = scratch ? scratch + (long)row_blocks * nkv * nsplit * AM_ROWS * hd : nullptr;
+  p.counters = counters;
+  p.status = status;
+  if (nsplit > 1 && (scratch == nullptr || counters == nullptr)) return (int)cudaErrorInvalidValue;
+  dim3 grid(row_blocks, nkv, nsplit);
+  if (hd == 64)
+    attn_mma_kernel<64><<<grid, AM_THREADS, 0, stream>>>(p);
+  else
+    attn_mma_kernel<128><<<grid, AM_THREADS, 0, stream>>>(p);
+  return LL_LAUNCH_RESULT();
+}

@@ -190,6 +190,55 @@ def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, q_stride: int, k
                 c_int(window or 0), c_float(scale), _ptr(status), _stream())
 
 
+def attn_mma_supported(dtype: torch.dtype, head_dim: int, page_size: int, q_stride: int) -> bool:
+    """Shapes the tensor-core attention kernel takes; everything else goes to the generic kernel."""
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 16 == 0 and q_stride % 8 == 0
+
+
+def attn_mma_scratch_floats(row_blocks: int, num_kv_heads: int, nsplit: int, head_dim: int) -> int:
+    return row_blocks * num_kv_heads * nsplit * 16 * (head_dim + 2)
+
+
+def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+             block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
+             num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+             window: Optional[int], scale: float, nsplit: int, scratch: Optional[torch.Tensor],
+             counters: Optional[torch.Tensor], status: Optional[torch.Tensor]) -> None:
+    """Tensor-core paged attention (bfloat16) of the step's entries: decode and prompt portions.
+
+    ``row_blocks`` is the sum over entries of ceil(q_len * group / 16).  With ``nsplit`` > 1 the
+    keys of every row block are split over that many CTAs, which park partial results in
+    ``scratch`` (float32, ``attn_mma_scratch_floats`` elements); ``counters`` (int32
+    [row_blocks * num_kv_heads]) must be zero and are left zero.
+    """
+    _need_cuda(out, q, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot, scratch, counters)
+    for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot"),
+                  (counters, "counters")):
+        _i32(t, nm)
+    _f32(scratch, "scratch")
+    _need(attn_mma_supported(q.dtype, head_dim, page_size, q_stride),
+          f"attn_mma takes bfloat16, head_dim 64 or 128 and pages of a multiple of 16 tokens, "
+          f"not {q.dtype}, {head_dim}, {page_size}")
+    _need(out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16,
+          "attn_mma: dtypes differ")
+    _need(out.stride(1) == 1 and out.shape[1] == num_heads * head_dim and out.stride(0) % 2 == 0, "attn_mma: out")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache plane must be contiguous")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache plane shape")
+    _need(cu_q.numel() >= num_entries + 1 and ctx_len.numel() >= num_entries and req_slot.numel() >= num_entries,
+          "attn_mma: entry arrays too short")
+    if nsplit > 1:
+        _need(scratch is not None and counters is not None, "attn_mma: splits need scratch and counters")
+        _need(scratch.numel() >= attn_mma_scratch_floats(row_blocks, num_kv_heads, nsplit, head_dim),
+              "attn_mma: scratch too small")
+        _need(counters.numel() >= row_blocks * num_kv_heads, "attn_mma: counters too small")
+    load_library("attn_mma").call(
+        "ll_attn_mma", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), _ptr(k_cache), _ptr(v_cache),
+        _ptr(block_table), c_int(block_table.stride(0)), _ptr(cu_q), _ptr(ctx_len), _ptr(req_slot),
+        c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), c_int(nsplit), _ptr(scratch),
+        _ptr(counters), _ptr(status), _stream())
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
            uniform: Optional[torch.Tensor] = None, rows: Optional[int] = None) -> None:
     """Greedy (temperature None or <= 0) or temperature sampling of each row of float32 logits."""

@@ -105,8 +105,50 @@ class GQAttention(Mixer):
         self.attend(attn, qkv, step, cache)
         return ops.linear(attn, self.w_o)
 
+    # scratch memory of the split kernel, shared by all layers (they run one after the other)
+    _workspaces: Dict[tuple, tuple] = {}
+    SM_COUNT = 148
+
+    @classmethod
+    def _workspace(cls, key, floats: int, counters: int, device):
+        ws = cls._workspaces.get(key)
+        if ws is None or ws[0].numel() < floats or ws[1].numel() < counters:
+            ws = (torch.empty(max(floats, 1), dtype=torch.float32, device=device),
+                  torch.zeros(max(counters, 1), dtype=torch.int32, device=device))
+            cls._workspaces[key] = ws
+        return ws
+
+    def _plan_mma(self, step, page_size):
+        """Row blocks, splits and scratch of the tensor-core kernel for this step (once per step)."""
+        key = ("attn_mma", self.num_heads, self.num_kv_heads, self.head_dim, self.window)
+        plan = step.scratch.get(key)
+        if plan is not None:
+            return plan
+        group = self.num_heads // self.num_kv_heads
+        blocks = sum((len(e.tokens) * group + 15) // 16 for e in step.entries)
+        blocks += (step.num_entries - len(step.entries)) * ((group + 15) // 16)     # padding entries
+        ctas = blocks * self.num_kv_heads
+        max_tiles = (step.max_kv_len + 15) // 16
+        nsplit = max(1, min((2 * self.SM_COUNT + ctas - 1) // ctas, max(1, max_tiles // 4)))
+        scratch = counters = None
+        if nsplit > 1:
+            # a captured step keeps its own buffers alive for as long as its graph exists
+            wkey = (key, blocks, nsplit) if getattr(step, "captured", False) else (key, "eager")
+            scratch, counters = self._workspace(
+                wkey, ops.attn_mma_scratch_floats(blocks, self.num_kv_heads, nsplit, self.head_dim),
+                blocks * self.num_kv_heads, step.token_ids.device)
+        plan = (blocks, nsplit, scratch, counters)
+        step.scratch[key] = plan
+        return plan
+
     def attend(self, out, qkv, step, cache) -> None:
         """Attention of the step's tokens over the cache plane; picks the kernel by shape."""
+        if ops.attn_mma_supported(qkv.dtype, self.head_dim, cache.page_size, qkv.stride(0)):
+            blocks, nsplit, scratch, counters = self._plan_mma(step, cache.page_size)
+            ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q, step.ctx_len,
+                         step.req_slot, step.num_entries, blocks, self.num_heads, self.num_kv_heads, self.head_dim,
+                         cache.page_size, self.window, self.scale, nsplit, scratch, counters, step.status)
+            return
         ops.paged_attention_generic(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.token_req,
                                     step.req_slot, step.positions, qkv.shape[0], self.num_heads, self.num_kv_heads,
                                     self.head_dim, cache.page_size, self.window, self.scale, step.status)

@@ -218,6 +218,94 @@ def test_generic_attention_finds_one_far_key(dtype, where):
     assert (mean_v > 4.5) == (where != "window_out")          # the case does what it is meant to do
 
 
+MMA_SHAPES = [
+    # nh, nkv, hd, page, lens, q_lens, window, nsplit
+    (12, 2, 128, 16, [700, 33, 1], [1, 1, 1], None, 1),          # decode, group 6
+    (12, 2, 128, 16, [700, 33, 1], [1, 1, 1], None, 7),          # the same, keys split over CTAs
+    (8, 2, 64, 16, [130, 64, 65, 17], [130, 1, 20, 17], None, 1),  # whole prompts and portions
+    (8, 2, 64, 32, [300, 90], [37, 90], None, 3),                # portions with splits, page 32
+    (3, 1, 128, 64, [257], [100], None, 2),                      # group 3, page 64
+    (40, 2, 64, 16, [99, 50], [2, 1], None, 4),                  # group 20: a token's heads span row blocks
+    (4, 4, 128, 16, [200, 77], [5, 1], 50, 2),                   # window
+    (8, 2, 64, 16, [160], [160], 33, 1),                         # window inside a whole prompt
+]
+
+
+def _run_mma(c, nh, nkv, hd, ps, window, nsplit):
+    from lite_lang_b200 import ops
+    d = dev()
+    lens, q_lens = c["lens"], c["q_lens"]
+    group = nh // nkv
+    cu = [0]
+    for ql in q_lens:
+        cu.append(cu[-1] + ql)
+    cu_q = torch.tensor(cu, dtype=torch.int32, device=d)
+    ctx = torch.tensor([l - ql for l, ql in zip(lens, q_lens)], dtype=torch.int32, device=d)
+    blocks = sum((ql * group + 15) // 16 for ql in q_lens)
+    scratch = counters = None
+    if nsplit > 1:
+        scratch = torch.full((ops.attn_mma_scratch_floats(blocks, nkv, nsplit, hd),), float("nan"), device=d)
+        counters = torch.zeros(blocks * nkv, dtype=torch.int32, device=d)
+    out = torch.full_like(c["q"], 3.0)
+    status = torch.zeros(1, dtype=torch.int32, device=d)
+    for _ in range(2):          # twice: the counters must come back to zero
+        ops.attn_mma(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], cu_q, ctx, c["req_slot"], len(lens),
+                     blocks, nh, nkv, hd, ps, window, hd ** -0.5, nsplit, scratch, counters, status)
+    assert status.item() == 0
+    if counters is not None:
+        assert int(counters.abs().sum()) == 0
+    return out
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,lens,q_lens,window,nsplit", MMA_SHAPES)
+def test_attn_mma(nh, nkv, hd, ps, lens, q_lens, window, nsplit):
+    c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, lens, q_lens, window, seed=15)
+    out = _run_mma(c, nh, nkv, hd, ps, window, nsplit)
+    assert_close(out, c["ref"], torch.bfloat16, "attn_mma")
+
+
+@pytest.mark.parametrize("nsplit", [1, 5])
+@pytest.mark.parametrize("where", ["first", "page_edge", "last_of_page", "window_in", "window_out"])
+def test_attn_mma_finds_one_far_key(where, nsplit):
+    nh, nkv, hd, ps, L, window = 12, 2, 128, 16, 1000, None
+    if where == "first":
+        peak = lambda l: 0
+    elif where == "page_edge":
+        peak = lambda l: 16 * 31
+    elif where == "last_of_page":
+        peak = lambda l: 16 * 31 + 15
+    else:
+        window = 300
+        peak = (lambda l: l - 300) if where == "window_in" else (lambda l: l - 301)
+    c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, [L], [1], window, seed=16, peak=peak)
+    out = _run_mma(c, nh, nkv, hd, ps, window, nsplit)
+    assert_close(out, c["ref"], torch.bfloat16, where)
+    assert (float(c["ref"].mean()) > 4.5) == (where != "window_out")
+
+
+def test_attn_mma_padding_entries_and_refusals():
+    from lite_lang_b200 import ops
+    c = _paged_case(torch.bfloat16, 8, 2, 64, 16, [50], [1], None, seed=17)
+    d = dev()
+    q = torch.cat([c["q"], c["q"], c["q"]])
+    cu_q = torch.tensor([0, 1, 2, 3], dtype=torch.int32, device=d)
+    ctx = torch.tensor([49, 0, 0], dtype=torch.int32, device=d)
+    req_slot = torch.tensor([int(c["req_slot"][0]), -1, -1], dtype=torch.int32, device=d)
+    out = torch.full_like(q, 9.0)
+    scratch = torch.zeros(ops.attn_mma_scratch_floats(3, 2, 4, 64), device=d)
+    counters = torch.zeros(6, dtype=torch.int32, device=d)
+    ops.attn_mma(out, q, q.stride(0), c["kc"], c["vc"], c["bt"], cu_q, ctx, req_slot, 3, 3, 8, 2, 64, 16, None,
+                 64 ** -0.5, 4, scratch, counters, None)
+    assert_close(out[:1], c["ref"], torch.bfloat16)
+    assert float(out[1:].float().abs().max()) == 0.0 and int(counters.abs().sum()) == 0
+    assert not ops.attn_mma_supported(torch.float32, 64, 16, 512)
+    assert not ops.attn_mma_supported(torch.bfloat16, 96, 16, 512)
+    assert not ops.attn_mma_supported(torch.bfloat16, 64, 8, 512)
+    with pytest.raises(ValueError, match="attn_mma takes"):
+        ops.attn_mma(out, q, q.stride(0), c["kc"], c["vc"], c["bt"], cu_q, ctx, req_slot, 3, 3, 8, 2, 96, 16, None,
+                     1.0, 1, None, None, None)
+
+
 def test_padding_entries_write_zeros_and_read_nothing():
     from lite_lang_b200 import ops
     c = _paged_case(torch.float32, 4, 2, 32, 8, [20], [1], None, seed=8)
