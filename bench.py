@@ -249,10 +249,19 @@ def run_ours(args):
     layers_full = QWEN2_1P5B["num_hidden_layers"]
     layers = args.layers or layers_full
     batch = args.batch
-    engine = build_engine(layers, max(64, batch))
+    engine = build_engine(layers, batch if args.only else max(64, batch))
     cfg = engine.model_config
     weight_bytes = engine.model.weight_bytes_per_step()
     kvb = kv_bytes_per_token(engine)
+    if args.only == "decode":
+        ms, ctx = device_decode(engine, batch, args.steps, args.warmup)
+        print(json.dumps({"only": "decode", "batch": batch, "layers": layers, "ms_per_step": round(ms, 4),
+                          "mean_context": ctx}))
+        return 0
+    if args.only == "prefill":
+        ms = prefill_once(engine, repeats=max(1, args.steps))
+        print(json.dumps({"only": "prefill", "layers": layers, "tokens": PROMPT_LEN, "ms": round(ms, 3)}))
+        return 0
 
     points = {}
     for b in (1, 64):
@@ -268,7 +277,7 @@ def run_ours(args):
     ms, ctx = device_decode(engine, batch, args.steps, args.warmup)
     clk = clocks.stop()
     bucket = engine.runner._bucket(batch)
-    per_step_kernels = engine.runner.graph_kernel_launches.get(bucket, 0) + 1        # + the sampling kernel
+    per_step_kernels = engine.runner.graph_kernel_launches.get(bucket, 0) + 2        # + the two sampling kernels
     value = batch / ms * 1e3
     step_bytes = weight_bytes + batch * ctx * kvb
     achieved = step_bytes / (ms * 1e-3) / 1e9
@@ -326,6 +335,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (reported in config)")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+                    help="a small case for profilers: only the decode steps or only the prefill; prints a short line")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not built (this engine has no multi-GPU path)")

@@ -369,20 +369,51 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
   __syncthreads();
   if (!sm_last) return;
   __threadfence();
+  // maxima of all splits first (independent loads), then the weighted sum
   float Mg = -INFINITY;
-  for (int s = 0; s < p.nsplit; ++s)
-    Mg = fmaxf(Mg, __ldcg(p.scratch_ml + ((item * p.nsplit + s) * AM_ROWS + row) * 2));
+  {
+    const float* mlbase = p.scratch_ml + (item * p.nsplit * AM_ROWS + row) * 2;
+    int s = 0;
+    for (; s + 4 <= p.nsplit; s += 4) {
+      const float m0 = __ldcg(mlbase + (size_t)(s + 0) * AM_ROWS * 2);
+      const float m1 = __ldcg(mlbase + (size_t)(s + 1) * AM_ROWS * 2);
+      const float m2 = __ldcg(mlbase + (size_t)(s + 2) * AM_ROWS * 2);
+      const float m3 = __ldcg(mlbase + (size_t)(s + 3) * AM_ROWS * 2);
+      Mg = fmaxf(fmaxf(Mg, fmaxf(m0, m1)), fmaxf(m2, m3));
+    }
+    for (; s < p.nsplit; ++s) Mg = fmaxf(Mg, __ldcg(mlbase + (size_t)s * AM_ROWS * 2));
+  }
   const float Mgs = (Mg == -INFINITY) ? 0.f : Mg;
   float Lg = 0.f;
 #pragma unroll
   for (int d = 0; d < DPT; ++d) acc[d] = 0.f;
-  for (int s = 0; s < p.nsplit; ++s) {
-    const float* sml = p.scratch_ml + ((item * p.nsplit + s) * AM_ROWS + row) * 2;
-    const float ws = fast_exp2(__ldcg(sml) - Mgs);
-    Lg += __ldcg(sml + 1) * ws;
-    const float* po = p.scratch_o + ((item * p.nsplit + s) * AM_ROWS + row) * HD + dbase;
+  for (int s0 = 0; s0 < p.nsplit; s0 += 2) {
+    float v[2][DPT], ms[2], ls[2];
 #pragma unroll
-    for (int d = 0; d < DPT; ++d) acc[d] += __ldcg(po + d) * ws;
+    for (int k = 0; k < 2; ++k) {
+      const int s = min(s0 + k, p.nsplit - 1);
+      const float* sml = p.scratch_ml + ((item * p.nsplit + s) * AM_ROWS + row) * 2;
+      const float* po = p.scratch_o + ((item * p.nsplit + s) * AM_ROWS + row) * HD + dbase;
+      ms[k] = __ldcg(sml);
+      ls[k] = __ldcg(sml + 1);
+#pragma unroll
+      for (int d = 0; d < DPT; d += 4) {
+        const float4 x = __ldcg(reinterpret_cast<const float4*>(po + d));
+        v[k][d] = x.x;
+        v[k][d + 1] = x.y;
+        v[k][d + 2] = x.z;
+        v[k][d + 3] = x.w;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (s0 + k < p.nsplit) {
+        const float ws = fast_exp2(ms[k] - Mgs);
+        Lg += ls[k] * ws;
+#pragma unroll
+        for (int d = 0; d < DPT; ++d) acc[d] += v[k][d] * ws;
+      }
+    }
   }
   if (rvalid) {
     const float inv = Lg > 0.f ? 1.0f / Lg : 0.f;

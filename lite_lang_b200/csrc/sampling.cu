@@ -8,10 +8,7 @@
 // index whose cumulative probability, summed in index order, reaches u times
 // the total.  A row whose temperature is <= 0 is greedy.
 //
-// One block of 1024 threads per row.
 #include "common.cuh"
-
-#define SM_THREADS 1024
 
 __device__ __forceinline__ void argmax_combine(float& v, int& i, float ov, int oi) {
   if (ov > v || (ov == v && oi < i)) {
@@ -65,77 +62,155 @@ __device__ int block_argmax(const float* __restrict__ row, int vocab, float* s_v
   return r == 0x7fffffff ? 0 : r;  // a row of NaN or -inf everywhere falls back to token 0
 }
 
-__global__ void __launch_bounds__(SM_THREADS)
-sample_kernel(const float* __restrict__ logits, long row_stride, const float* __restrict__ temperature,
-              const float* __restrict__ uniform, int* __restrict__ out, int vocab) {
+// ---------------------------------------------------------------------------------------
+// Two stages, so that a few rows of a large vocabulary still fill the GPU.
+//
+// Stage 1: one block per (chunk of SM_CHUNK columns, row): the chunk's maximum m_c and
+// its first argmax, and for sampled rows s_c = sum exp((x - m_c) / T) over the chunk.
+// Stage 2: one block per row: M = max m_c (ties to the lowest chunk, hence the lowest
+// index), total = sum s_c exp((m_c - M) / T); the chunk whose cumulative share reaches
+// u * total is found, and the walk inside that chunk is done by the block (partial sums
+// per thread, then the owner thread walks its few elements), all in index order.
+// ---------------------------------------------------------------------------------------
+#define SM_CHUNK 2048
+#define SM_T1 256
+
+__global__ void __launch_bounds__(SM_T1)
+sample_stage1_kernel(const float* __restrict__ logits, long row_stride, const float* __restrict__ temperature,
+                     float* __restrict__ part, int vocab, int nchunks) {
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
-  __shared__ float s_part[SM_THREADS];
-  __shared__ int s_choice;
-  const int r = blockIdx.x;
-  const float* row = logits + (size_t)r * row_stride;
+  __shared__ float s_sum[32];
+  const int chunk = blockIdx.x, r = blockIdx.y;
+  const int c0 = chunk * SM_CHUNK, n = min(SM_CHUNK, vocab - c0);
+  const float* row = logits + (size_t)r * row_stride + c0;
   float mx;
-  const int greedy = block_argmax(row, vocab, s_val, s_idx, &mx);
+  const int arg = block_argmax(row, n, s_val, s_idx, &mx);
   const float temp = temperature ? temperature[r] : 0.f;
-  if (!(temp > 0.f)) {
-    if (threadIdx.x == 0) out[r] = greedy;
+  float sum = 0.f;
+  if (temp > 0.f) {
+    const float inv_t = 1.0f / temp;
+    float part_sum = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) part_sum += expf((row[i] - mx) * inv_t);
+    sum = block_sum(part_sum, s_sum);
+  }
+  if (threadIdx.x == 0) {
+    float* o = part + ((size_t)r * nchunks + chunk) * 3;
+    o[0] = mx;
+    o[1] = __int_as_float(c0 + arg);
+    o[2] = sum;
+  }
+}
+
+__global__ void __launch_bounds__(SM_T1)
+sample_stage2_kernel(const float* __restrict__ logits, long row_stride, const float* __restrict__ temperature,
+                     const float* __restrict__ uniform, const float* __restrict__ part, int* __restrict__ out,
+                     int vocab, int nchunks) {
+  __shared__ float s_part[SM_T1];
+  __shared__ float s_M;
+  __shared__ int s_arg, s_chunk;
+  __shared__ float s_before, s_target, s_scale;
+  const int r = blockIdx.x;
+  const float* pr = part + (size_t)r * nchunks * 3;
+  const float temp = temperature ? temperature[r] : 0.f;
+  if (threadIdx.x == 0) {
+    float M = -INFINITY;
+    int arg = 0;
+    for (int c = 0; c < nchunks; ++c)
+      if (pr[c * 3] > M) {
+        M = pr[c * 3];
+        arg = __float_as_int(pr[c * 3 + 1]);
+      }
+    s_M = M;
+    s_arg = arg;
+    s_chunk = -1;
+    if (temp > 0.f) {
+      const float inv_t = 1.0f / temp;
+      float total = 0.f;
+      for (int c = 0; c < nchunks; ++c) total += pr[c * 3 + 2] * expf((pr[c * 3] - M) * inv_t);
+      const float target = uniform[r] * total;
+      float run = 0.f;
+      for (int c = 0; c < nchunks; ++c) {
+        const float share = pr[c * 3 + 2] * expf((pr[c * 3] - M) * inv_t);
+        if (share > 0.f && run + share >= target) {
+          s_chunk = c;
+          break;
+        }
+        run += share;
+      }
+      s_before = run;
+      s_target = target;
+    }
+  }
+  __syncthreads();
+  if (!(temp > 0.f) || s_chunk < 0) {  // greedy, or rounding pushed the target past the last chunk
+    if (threadIdx.x == 0) out[r] = s_arg;
     return;
   }
-  // contiguous chunk of the vocabulary per thread, so that the CDF runs in index order
-  const int chunk = (vocab + SM_THREADS - 1) / SM_THREADS;
-  const int c0 = min(vocab, (int)threadIdx.x * chunk), c1 = min(vocab, c0 + chunk);
-  const float inv_t = 1.0f / temp;
-  float part = 0.f;
-  for (int i = c0; i < c1; ++i) part += expf((row[i] - mx) * inv_t);
-  s_part[threadIdx.x] = part;
+  const int chunk = s_chunk;
+  const int c0 = chunk * SM_CHUNK, n = min(SM_CHUNK, vocab - c0);
+  const float* row = logits + (size_t)r * row_stride + c0;
+  const float inv_t = 1.0f / temp, M = s_M;
+  constexpr int PER = SM_CHUNK / SM_T1;
+  const int i0 = threadIdx.x * PER;
+  float mine = 0.f;
+  for (int i = i0; i < min(n, i0 + PER); ++i) mine += expf((row[i] - M) * inv_t);
+  s_part[threadIdx.x] = mine;
   __syncthreads();
   if (threadIdx.x == 0) {
-    float total = 0.f;
-    for (int i = 0; i < SM_THREADS; ++i) total += s_part[i];
-    const float target = uniform[r] * total;
-    float run = 0.f;
+    float run = s_before;
     int owner = -1;
-    for (int i = 0; i < SM_THREADS; ++i) {
-      if (run + s_part[i] >= target && s_part[i] > 0.f) {
-        owner = i;
+    for (int t = 0; t < SM_T1; ++t) {
+      if (s_part[t] > 0.f && run + s_part[t] >= s_target) {
+        owner = t;
         break;
       }
-      run += s_part[i];
+      run += s_part[t];
     }
-    int choice = greedy;
+    int choice = -1;
     if (owner >= 0) {
-      const int o0 = owner * chunk, o1 = min(vocab, o0 + chunk);
-      choice = -1;
-      for (int i = o0; i < o1; ++i) {
-        const float e = expf((row[i] - mx) * inv_t);
+      for (int i = owner * PER; i < min(n, owner * PER + PER); ++i) {
+        const float e = expf((row[i] - M) * inv_t);
         run += e;
-        if (run >= target && e > 0.f) {
-          choice = i;
+        if (e > 0.f && run >= s_target) {
+          choice = c0 + i;
           break;
         }
       }
-      if (choice < 0) {  // rounding left the target just above the chunk's sum: last non-zero entry
-        for (int i = o1 - 1; i >= o0; --i)
-          if (expf((row[i] - mx) * inv_t) > 0.f) {
-            choice = i;
+      if (choice < 0)  // rounding: the last non-zero element of the owner's piece
+        for (int i = min(n, owner * PER + PER) - 1; i >= owner * PER; --i)
+          if (expf((row[i] - M) * inv_t) > 0.f) {
+            choice = c0 + i;
             break;
           }
-        if (choice < 0) choice = greedy;
-      }
     }
-    s_choice = choice;
+    if (choice < 0) {  // rounding: the last non-zero element of the chunk
+      for (int i = n - 1; i >= 0; --i)
+        if (expf((row[i] - M) * inv_t) > 0.f) {
+          choice = c0 + i;
+          break;
+        }
+    }
+    out[r] = choice >= 0 ? choice : s_arg;
   }
-  __syncthreads();
-  if (threadIdx.x == 0) out[r] = s_choice;
+}
+
+extern "C" long ll_sample_scratch_floats(int rows, int vocab) {
+  return (long)rows * ((vocab + SM_CHUNK - 1) / SM_CHUNK) * 3;
 }
 
 // logits: float32 [rows, vocab] with row stride row_stride; temperature and
-// uniform: float32 [rows] or null (all greedy); out: int32 [rows].
+// uniform: float32 [rows] or null (all greedy); out: int32 [rows]; scratch: float32,
+// ll_sample_scratch_floats(rows, vocab) elements.
 extern "C" int ll_sample(const float* logits, long row_stride, const float* temperature, const float* uniform,
-                         int* out, int rows, int vocab, cudaStream_t stream) {
+                         int* out, int rows, int vocab, float* scratch, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (vocab <= 0) return (int)cudaErrorInvalidValue;
+  if (vocab <= 0 || scratch == nullptr || rows > 65535) return (int)cudaErrorInvalidValue;
   if (temperature != nullptr && uniform == nullptr) return (int)cudaErrorInvalidValue;
-  sample_kernel<<<rows, SM_THREADS, 0, stream>>>(logits, row_stride, temperature, uniform, out, vocab);
+  const int nchunks = (vocab + SM_CHUNK - 1) / SM_CHUNK;
+  sample_stage1_kernel<<<dim3(nchunks, rows), SM_T1, 0, stream>>>(logits, row_stride, temperature, scratch, vocab,
+                                                                   nchunks);
+  sample_stage2_kernel<<<rows, SM_T1, 0, stream>>>(logits, row_stride, temperature, uniform, scratch, out, vocab,
+                                                   nchunks);
   return LL_LAUNCH_RESULT();
 }

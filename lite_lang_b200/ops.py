@@ -239,9 +239,21 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
         _ptr(counters), _ptr(status), _stream())
 
 
+_sample_scratch = {}
+
+
+def sample_scratch_floats(rows: int, vocab: int) -> int:
+    return rows * ((vocab + 2047) // 2048) * 3
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
-           uniform: Optional[torch.Tensor] = None, rows: Optional[int] = None) -> None:
-    """Greedy (temperature None or <= 0) or temperature sampling of each row of float32 logits."""
+           uniform: Optional[torch.Tensor] = None, rows: Optional[int] = None,
+           scratch: Optional[torch.Tensor] = None) -> None:
+    """Greedy (temperature None or <= 0) or temperature sampling of each row of float32 logits.
+
+    Two kernels (per-chunk partial results, then one block per row); ``scratch`` holds the partial
+    results (float32, ``sample_scratch_floats`` elements) and is taken from a per-device cache if
+    not given."""
     _need_cuda(logits, out, temperature, uniform)
     _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "logits must be float32 2-D")
     _i32(out, "out")
@@ -249,8 +261,16 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
     _f32(uniform, "uniform")
     n = logits.shape[0] if rows is None else rows
     _need(out.numel() >= n, "sample: out too small")
+    need = sample_scratch_floats(n, logits.shape[1])
+    if scratch is None:
+        scratch = _sample_scratch.get(logits.device)
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.empty(max(need, 1024), dtype=torch.float32, device=logits.device)
+            _sample_scratch[logits.device] = scratch
+    _f32(scratch, "scratch")
+    _need(scratch.numel() >= need, "sample: scratch too small")
     core().call("ll_sample", _ptr(logits), c_long(logits.stride(0)), _ptr(temperature), _ptr(uniform), _ptr(out),
-                c_int(n), c_int(logits.shape[1]), _stream())
+                c_int(n), c_int(logits.shape[1]), _ptr(scratch), _stream())
 
 
 # --------------------------------------------------------------------------

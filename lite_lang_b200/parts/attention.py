@@ -129,7 +129,7 @@ class GQAttention(Mixer):
         blocks += (step.num_entries - len(step.entries)) * ((group + 15) // 16)     # padding entries
         ctas = blocks * self.num_kv_heads
         max_tiles = (step.max_kv_len + 15) // 16
-        nsplit = max(1, min((2 * self.SM_COUNT + ctas - 1) // ctas, max(1, max_tiles // 4)))
+        nsplit = max(1, min((2 * self.SM_COUNT) // ctas, max(1, max_tiles // 4)))    # one wave of CTAs
         scratch = counters = None
         if nsplit > 1:
             # a captured step keeps its own buffers alive for as long as its graph exists
