@@ -35,6 +35,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
 LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "core": (("embedding.cu", "norm.cu", "rope.cu", "activation.cu", "sampling.cu", "attention_generic.cu"), ()),
     "attn_mma": (("attention_mma.cu",), ()),
+    "gemm_smallm": (("gemm_smallm.cu",), ()),
 }
 
 _HEADERS = ("common.cuh",)

@@ -274,15 +274,74 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
 
 
 # --------------------------------------------------------------------------
+SMALL_M = 64          # the most tokens the weight-streaming kernel takes
+
+
+def smallm_preferred(x: torch.Tensor, weight: torch.Tensor, gated: bool = False) -> bool:
+    """Where the hand-written kernel is used instead of the library product: few tokens and a
+    weight matrix small enough that the library's tile shapes leave most SMs idle (measured on
+    B200: the q|k|v and output projections; the library wins on the wide feed-forward and
+    lm_head products)."""
+    if not smallm_supported(x, weight):
+        return False
+    n, k = weight.shape
+    return x.shape[0] <= 16 and n <= 4096 and k <= 2048 and not gated
+
+
+def smallm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+            and 0 < x.shape[0] <= SMALL_M and x.shape[1] % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and weight.is_contiguous() and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False) -> torch.Tensor:
+    """out = x @ weight.T for up to 64 tokens with the weight-streaming kernel.
+
+    ``gated``: weight holds gate rows then up rows ([2 I, K]); out [M, I] = silu(gate) * up.
+    out may be bfloat16 or (not gated) float32.
+    """
+    _need_cuda(x, weight, out)
+    _need(smallm_supported(x, weight), "gemm_smallm: bfloat16, at most 64 tokens, K a multiple of 32")
+    m, k = x.shape
+    n = weight.shape[0] // 2 if gated else weight.shape[0]
+    _need(weight.shape[1] == k and (not gated or weight.shape[0] % 2 == 0), "gemm_smallm: weight shape")
+    _need(out.shape[0] == m and out.shape[1] == n and out.stride(1) == 1, "gemm_smallm: out shape")
+    _need(out.dtype in (torch.bfloat16, torch.float32) and not (gated and out.dtype != torch.bfloat16),
+          "gemm_smallm: out dtype")
+    load_library("gemm_smallm").call(
+        "ll_gemm_smallm", _ptr(out), c_long(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0), _ptr(x),
+        c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(1 if gated else 0), _stream())
+    return out
+
+
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x @ Wg.T) * (x @ Wu.T) with W = [Wg; Wu]: fused for few tokens, else product + kernel."""
+    inter = w_gate_up.shape[0] // 2
+    act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
+    if smallm_preferred(x, w_gate_up, gated=True):
+        return gemm_smallm(x, w_gate_up, act, gated=True)
+    gu = linear(x, w_gate_up)
+    silu_mul(act, gu)
+    return act
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """x [n, in] times weight [out, in] transposed: a library (cuBLAS) product.
+    """x [n, in] times weight [out, in] transposed.
 
-    float32 operands give a true float32 product (TF32 is off); bfloat16
+    For up to 64 bfloat16 tokens this is the hand-written weight-streaming kernel
+    (``gemm_smallm``).  Otherwise it is a library (cuBLAS) product, as in the
+    reference: float32 operands give a true float32 product (TF32 is off); bfloat16
     operands accumulate in float32.  ``out_dtype=torch.float32`` with bfloat16
     operands keeps the float32 accumulator as the result (the logits).
     """
     _need_cuda(x, weight)
+    if smallm_preferred(x, weight) and (out is None or out.stride(1) == 1):
+        dt = out_dtype or x.dtype
+        if out is None:
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=dt, device=x.device)
+        if out.dtype == dt:
+            return gemm_smallm(x, weight, out)
     if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise RuntimeError("TF32 is on; call ops.configure_matmul_precision() before a float32 product")
     if out_dtype is not None and out_dtype != x.dtype:

@@ -80,6 +80,14 @@ class GQAttention(Mixer):
     def cache_need(self):
         return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
 
+    def kernel_libraries(self):
+        libs = ["core"]
+        if self.w_qkv is not None and self.w_qkv.dtype == torch.bfloat16:
+            libs.append("gemm_smallm")
+            if self.head_dim in (64, 128):
+                libs.append("attn_mma")
+        return libs
+
     def prepare(self, device, dtype) -> None:
         if self.position is not None:
             self.position.prepare(device)

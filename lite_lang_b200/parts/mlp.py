@@ -43,13 +43,15 @@ class GatedMLP(FeedForward):
         self.w_gate_up = torch.cat((gate, up), dim=0).to(device).contiguous()
         self.w_down = fetch("down_proj.weight").to(dtype).to(device).contiguous()
 
+    def kernel_libraries(self):
+        bf16 = self.w_down is not None and self.w_down.dtype == torch.bfloat16
+        return ["core", "gemm_smallm"] if bf16 else ["core"]
+
     def weight_bytes(self) -> int:
         return self.w_gate_up.numel() * self.w_gate_up.element_size() + self.w_down.numel() * self.w_down.element_size()
 
     def forward(self, x, step):
-        gu = ops.linear(x, self.w_gate_up)
-        act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.silu_mul(act, gu)
+        act = ops.gated_linear(x, self.w_gate_up)
         return ops.linear(act, self.w_down)
 
 

@@ -366,6 +366,61 @@ def test_temperature_sampling_walks_the_cdf(vocab):
     assert float((freq - P.temperature_probs(row[0], 0.8)).abs().max()) < 0.03
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 48, 64), (8, 2048, 1536), (5, 1536, 8960), (13, 100, 96), (33, 331, 160),
+                                   (64, 272, 1024), (2, 16, 32)])
+def test_gemm_smallm(m, n, k):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    ref = P.linear(x.float(), w.float())
+    for dt in (torch.bfloat16, torch.float32):
+        out = torch.full((m, n), 7.0, dtype=dt, device=dev())
+        ops.gemm_smallm(x.to(dev()), w.to(dev()), out)
+        scale = float(ref.abs().max())
+        err = float((out.float().cpu() - ref).abs().max()) / scale
+        assert err <= (8e-3 if dt == torch.bfloat16 else 2e-5), (dt, err)
+    # a view with a row stride (the q part of a fused projection)
+    wide = torch.randn(m, k + 64, generator=g).to(torch.bfloat16).to(dev())
+    out = torch.empty(m, n, dtype=torch.float32, device=dev())
+    ops.gemm_smallm(wide[:, :k], w.to(dev()), out)
+    ref2 = P.linear(wide[:, :k].float().cpu(), w.float())
+    assert float((out.cpu() - ref2).abs().max()) / float(ref2.abs().max()) <= 2e-5
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 128, 64), (8, 8960, 1536), (20, 203, 96), (64, 320, 256)])
+def test_gemm_smallm_gated_equals_product_then_activation(m, inter, k):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(22)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(dev())
+    w = (2 * torch.randn(2 * inter, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(dev())
+    fused = ops.gemm_smallm(x, w, torch.empty(m, inter, dtype=torch.bfloat16, device=dev()), gated=True)
+    gu = torch.mm(x, w.t())
+    unfused = torch.empty(m, inter, dtype=torch.bfloat16, device=dev())
+    ops.silu_mul(unfused, gu)
+    ref = P.silu_and_mul(P.linear(x.float().cpu(), w[:inter].float().cpu()), P.linear(x.float().cpu(), w[inter:].float().cpu()))
+    assert_close(fused, ref, torch.bfloat16, "gated")
+    # the same roundings as the unfused path: equal up to the order of the float32 sums
+    assert float((fused.float() - unfused.float()).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
+def test_linear_picks_the_library_for_other_shapes():
+    from lite_lang_b200 import ops
+    ops.configure_matmul_precision()
+    g = torch.Generator().manual_seed(23)
+    for m, n, k, dt in [(65, 40, 64, torch.bfloat16), (4, 40, 50, torch.bfloat16), (4, 40, 64, torch.float32)]:
+        x = torch.randn(m, k, generator=g).to(dt).to(dev())
+        w = torch.randn(n, k, generator=g).to(dt).to(dev())
+        assert not ops.smallm_preferred(x, w)
+        y = ops.linear(x, w)
+        assert_close(y, P.linear(x.float().cpu(), w.float().cpu()), dt if dt == torch.bfloat16 else torch.float32)
+    x = torch.randn(3, 64, generator=g).to(torch.bfloat16).to(dev())
+    w = torch.randn(40, 64, generator=g).to(torch.bfloat16).to(dev())
+    y = ops.linear(x, w, out_dtype=torch.float32)
+    assert y.dtype == torch.float32
+    assert_close(y, P.linear(x.float().cpu(), w.float().cpu()), torch.float32, "float32 logits from bfloat16 operands")
+
+
 def test_kernels_refuse_what_they_do_not_take():
     from lite_lang_b200 import ops
     x = torch.zeros(2, 8)
