@@ -16,6 +16,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -38,7 +39,7 @@ LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "gemm_smallm": (("gemm_smallm.cu",), ()),
 }
 
-_HEADERS = ("common.cuh",)
+_INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
 LAUNCHES = 0   # launcher calls so far (each launches one kernel unless its docstring says otherwise)
 _lock = threading.Lock()
 _loaded: Dict[str, "Library"] = {}
@@ -89,10 +90,25 @@ def _src_path(s: str) -> str:
     return s if os.path.isabs(s) else os.path.join(_HERE, s)
 
 
+def _with_includes(sources: Iterable[str]) -> List[str]:
+    """The sources and every file of this folder they include with #include "..." (recursively)."""
+    seen: List[str] = []
+    todo = [_src_path(s) for s in sources]
+    while todo:
+        path = todo.pop(0)
+        if path in seen or not os.path.isfile(path):
+            continue
+        seen.append(path)
+        with open(path, "r", encoding="utf-8") as fh:
+            for inc in _INCLUDE.findall(fh.read()):
+                todo.append(os.path.join(os.path.dirname(path), inc))
+    return seen
+
+
 def _digest(sources: Iterable[str], definitions: Iterable[str]) -> str:
     h = hashlib.sha256()
-    for s in list(sources) + [os.path.join(_HERE, x) for x in _HEADERS]:
-        with open(_src_path(s), "rb") as fh:
+    for s in _with_includes(sources):
+        with open(s, "rb") as fh:
             h.update(fh.read())
         h.update(b"\0")
     h.update(" ".join(list(definitions) + ARCH_FLAGS + NVCC_FLAGS).encode())
