@@ -37,6 +37,7 @@ LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "core": (("embedding.cu", "norm.cu", "rope.cu", "activation.cu", "sampling.cu", "attention_generic.cu"), ()),
     "attn_mma": (("attention_mma.cu",), ()),
     "gemm_smallm": (("gemm_smallm.cu",), ()),
+    "gemm_stream": (("gemm_stream.cu",), ()),
     "attn_mma_static": (("attention_mma_static.cu",), ()),
 }
 

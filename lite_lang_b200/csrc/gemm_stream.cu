@@ -1,0 +1,412 @@
+// Weight-streaming matrix product for decode: y[M, N] = x[M, K] * W[N, K]^T, bfloat16,
+// float32 accumulation, M <= 32 tokens.
+//
+// A decode step is a stream of every weight through the SMs, so this kernel is built
+// around the copy engine, not around the tensor core: persistent CTAs, each with one
+// producer warp that keeps a ring of shared-memory stages filled by TMA (tiled
+// cp.async.bulk.tensor.2d through a tensor map of W, boxes of 64 k x 16..64 rows with the
+// 128-byte swizzle, completion counted by an mbarrier per stage; no multicast), and four
+// consumer warps that feed mma.sync.m16n8k16 from the stages and hand them back through a
+// second mbarrier.  Bytes in flight are bounded by shared memory (about 100 KB a CTA, two
+// CTAs an SM), not by registers or occupancy, and the producer runs ahead over the end of a
+// work unit, so the stream does not stop while a unit's results are written.  (One bulk
+// copy per weight row was tried first: the SM's copy unit took about 35 cycles a copy
+// whatever its size, so 256-byte copies capped the kernel at 2 TB/s.)
+//
+// The weights take the M side of the MMA (16 rows a tile), the tokens the N side.  As in
+// gemm_smallm.cu the contraction index of an MMA step is mapped to 8 contiguous elements
+// per thread, so a thread's A fragment is one 16-byte read from a stage row and its B
+// fragment one 16-byte read of a token row (global memory, L1 resident).
+//
+// Three shapes of work unit:
+//   WIDE    64 output features x all of K; a stage is 64 rows x 128 k (two boxes); warp w
+//           owns rows 16 w .. 16 w + 15.  For wide products (lm_head).
+//   GATED   32 features of the SiLU-gated feed-forward; W is [2 I, K], gate rows first.
+//           Warp w's tile has 8 gate rows and, as rows 8..15, the up rows of the same 8
+//           features, so the thread that holds gate(f, token) also holds up(f, token)
+//           and writes silu(gate) * up: the [M, 2 I] intermediate never exists.
+//   NARROW  16 features x all of K; a stage is 16 rows x 256 k (four boxes) and warp w takes
+//           one box; the four partial tiles are added through shared memory.  For
+//           products with few output features (q|k|v, o, down), where units, not k, are scarce.
+//
+// Every wait on an mbarrier is bounded (about two seconds of clock); a wait that runs out
+// sets LL_ERR_WAIT_TIMEOUT in the status word and the kernel carries on to its end.
+//
+// Needs K % 256 == 0 (NARROW) or K % 128 == 0 (WIDE, GATED) and 16-byte aligned rows.
+// Rows of W beyond N are filled with zeros by TMA.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define LL_ERR_WAIT_TIMEOUT 5
+
+#define GT_CONSUMERS 4
+#define GT_THREADS ((GT_CONSUMERS + 1) * 32)
+#define GT_MODE_WIDE 0
+#define GT_MODE_GATED 1
+#define GT_MODE_NARROW 2
+
+template <int MODE> struct GtShape;
+// ROWS x KC elements a stage, made of boxes of BOX_ROWS rows x 64 k (128 bytes a row).
+template <> struct GtShape<GT_MODE_WIDE> {
+  static constexpr int ROWS = 64, KC = 128, BOX_ROWS = 64, STAGES = 6;
+};
+template <> struct GtShape<GT_MODE_GATED> {
+  static constexpr int ROWS = 64, KC = 128, BOX_ROWS = 32, STAGES = 6;
+};
+template <> struct GtShape<GT_MODE_NARROW> {
+  static constexpr int ROWS = 16, KC = 256, BOX_ROWS = 16, STAGES = 12;
+};
+
+__device__ __forceinline__ unsigned gt_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void gt_mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void gt_mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void gt_mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool gt_mbar_try(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after about two seconds, records it, and lets the caller go on.
+__device__ __forceinline__ void gt_mbar_wait(unsigned bar, unsigned parity, int* status) {
+  if (gt_mbar_try(bar, parity)) return;
+  const long long t0 = clock64();
+  while (!gt_mbar_try(bar, parity)) {
+    if (clock64() - t0 > 4000000000ll) {
+      set_status(status, LL_ERR_WAIT_TIMEOUT);
+      return;
+    }
+  }
+}
+// One TMA box: rows [y, y + box rows) x k [x, x + 64) of W into shared memory (x is a multiple of 64
+// elements, i.e. of 128 bytes, as TMA's 16-byte rule on the innermost coordinate demands).
+__device__ __forceinline__ void gt_tma_load(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ uint4 gt_lds16(unsigned addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void gt_mma(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                       unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void gt_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(GT_CONSUMERS * 32)); }
+
+template <typename OutT> __device__ __forceinline__ OutT gt_out(float v);
+template <> __device__ __forceinline__ float gt_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 gt_out<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+struct GtParams {
+  const bf16* x;
+  void* out;
+  long x_stride, out_stride;
+  int M, N, K;  // N: output features (GATED: the intermediate size; W has 2 N rows)
+  int units;    // feature units times ksplit
+  int ksplit;   // parts the k range is cut into; > 1: out is float32 [ksplit, M, N] partial sums
+  int cpp;      // k chunks (stages) per part
+  int* status;
+};
+
+template <int MODE, int MT, typename OutT>
+__global__ void __launch_bounds__(GT_THREADS)
+gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
+  using S = GtShape<MODE>;
+  constexpr int KBOXES = S::KC / 64;                 // boxes along k in a stage
+  constexpr int BOX_BYTES = S::BOX_ROWS * 128;       // one box: BOX_ROWS rows of 128 bytes, swizzled
+  constexpr int RBOXES = S::ROWS / S::BOX_ROWS;      // boxes along the rows (GATED: gate box, up box)
+  constexpr int STAGE_BYTES = S::ROWS * S::KC * 2;
+  extern __shared__ unsigned char smem_raw[];
+  // the swizzle pattern repeats every 1024 bytes: stages start on a 1024-byte boundary
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + S::STAGES * STAGE_BYTES);
+  float* red = reinterpret_cast<float*>(smem + S::STAGES * STAGE_BYTES + 2 * S::STAGES * 8);
+  const unsigned full0 = gt_smem(bars), empty0 = gt_smem(bars + S::STAGES);
+  const unsigned stage0 = gt_smem(smem);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      gt_mbar_init(full0 + 8 * s, 1);
+      gt_mbar_init(empty0 + 8 * s, GT_CONSUMERS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  const int kchunks = p.K / S::KC;
+
+  if (warp == GT_CONSUMERS) {
+    // ------------------------------ producer ------------------------------
+    // The weights do not depend on the kernel before this one, so streaming starts at once.
+    if (lane == 0) {
+      long it = 0;
+      for (int uu = blockIdx.x; uu < p.units; uu += gridDim.x) {
+        const int u = uu / p.ksplit, kp = uu - u * p.ksplit;
+        int y[RBOXES];
+        if (MODE == GT_MODE_WIDE) {
+          y[0] = u * 64;
+        } else if (MODE == GT_MODE_GATED) {
+          y[0] = u * 32;                 // gate rows of the unit's 32 features
+          y[RBOXES - 1] = p.N + u * 32;  // their up rows
+        } else {
+          y[0] = u * 16;
+        }
+        const int kc_end = min(kchunks, (kp + 1) * p.cpp);
+        for (int kc = kp * p.cpp; kc < kc_end; ++kc, ++it) {
+          const int s = (int)(it % S::STAGES);
+          const unsigned ph = (unsigned)((it / S::STAGES) & 1);
+          gt_mbar_wait(empty0 + 8 * s, ph ^ 1, p.status);
+          gt_mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+#pragma unroll
+          for (int kb = 0; kb < KBOXES; ++kb)
+#pragma unroll
+            for (int rb = 0; rb < RBOXES; ++rb)
+              gt_tma_load(stage0 + s * STAGE_BYTES + (kb * RBOXES + rb) * BOX_BYTES, &wmap, kc * S::KC + kb * 64, y[rb],
+                          full0 + 8 * s);
+        }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------ consumers ------------------------------
+  const int g = lane >> 2, c = lane & 3;
+  const bf16* xp[MT];
+#pragma unroll
+  for (int j = 0; j < MT; ++j) xp[j] = p.x + (size_t)min(8 * j + g, p.M - 1) * p.x_stride + 8 * c;
+  // the token rows are written by the kernel before this one
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // k boxes of a stage this warp works on, and where its two A rows sit inside a box
+  constexpr int MYBOXES = (MODE == GT_MODE_NARROW) ? 1 : KBOXES;
+  const int kb0 = (MODE == GT_MODE_NARROW) ? warp : 0;
+  unsigned row_off[2];  // byte offset of row g / row g + 8 of this warp's tile inside a k box
+  if (MODE == GT_MODE_WIDE) {
+    row_off[0] = (16 * warp + g) * 128;
+    row_off[1] = (16 * warp + g + 8) * 128;
+  } else if (MODE == GT_MODE_GATED) {
+    row_off[0] = (8 * warp + g) * 128;               // gate box
+    row_off[1] = BOX_BYTES + (8 * warp + g) * 128;   // up box
+  } else {
+    row_off[0] = g * 128;
+    row_off[1] = (g + 8) * 128;
+  }
+  // 16-byte chunk q of a 128-byte row r sits at chunk q ^ (r & 7); all rows used here have r & 7 == g
+  const unsigned sw = (unsigned)g;
+
+  long it = 0;
+  for (int uu = blockIdx.x; uu < p.units; uu += gridDim.x) {
+    const int u = uu / p.ksplit, kp = uu - u * p.ksplit;
+    float acc[MT][4];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const int kc_end = min(kchunks, (kp + 1) * p.cpp);
+    for (int kc = kp * p.cpp; kc < kc_end; ++kc, ++it) {
+      const int s = (int)(it % S::STAGES);
+      const unsigned ph = (unsigned)((it / S::STAGES) & 1);
+      uint4 xv[MYBOXES][2][MT];
+#pragma unroll
+      for (int b = 0; b < MYBOXES; ++b)
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int j = 0; j < MT; ++j)
+            xv[b][i][j] = *reinterpret_cast<const uint4*>(xp[j] + (size_t)kc * S::KC + (kb0 + b) * 64 + 32 * i);
+      gt_mbar_wait(full0 + 8 * s, ph, p.status);
+#pragma unroll
+      for (int b = 0; b < MYBOXES; ++b) {
+        const unsigned box = stage0 + s * STAGE_BYTES + (kb0 + b) * RBOXES * BOX_BYTES;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const unsigned chunk = ((unsigned)(4 * i + c) ^ sw) * 16;
+          const uint4 wa = gt_lds16(box + row_off[0] + chunk);
+          const uint4 wb = gt_lds16(box + row_off[1] + chunk);
+#pragma unroll
+          for (int j = 0; j < MT; ++j) {
+            gt_mma(acc[j], wa.x, wb.x, wa.y, wb.y, xv[b][i][j].x, xv[b][i][j].y);
+            gt_mma(acc[j], wa.z, wb.z, wa.w, wb.w, xv[b][i][j].z, xv[b][i][j].w);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) gt_mbar_arrive(empty0 + 8 * s);
+    }
+    // ---- the unit's results ----
+    OutT* out = reinterpret_cast<OutT*>(p.out) + (size_t)kp * p.M * p.out_stride;  // this part's [M, N] block
+    if (MODE == GT_MODE_WIDE) {
+      const int fa = u * 64 + 16 * warp + g, fb = fa + 8;
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        const int t0 = 8 * j + 2 * c, t1 = t0 + 1;
+        if (fa < p.N) {
+          if (t0 < p.M) out[(size_t)t0 * p.out_stride + fa] = gt_out<OutT>(acc[j][0]);
+          if (t1 < p.M) out[(size_t)t1 * p.out_stride + fa] = gt_out<OutT>(acc[j][1]);
+        }
+        if (fb < p.N) {
+          if (t0 < p.M) out[(size_t)t0 * p.out_stride + fb] = gt_out<OutT>(acc[j][2]);
+          if (t1 < p.M) out[(size_t)t1 * p.out_stride + fb] = gt_out<OutT>(acc[j][3]);
+        }
+      }
+    } else if (MODE == GT_MODE_GATED) {
+      const int f = u * 32 + 8 * warp + g;
+      if (f < p.N) {
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int t = 8 * j + 2 * c + h;
+            if (t < p.M) {
+              // gate and up are rounded to bfloat16 first, as the unfused path does between product and activation
+              const float gt = __bfloat162float(__float2bfloat16_rn(acc[j][h]));
+              const float up = __bfloat162float(__float2bfloat16_rn(acc[j][2 + h]));
+              out[(size_t)t * p.out_stride + f] = gt_out<OutT>(gt / (1.0f + expf(-gt)) * up);
+            }
+          }
+        }
+      }
+    } else {
+      constexpr int TOK = 8 * MT;
+      float* r = red + (size_t)warp * 16 * TOK;
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        r[g * TOK + 8 * j + 2 * c] = acc[j][0];
+        r[g * TOK + 8 * j + 2 * c + 1] = acc[j][1];
+        r[(g + 8) * TOK + 8 * j + 2 * c] = acc[j][2];
+        r[(g + 8) * TOK + 8 * j + 2 * c + 1] = acc[j][3];
+      }
+      gt_consumer_sync();
+      for (int idx = tid; idx < 16 * TOK; idx += GT_CONSUMERS * 32) {
+        const int t = idx >> 4, f = idx & 15;
+        if (t < p.M && u * 16 + f < p.N) {
+          float sum = 0.f;
+#pragma unroll
+          for (int wi = 0; wi < GT_CONSUMERS; ++wi) sum += red[((size_t)wi * 16 + f) * TOK + t];
+          out[(size_t)t * p.out_stride + u * 16 + f] = gt_out<OutT>(sum);
+        }
+      }
+      gt_consumer_sync();
+    }
+  }
+}
+
+typedef CUresult (*gt_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static gt_encode_fn gt_encoder() {
+  static gt_encode_fn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (gt_encode_fn)ptr;
+  }
+  return fn;
+}
+
+// Tensor map of W [rows, K] (bfloat16, row-major) with boxes of box_rows rows x 64 k, 128-byte swizzle.
+static int gt_make_map(CUtensorMap* map, const void* w, long rows, long K, int box_rows) {
+  gt_encode_fn enc = gt_encoder();
+  if (enc == nullptr) return (int)cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int MODE, int MT, typename OutT>
+static int gt_launch(const GtParams& p, const void* w, int sm_count, cudaStream_t stream) {
+  using S = GtShape<MODE>;
+  CUtensorMap map;
+  const long w_rows = (MODE == GT_MODE_GATED) ? 2l * p.N : p.N;
+  const int rc = gt_make_map(&map, w, w_rows, p.K, S::BOX_ROWS);
+  if (rc != 0) return rc;
+  const size_t smem = 1024 + (size_t)S::STAGES * S::ROWS * S::KC * 2 + 2 * S::STAGES * 8 +
+                      (MODE == GT_MODE_NARROW ? sizeof(float) * GT_CONSUMERS * 16 * 8 * MT : 0);
+  cudaFuncSetAttribute(gemm_stream_kernel<MODE, MT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const int grid = p.units < 2 * sm_count ? p.units : 2 * sm_count;
+  gemm_stream_kernel<MODE, MT, OutT><<<grid, GT_THREADS, smem, stream>>>(p, map);
+  return LL_LAUNCH_RESULT();
+}
+
+template <int MODE, typename OutT>
+static int gt_dispatch_m(const GtParams& p, const void* w, int sm_count, cudaStream_t stream) {
+  if (p.M <= 8) return gt_launch<MODE, 1, OutT>(p, w, sm_count, stream);
+  if (p.M <= 16) return gt_launch<MODE, 2, OutT>(p, w, sm_count, stream);
+  if (p.M <= 32) return gt_launch<MODE, 4, OutT>(p, w, sm_count, stream);
+  return (int)cudaErrorInvalidValue;
+}
+
+// mode: 0 wide, 1 gated, 2 narrow.  x: bfloat16 [M, K] with row stride x_stride; w: bfloat16
+// [N, K] contiguous (gated: [2 N, K]); out: [M, N] bfloat16, or float32 with out_f32 = 1
+// (not for gated).  ksplit > 1 cuts the k range into that many parts, each a work unit of
+// its own: out must then be float32 [ksplit, M, N] (out_stride = N) and receives partial
+// sums that the caller adds (the fused residual-and-norm kernel does).
+// sm_count: SMs of the device (the grid is at most two CTAs an SM).
+extern "C" int ll_gemm_stream(void* out, long out_stride, int out_f32, const void* x, long x_stride, const void* w,
+                              int M, int N, int K, int mode, int ksplit, int sm_count, int* status,
+                              cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 32 || K <= 0 || (x_stride % 8) != 0 || sm_count <= 0 || ksplit < 1) return (int)cudaErrorInvalidValue;
+  if (ksplit > 1 && (!out_f32 || mode == GT_MODE_GATED)) return (int)cudaErrorInvalidValue;
+  GtParams p;
+  p.x = (const bf16*)x;
+  p.out = out;
+  p.x_stride = x_stride;
+  p.out_stride = out_stride;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.status = status;
+  if (mode == GT_MODE_WIDE) {
+    if (K % 128) return (int)cudaErrorInvalidValue;
+    p.cpp = (K / 128 + ksplit - 1) / ksplit;
+    p.ksplit = (K / 128 + p.cpp - 1) / p.cpp;
+    if (p.ksplit != ksplit) return (int)cudaErrorInvalidValue;  // the caller's partial buffer would not fit
+    p.units = ((N + 63) / 64) * p.ksplit;
+    return out_f32 ? gt_dispatch_m<GT_MODE_WIDE, float>(p, w, sm_count, stream)
+                   : gt_dispatch_m<GT_MODE_WIDE, bf16>(p, w, sm_count, stream);
+  }
+  if (mode == GT_MODE_GATED) {
+    if (K % 128 || out_f32) return (int)cudaErrorInvalidValue;
+    p.cpp = K / 128;
+    p.ksplit = 1;
+    p.units = (N + 31) / 32;
+    return gt_dispatch_m<GT_MODE_GATED, bf16>(p, w, sm_count, stream);
+  }
+  if (mode == GT_MODE_NARROW) {
+    if (K % 256) return (int)cudaErrorInvalidValue;
+    p.cpp = (K / 256 + ksplit - 1) / ksplit;
+    p.ksplit = (K / 256 + p.cpp - 1) / p.cpp;
+    if (p.ksplit != ksplit) return (int)cudaErrorInvalidValue;
+    p.units = ((N + 15) / 16) * p.ksplit;
+    return out_f32 ? gt_dispatch_m<GT_MODE_NARROW, float>(p, w, sm_count, stream)
+                   : gt_dispatch_m<GT_MODE_NARROW, bf16>(p, w, sm_count, stream);
+  }
+  return (int)cudaErrorInvalidValue;
+}

@@ -32,6 +32,7 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x, con
 
 template <typename T>
 __global__ void add_rmsnorm_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __restrict__ delta,
+                                   const float* __restrict__ partial, int parts, long part_stride,
                                    const float* __restrict__ w, float eps, int hidden,
                                    const int* __restrict__ rows, int write_residual) {
   extern __shared__ float row[];
@@ -40,11 +41,19 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ out, T* __restrict__ residual
   const int r = rows ? rows[i_out] : i_out;
   T* res = residual + (size_t)r * hidden;
   const T* del = delta ? delta + (size_t)r * hidden : nullptr;
+  const float* par = partial ? partial + (size_t)r * hidden : nullptr;
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = to_f32<T>(res[i]);
     if (del) {
       v = round_to<T>(v + to_f32<T>(del[i]));
+      if (write_residual) res[i] = from_f32<T>(v);
+    } else if (par) {
+      // delta arrives as float32 partial sums of a product split over k: add the parts, round the
+      // sum to the storage type as the unsplit product would have been, then add it
+      float d = 0.f;
+      for (int q = 0; q < parts; ++q) d += par[(size_t)q * part_stride + i];
+      v = round_to<T>(v + round_to<T>(d));
       if (write_residual) res[i] = from_f32<T>(v);
     }
     row[i] = v;
@@ -77,18 +86,20 @@ extern "C" int ll_rmsnorm(int dtype, void* out, const void* x, const float* w, f
 }
 
 // out[i] = norm(residual[r] + delta[r]) with r = rows ? rows[i] : i.
-// delta may be null (plain norm of residual rows).  write_residual stores the
-// rounded sum back into residual (only sensible without `rows`).
-extern "C" int ll_add_rmsnorm(int dtype, void* out, void* residual, const void* delta, const float* w, float eps,
-                              int n_out, int hidden, const int* rows, int write_residual, cudaStream_t stream) {
+// delta may be null (plain norm of residual rows), or given instead as `partial`: float32
+// [parts][tokens, hidden] partial sums (part_stride elements apart) that are added up first.
+// write_residual stores the rounded sum back into residual (only sensible without `rows`).
+extern "C" int ll_add_rmsnorm(int dtype, void* out, void* residual, const void* delta, const float* partial,
+                              int parts, long part_stride, const float* w, float eps, int n_out, int hidden,
+                              const int* rows, int write_residual, cudaStream_t stream) {
   if (n_out <= 0) return 0;
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   LL_DISPATCH_DTYPE(dtype, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<T><<<n_out, norm_threads(hidden), smem, stream>>>((T*)out, (T*)residual, (const T*)delta, w,
-                                                                         eps, hidden, rows, write_residual);
+    add_rmsnorm_kernel<T><<<n_out, norm_threads(hidden), smem, stream>>>(
+        (T*)out, (T*)residual, (const T*)delta, partial, parts, part_stride, w, eps, hidden, rows, write_residual);
   });
   return LL_LAUNCH_RESULT();
 }

@@ -107,14 +107,20 @@ def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: Optional[torch
     _i32(rows, "rows")
     hidden = residual.shape[1]
     _need(residual.is_contiguous() and out.is_contiguous() and out.dtype == residual.dtype, "add_rmsnorm: layout")
-    if delta is not None:
+    if delta is not None and delta.dim() == 2:
         _need(delta.is_contiguous() and delta.dtype == residual.dtype and delta.shape[1] == hidden,
               "add_rmsnorm: delta layout")
     n_out = rows.numel() if rows is not None else residual.shape[0]
     _need(out.shape[0] >= n_out and out.shape[1] == hidden, "add_rmsnorm: out shape")
     wr = 1 if (write_residual and rows is None and delta is not None) else 0
-    core().call("ll_add_rmsnorm", c_int(_dtype_code(residual)), _ptr(out), _ptr(residual), _ptr(delta), _ptr(weight),
-                c_float(eps), c_int(n_out), c_int(hidden), _ptr(rows), c_int(wr), _stream())
+    partial, parts, part_stride = None, 0, 0
+    if delta is not None and delta.dim() == 3:      # float32 partial sums [parts, tokens, hidden]
+        _need(delta.dtype == torch.float32 and delta.is_contiguous() and delta.shape[2] == hidden,
+              "add_rmsnorm: partial sums must be contiguous float32 [parts, tokens, hidden]")
+        partial, parts, part_stride, delta = delta, delta.shape[0], delta.shape[1] * hidden, None
+    core().call("ll_add_rmsnorm", c_int(_dtype_code(residual)), _ptr(out), _ptr(residual), _ptr(delta),
+                _ptr(partial), c_int(parts), c_long(part_stride), _ptr(weight), c_float(eps), c_int(n_out),
+                c_int(hidden), _ptr(rows), c_int(wr), _stream())
 
 
 def bias_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: Optional[torch.Tensor],
@@ -314,10 +320,86 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated:
     return out
 
 
+STREAM_M = 32         # the most tokens the bulk-copy streaming kernel takes
+_sm_count = {}
+
+
+def sm_count(device) -> int:
+    n = _sm_count.get(device)
+    if n is None:
+        n = torch.cuda.get_device_properties(device).multi_processor_count
+        _sm_count[device] = n
+    return n
+
+
+def stream_mode(x: torch.Tensor, weight: torch.Tensor, gated: bool = False) -> Optional[int]:
+    """Work-unit shape of ``gemm_stream`` for this product (0 wide, 1 gated, 2 narrow), or None."""
+    if not (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+            and 0 < x.shape[0] <= STREAM_M and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and weight.is_contiguous() and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+        return None
+    k = x.shape[1]
+    if gated:
+        return 1 if k % 128 == 0 else None
+    n = weight.shape[0]
+    if n >= 8192 and k % 128 == 0:
+        return 0
+    if k % 256 == 0:
+        return 2
+    return 0 if k % 128 == 0 else None
+
+
+def stream_ksplit(n: int, k: int, mode: int, device) -> int:
+    """Parts to cut k into so that a product with few output features still has work units for every
+    SM (only worth it for a long k).  The kernel needs every part non-empty: the count is normalised."""
+    if mode == 1 or k < 4096:
+        return 1
+    feats, chunk = (64, 128) if mode == 0 else (16, 256)
+    units = (n + feats - 1) // feats
+    chunks = k // chunk
+    want = max(1, min((2 * sm_count(device)) // units, chunks // 4))
+    cpp = (chunks + want - 1) // want
+    return (chunks + cpp - 1) // cpp
+
+
+def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: int,
+                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = x @ weight.T for up to 32 bfloat16 tokens with the TMA weight-streaming kernel.
+
+    mode 0: units of 64 output features; 1: SiLU-gated (weight [2 I, K], out [M, I]);
+    2: units of 16 features with k split over the warps.  A float32 ``out`` of shape
+    [parts, M, N] receives partial sums of a k range cut into ``parts`` (see ``stream_ksplit``).
+    """
+    _need_cuda(x, weight, out, status)
+    m, k = x.shape
+    gated = mode == 1
+    n = weight.shape[0] // 2 if gated else weight.shape[0]
+    _need(stream_mode(x, weight, gated) is not None, "gemm_stream: bfloat16, at most 32 tokens, K % 128 == 0")
+    _need(mode in (0, 1, 2) and k % (256 if mode == 2 else 128) == 0, "gemm_stream: K does not fit the mode")
+    _need(weight.shape[1] == k, "gemm_stream: weight shape")
+    ksplit = 1
+    if out.dim() == 3:
+        ksplit = out.shape[0]
+        _need(out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape[1:]) == (m, n) and not gated,
+              "gemm_stream: partial sums go to a contiguous float32 [parts, M, N]")
+        out_stride = n
+    else:
+        _need(out.shape[0] == m and out.shape[1] == n and out.stride(1) == 1, "gemm_stream: out shape")
+        out_stride = out.stride(0)
+    _need(out.dtype == torch.bfloat16 or (out.dtype == torch.float32 and not gated), "gemm_stream: out dtype")
+    load_library("gemm_stream").call(
+        "ll_gemm_stream", _ptr(out), c_long(out_stride), c_int(1 if out.dtype == torch.float32 else 0), _ptr(x),
+        c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(mode), c_int(ksplit),
+        c_int(sm_count(x.device)), _ptr(status), _stream())
+    return out
+
+
 def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x @ Wg.T) * (x @ Wu.T) with W = [Wg; Wu]: fused for few tokens, else product + kernel."""
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
+    if stream_mode(x, w_gate_up, gated=True) is not None:
+        return gemm_stream(x, w_gate_up, act, 1)
     if smallm_preferred(x, w_gate_up, gated=True):
         return gemm_smallm(x, w_gate_up, act, gated=True)
     gu = linear(x, w_gate_up)
@@ -326,16 +408,29 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, partial_ok: bool = False) -> torch.Tensor:
     """x [n, in] times weight [out, in] transposed.
 
-    For up to 64 bfloat16 tokens this is the hand-written weight-streaming kernel
-    (``gemm_smallm``).  Otherwise it is a library (cuBLAS) product, as in the
-    reference: float32 operands give a true float32 product (TF32 is off); bfloat16
-    operands accumulate in float32.  ``out_dtype=torch.float32`` with bfloat16
-    operands keeps the float32 accumulator as the result (the logits).
+    Up to 32 bfloat16 tokens (decode) go to the hand-written TMA weight-streaming kernel
+    (``gemm_stream``), or to ``gemm_smallm`` for shapes that one does not take.  Everything
+    else is a library (cuBLAS) product, as in the reference: float32 operands give a true
+    float32 product (TF32 is off); bfloat16 operands accumulate in float32.
+    ``out_dtype=torch.float32`` with bfloat16 operands keeps the float32 accumulator as the
+    result (the logits).  ``partial_ok``: the caller's consumer (the fused residual-and-norm
+    kernel) accepts float32 partial sums [parts, n, out] of a product split over k.
     """
     _need_cuda(x, weight)
+    mode = stream_mode(x, weight) if (out is None or out.stride(1) == 1) else None
+    if mode is not None:
+        dt = out_dtype or x.dtype
+        if out is None:
+            parts = stream_ksplit(weight.shape[0], x.shape[1], mode, x.device) if (partial_ok and dt == x.dtype) else 1
+            if parts > 1:
+                out = torch.empty((parts, x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+                return gemm_stream(x, weight, out, mode)
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=dt, device=x.device)
+        if out.dtype == dt:
+            return gemm_stream(x, weight, out, mode)
     if smallm_preferred(x, weight) and (out is None or out.stride(1) == 1):
         dt = out_dtype or x.dtype
         if out is None:

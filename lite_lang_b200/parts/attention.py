@@ -83,7 +83,7 @@ class GQAttention(Mixer):
     def kernel_libraries(self):
         libs = ["core"]
         if self.w_qkv is not None and self.w_qkv.dtype == torch.bfloat16:
-            libs.append("gemm_smallm")
+            libs.extend(["gemm_smallm", "gemm_stream"])
             if self.head_dim in (64, 128):
                 libs.append("attn_mma")
         return libs
@@ -111,7 +111,7 @@ class GQAttention(Mixer):
                                     slot_map, cache.k, cache.v, cache.page_size, step.status, n)
         attn = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
         self.attend(attn, qkv, step, cache)
-        return ops.linear(attn, self.w_o)
+        return ops.linear(attn, self.w_o, partial_ok=True)
 
     # scratch memory of the split kernel, shared by all layers (they run one after the other)
     _workspaces: Dict[tuple, tuple] = {}

@@ -92,7 +92,11 @@ class Norm(Part):
         """residual += delta (in place, unless ``rows`` selects rows), then the norm of it.
 
         The default is the unfused form; a part with a fused kernel overrides it.
+        ``delta`` may also be float32 partial sums [parts, tokens, hidden] of a product that was
+        split over its inner dimension; they are added up first.
         """
+        if delta is not None and delta.dim() == 3:
+            delta = delta.sum(0).to(residual.dtype)
         if rows is not None:
             picked = residual.index_select(0, rows.long())
             if delta is not None:

@@ -404,6 +404,66 @@ def test_gemm_smallm_gated_equals_product_then_activation(m, inter, k):
     assert float((fused.float() - unfused.float()).abs().max()) <= 2e-2 * float(ref.abs().max())
 
 
+@pytest.mark.parametrize("mode,m,n,k", [(2, 1, 48, 256), (2, 8, 2048, 1536), (2, 5, 1536, 8960), (2, 13, 100, 512),
+                                        (0, 8, 9000, 1536), (0, 3, 331, 128), (0, 32, 151936, 256), (2, 32, 272, 1024),
+                                        (0, 16, 64, 384), (2, 16, 17, 768)])
+def test_gemm_stream(mode, m, n, k):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(24)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    for dt in (torch.bfloat16, torch.float32):
+        out = torch.full((m, n), 7.0, dtype=dt, device=dev())
+        for _ in range(2):
+            ops.gemm_stream(x.to(dev()), w.to(dev()), out, mode, status)
+        err = float((out.double().cpu() - ref).abs().max()) / float(ref.abs().max())
+        assert err <= (8e-3 if dt == torch.bfloat16 else 2e-5), (dt, err)
+    assert status.item() == 0
+
+
+@pytest.mark.parametrize("mode,m,n,k,parts", [(2, 8, 1536, 8960, 3), (0, 5, 1536, 8960, 12), (2, 32, 100, 1024, 2),
+                                              (2, 1, 1536, 8960, 35)])
+def test_gemm_stream_split_over_k_and_summed_by_the_norm(mode, m, n, k, parts):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(26)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    out = torch.full((parts, m, n), float("nan"), dtype=torch.float32, device=dev())
+    ops.gemm_stream(x.to(dev()), w.to(dev()), out, mode)
+    total = out.double().sum(0).cpu()
+    assert float((total - ref).abs().max()) / float(ref.abs().max()) <= 2e-5
+    # the fused residual-and-norm kernel takes the partial sums as its delta
+    res = torch.randn(m, n, generator=g).to(torch.bfloat16)
+    wn = 1 + 0.1 * torch.randn(n, generator=g)
+    res_dev = res.to(dev()).clone()
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=dev())
+    ops.add_rmsnorm(y, res_dev, out, wn.to(dev()), 1e-6)
+    s_ref = (res.float() + ref.float().to(torch.bfloat16).float()).to(torch.bfloat16)
+    assert float((res_dev.float().cpu() - s_ref.float()).abs().max()) <= 2 ** -6 * float(s_ref.float().abs().max())
+    assert_close(y, P.rms_norm(s_ref.float(), wn, 1e-6), torch.bfloat16, "norm of residual + partial sums")
+    assert ops.stream_ksplit(1536, 8960, 2, dev()) == 3 and ops.stream_ksplit(2048, 1536, 2, dev()) == 1
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 128, 128), (8, 8960, 1536), (20, 203, 384), (32, 320, 256)])
+def test_gemm_stream_gated(m, inter, k):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(25)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(dev())
+    w = (2 * torch.randn(2 * inter, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(dev())
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    fused = ops.gemm_stream(x, w, torch.empty(m, inter, dtype=torch.bfloat16, device=dev()), 1, status)
+    gu = torch.mm(x, w.t())
+    unfused = torch.empty(m, inter, dtype=torch.bfloat16, device=dev())
+    ops.silu_mul(unfused, gu)
+    ref = P.silu_and_mul(P.linear(x.float().cpu(), w[:inter].float().cpu()), P.linear(x.float().cpu(), w[inter:].float().cpu()))
+    assert_close(fused, ref, torch.bfloat16, "gated")
+    assert float((fused.float() - unfused.float()).abs().max()) <= 2e-2 * float(ref.abs().max())
+    assert status.item() == 0
+
+
 def test_linear_picks_the_library_for_other_shapes():
     from lite_lang_b200 import ops
     ops.configure_matmul_precision()
