@@ -6,6 +6,8 @@
 
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, long total, int inter) {
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
   const long idx0 = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const long step = (long)gridDim.x * blockDim.x;
   for (long idx = idx0; idx < total; idx += step) {
@@ -19,6 +21,8 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, l
 
 // 8 bf16 values a thread; needs inter % 8 == 0.
 __global__ void silu_mul_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restrict__ gu, long total8, int inter8) {
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
   const long idx0 = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const long step = (long)gridDim.x * blockDim.x;
   for (long idx = idx0; idx < total8; idx += step) {
@@ -46,11 +50,12 @@ extern "C" int ll_silu_mul(int dtype, void* out, const void* gate_up, int num_to
   if (dtype == LL_DTYPE_BF16 && (inter % 8) == 0) {
     const long total8 = total / 8;
     const int blocks = (int)min((total8 + 255) / 256, (long)148 * 16);
-    silu_mul_bf16x8_kernel<<<blocks, 256, 0, stream>>>((bf16*)out, (const bf16*)gate_up, total8, inter / 8);
+    ll_launch(silu_mul_bf16x8_kernel, dim3(blocks), dim3(256), 0, stream, (bf16*)out, (const bf16*)gate_up, total8,
+              inter / 8);
     return LL_LAUNCH_RESULT();
   }
   const int blocks = (int)min((total + 255) / 256, (long)148 * 16);
-  LL_DISPATCH_DTYPE(dtype,
-                    (silu_mul_kernel<T><<<blocks, 256, 0, stream>>>((T*)out, (const T*)gate_up, total, inter)));
+  LL_DISPATCH_DTYPE(dtype, ll_launch(silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)out,
+                                     (const T*)gate_up, total, inter));
   return LL_LAUNCH_RESULT();
 }

@@ -31,6 +31,8 @@ paged_attention_generic_kernel(T* __restrict__ out, long out_stride, const T* __
                                const int* __restrict__ req_slot, const int* __restrict__ positions, int nh, int nkv,
                                int hd, int page_size, int num_pages, int window, float scale, int* status) {
   extern __shared__ float smem[];
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
   const int t = blockIdx.x;
   const int kvh = blockIdx.y;
   const int group = nh / nkv;
@@ -175,9 +177,9 @@ extern "C" int ll_paged_attention_generic(int dtype, void* out, long out_stride,
   LL_DISPATCH_DTYPE(dtype, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(paged_attention_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    paged_attention_generic_kernel<T><<<grid, AG_THREADS, smem, stream>>>(
-        (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, bt_stride,
-        token_req, req_slot, positions, nh, nkv, hd, page_size, num_pages, window, scale, status);
+    ll_launch(paged_attention_generic_kernel<T>, grid, dim3(AG_THREADS), smem, stream, (T*)out, out_stride,
+              (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, bt_stride, token_req, req_slot,
+              positions, nh, nkv, hd, page_size, num_pages, window, scale, status);
   });
   return LL_LAUNCH_RESULT();
 }

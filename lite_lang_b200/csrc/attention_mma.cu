@@ -90,6 +90,8 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
   __shared__ float sm_l[AM_WARPS][AM_ROWS];
   __shared__ int sm_last;
 
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int kvh = blockIdx.y, split = blockIdx.z;
@@ -472,8 +474,8 @@ extern "C" int ll_attn_mma(void* out, long out_stride, const void* q, long q_str
   if (nsplit > 1 && (scratch == nullptr || counters == nullptr)) return (int)cudaErrorInvalidValue;
   dim3 grid(row_blocks, nkv, nsplit);
   if (hd == 64)
-    attn_mma_kernel<64><<<grid, AM_THREADS, 0, stream>>>(p);
+    ll_launch(attn_mma_kernel<64>, grid, dim3(AM_THREADS), 0, stream, p);
   else
-    attn_mma_kernel<128><<<grid, AM_THREADS, 0, stream>>>(p);
+    ll_launch(attn_mma_kernel<128>, grid, dim3(AM_THREADS), 0, stream, p);
   return LL_LAUNCH_RESULT();
 }

@@ -88,3 +88,47 @@ __device__ __forceinline__ void set_status(int* status, int code) {
   } while (0)
 
 #define LL_LAUNCH_RESULT() ((int)cudaGetLastError())
+
+// ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of this package starts with LL_PDL_WAIT():
+// it may be scheduled while the kernel before it on the stream is still running, and
+// blocks there until that kernel has finished and its writes are visible.  What a kernel
+// does before the wait must not depend on earlier kernels (the weight-streaming product
+// starts its TMA copies of the weights there).  LL_PDL_TRIGGER() lets the next kernel be
+// scheduled.  Every CTA executes the wait before it exits, so "the kernel before has
+// finished" carries over along the whole chain.  Launched without the attribute (grids of
+// many waves, or LITE_LANG_B200_PDL=0) both instructions do nothing.
+// ---------------------------------------------------------------------------------------
+#define LL_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
+#define LL_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+
+#include <stdlib.h>
+#include <utility>
+static inline bool ll_pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LITE_LANG_B200_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+// Launch with the programmatic-serialization attribute when the grid is small enough to be
+// resident at once (a dependent kernel that waits on an SM must not keep CTAs of a grid of
+// many waves from running).
+template <typename... KArgs, typename... Args>
+static inline void ll_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  const unsigned long long ctas = (unsigned long long)grid.x * grid.y * grid.z;
+  attr[0].val.programmaticStreamSerializationAllowed = (ll_pdl_enabled() && ctas <= 1024) ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}

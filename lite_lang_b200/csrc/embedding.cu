@@ -8,6 +8,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ table,
                                     const int* __restrict__ ids, int hidden, int vocab, int* status) {
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = (id >= 0 && id < vocab);
@@ -28,7 +30,7 @@ __global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ t
 extern "C" int ll_embed_gather(int dtype, void* out, const void* table, const int* ids, int num_tokens,
                                int hidden, int vocab, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  LL_DISPATCH_DTYPE(dtype, (embed_gather_kernel<T><<<num_tokens, 128, 0, stream>>>(
-                               (T*)out, (const T*)table, ids, hidden, vocab, status)));
+  LL_DISPATCH_DTYPE(dtype, ll_launch(embed_gather_kernel<T>, dim3(num_tokens), dim3(128), 0, stream, (T*)out,
+                                     (const T*)table, ids, hidden, vocab, status));
   return LL_LAUNCH_RESULT();
 }

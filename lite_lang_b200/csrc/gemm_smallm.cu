@@ -55,6 +55,8 @@ gemm_smallm_kernel(OutT* __restrict__ out, long out_stride, const bf16* __restri
   extern __shared__ float red[];  // [GS_WARPS][GATED ? 2 : 1][16][8 * MT]
   constexpr int TOK = 8 * MT;
   constexpr int NACC = GATED ? 2 : 1;
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int f0 = blockIdx.x * 16;
@@ -159,8 +161,8 @@ static int gs_launch(void* out, long out_stride, const void* x, long x_stride, c
   const size_t smem = sizeof(float) * GS_WARPS * (GATED ? 2 : 1) * 16 * 8 * MT;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(gemm_smallm_kernel<MT, GATED, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  gemm_smallm_kernel<MT, GATED, OutT><<<(N + 15) / 16, GS_THREADS, smem, stream>>>(
-      (OutT*)out, out_stride, (const bf16*)x, x_stride, (const bf16*)w, M, N, K);
+  ll_launch(gemm_smallm_kernel<MT, GATED, OutT>, dim3((N + 15) / 16), dim3(GS_THREADS), smem, stream, (OutT*)out,
+            out_stride, (const bf16*)x, x_stride, (const bf16*)w, M, N, K);
   return LL_LAUNCH_RESULT();
 }
 

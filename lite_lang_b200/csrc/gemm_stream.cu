@@ -151,7 +151,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  LL_PDL_TRIGGER();
 
   const int kchunks = p.K / S::KC;
 
@@ -194,8 +194,9 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
   const bf16* xp[MT];
 #pragma unroll
   for (int j = 0; j < MT; ++j) xp[j] = p.x + (size_t)min(8 * j + g, p.M - 1) * p.x_stride + 8 * c;
-  // the token rows are written by the kernel before this one
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // the token rows are written by the kernel before this one; the producer warp does not wait (it
+  // only reads weights), the consumers do, so no CTA exits before the kernel before has finished
+  LL_PDL_WAIT();
 
   // k boxes of a stage this warp works on, and where its two A rows sit inside a box
   constexpr int MYBOXES = (MODE == GT_MODE_NARROW) ? 1 : KBOXES;
@@ -350,7 +351,7 @@ static int gt_launch(const GtParams& p, const void* w, int sm_count, cudaStream_
                       (MODE == GT_MODE_NARROW ? sizeof(float) * GT_CONSUMERS * 16 * 8 * MT : 0);
   cudaFuncSetAttribute(gemm_stream_kernel<MODE, MT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const int grid = p.units < 2 * sm_count ? p.units : 2 * sm_count;
-  gemm_stream_kernel<MODE, MT, OutT><<<grid, GT_THREADS, smem, stream>>>(p, map);
+  ll_launch(gemm_stream_kernel<MODE, MT, OutT>, dim3(grid), dim3(GT_THREADS), smem, stream, p, map);
   return LL_LAUNCH_RESULT();
 }
 

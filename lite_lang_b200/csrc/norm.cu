@@ -16,6 +16,8 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x, con
                                float eps, int hidden, long x_stride, long out_stride) {
   extern __shared__ float row[];
   __shared__ float scratch[32];
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
   const int r = blockIdx.x;
   const T* xr = x + (size_t)r * x_stride;
   float ss = 0.f;
@@ -37,6 +39,8 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ out, T* __restrict__ residual
                                    const int* __restrict__ rows, int write_residual) {
   extern __shared__ float row[];
   __shared__ float scratch[32];
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
   const int i_out = blockIdx.x;
   const int r = rows ? rows[i_out] : i_out;
   T* res = residual + (size_t)r * hidden;
@@ -79,8 +83,8 @@ extern "C" int ll_rmsnorm(int dtype, void* out, const void* x, const float* w, f
   LL_DISPATCH_DTYPE(dtype, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    rmsnorm_kernel<T><<<rows, norm_threads(hidden), smem, stream>>>((T*)out, (const T*)x, w, eps, hidden, x_stride,
-                                                                     out_stride);
+    ll_launch(rmsnorm_kernel<T>, dim3(rows), dim3(norm_threads(hidden)), smem, stream, (T*)out, (const T*)x, w, eps,
+              hidden, x_stride, out_stride);
   });
   return LL_LAUNCH_RESULT();
 }
@@ -98,8 +102,8 @@ extern "C" int ll_add_rmsnorm(int dtype, void* out, void* residual, const void* 
   LL_DISPATCH_DTYPE(dtype, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<T><<<n_out, norm_threads(hidden), smem, stream>>>(
-        (T*)out, (T*)residual, (const T*)delta, partial, parts, part_stride, w, eps, hidden, rows, write_residual);
+    ll_launch(add_rmsnorm_kernel<T>, dim3(n_out), dim3(norm_threads(hidden)), smem, stream, (T*)out, (T*)residual,
+              (const T*)delta, partial, parts, part_stride, w, eps, hidden, rows, write_residual);
   });
   return LL_LAUNCH_RESULT();
 }

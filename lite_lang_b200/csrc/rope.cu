@@ -25,6 +25,8 @@ __global__ void bias_rope_store_kernel(T* __restrict__ qkv, long qkv_stride, con
                                        const int* __restrict__ slot_map, T* __restrict__ k_cache,
                                        T* __restrict__ v_cache, int page_size, long num_slots, int write_q,
                                        int* status) {
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
   const int t = blockIdx.x;
   T* row = qkv + (size_t)t * qkv_stride;
   int pos = positions ? positions[t] : 0;
@@ -114,8 +116,8 @@ extern "C" int ll_bias_rope_store(int dtype, void* qkv, long qkv_stride, const f
   if (do_rope && (rot_dim <= 0 || (rot_dim & 1) || rot_dim > hd)) return (int)cudaErrorInvalidValue;
   if (!do_rope) rot_dim = 0;
   const int write_q = (bias != nullptr) || do_rope;
-  LL_DISPATCH_DTYPE(dtype, (bias_rope_store_kernel<T><<<num_tokens, 256, 0, stream>>>(
-                               (T*)qkv, qkv_stride, bias, positions, cos_sin, max_pos, rot_dim, do_rope, nh, nkv, hd,
-                               slot_map, (T*)k_cache, (T*)v_cache, page_size, num_slots, write_q, status)));
+  LL_DISPATCH_DTYPE(dtype, ll_launch(bias_rope_store_kernel<T>, dim3(num_tokens), dim3(256), 0, stream, (T*)qkv,
+                                     qkv_stride, bias, positions, cos_sin, max_pos, rot_dim, do_rope, nh, nkv, hd,
+                                     slot_map, (T*)k_cache, (T*)v_cache, page_size, num_slots, write_q, status));
   return LL_LAUNCH_RESULT();
 }

@@ -81,6 +81,8 @@ sample_stage1_kernel(const float* __restrict__ logits, long row_stride, const fl
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ float s_sum[32];
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
   const int chunk = blockIdx.x, r = blockIdx.y;
   const int c0 = chunk * SM_CHUNK, n = min(SM_CHUNK, vocab - c0);
   const float* row = logits + (size_t)r * row_stride + c0;
@@ -109,7 +111,9 @@ sample_stage2_kernel(const float* __restrict__ logits, long row_stride, const fl
   __shared__ float s_part[SM_T1];
   __shared__ float s_M;
   __shared__ int s_arg, s_chunk;
-  __shared__ float s_before, s_target, s_scale;
+  __shared__ float s_before, s_target;
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
   const int r = blockIdx.x;
   const float* pr = part + (size_t)r * nchunks * 3;
   const float temp = temperature ? temperature[r] : 0.f;
@@ -208,9 +212,9 @@ extern "C" int ll_sample(const float* logits, long row_stride, const float* temp
   if (vocab <= 0 || scratch == nullptr || rows > 65535) return (int)cudaErrorInvalidValue;
   if (temperature != nullptr && uniform == nullptr) return (int)cudaErrorInvalidValue;
   const int nchunks = (vocab + SM_CHUNK - 1) / SM_CHUNK;
-  sample_stage1_kernel<<<dim3(nchunks, rows), SM_T1, 0, stream>>>(logits, row_stride, temperature, scratch, vocab,
-                                                                   nchunks);
-  sample_stage2_kernel<<<rows, SM_T1, 0, stream>>>(logits, row_stride, temperature, uniform, scratch, out, vocab,
-                                                   nchunks);
+  ll_launch(sample_stage1_kernel, dim3(nchunks, rows), dim3(SM_T1), 0, stream, logits, row_stride, temperature,
+            scratch, vocab, nchunks);
+  ll_launch(sample_stage2_kernel, dim3(rows), dim3(SM_T1), 0, stream, logits, row_stride, temperature, uniform,
+            (const float*)scratch, out, vocab, nchunks);
   return LL_LAUNCH_RESULT();
 }
