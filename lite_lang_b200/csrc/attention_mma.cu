@@ -53,6 +53,7 @@ struct AttnMmaParams {
   int window;
   float scale_log2;  // softmax scale times log2(e)
   int nsplit;
+  int all_single;  // every entry brings one token and a group fits a row block: entry = blockIdx.x
   float* scratch_o;   // [row blocks * nkv * nsplit][16][HD]
   float* scratch_ml;  // [row blocks * nkv * nsplit][16][2]
   int* counters;      // [row blocks * nkv], zero before and after every launch
@@ -97,17 +98,26 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
   const int kvh = blockIdx.y, split = blockIdx.z;
 
   // ---- which entry does this row block belong to ----
-  int e = 0, base = 0, ql = 0;
-  for (; e < p.n_entries; ++e) {
-    ql = p.cu_q[e + 1] - p.cu_q[e];
-    const int nb = (ql * p.group + AM_ROWS - 1) / AM_ROWS;
-    if ((int)blockIdx.x < base + nb) break;
-    base += nb;
+  int e = 0, base = 0, ql = 0, tok0;
+  if (p.all_single) {  // decode: no search, and one memory round trip less
+    e = blockIdx.x;
+    base = e;
+    ql = 1;
+    tok0 = e;
+    if (e >= p.n_entries) return;
+  } else {
+    for (; e < p.n_entries; ++e) {
+      ql = p.cu_q[e + 1] - p.cu_q[e];
+      const int nb = (ql * p.group + AM_ROWS - 1) / AM_ROWS;
+      if ((int)blockIdx.x < base + nb) break;
+      base += nb;
+    }
+    if (e >= p.n_entries) return;
+    tok0 = p.cu_q[e];
   }
-  if (e >= p.n_entries) return;
   const int r0 = ((int)blockIdx.x - base) * AM_ROWS;
-  const int tok0 = p.cu_q[e];
   const int slot = p.req_slot[e];
+  const int ctx = p.ctx_len[e];
   const int total_rows = ql * p.group;
 
   // rows of this thread: g and g + 8
@@ -121,6 +131,18 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
     tokr[i] = rr / p.group;
     headr[i] = kvh * p.group + (rr - tokr[i] * p.group);
   }
+  // ---- Q fragments (issued before anything waits for the slot and the context length) ----
+  uint4 qa[KS], qb[KS];
+  {
+    const bf16* qra = p.q + (size_t)(tok0 + tokr[0]) * p.q_stride + (size_t)headr[0] * HD + 8 * c;
+    const bf16* qrb = p.q + (size_t)(tok0 + tokr[1]) * p.q_stride + (size_t)headr[1] * HD + 8 * c;
+#pragma unroll
+    for (int s = 0; s < KS; ++s) {
+      qa[s] = validr[0] ? ldg16(qra + 32 * s) : make_uint4(0, 0, 0, 0);
+      qb[s] = validr[1] ? ldg16(qrb + 32 * s) : make_uint4(0, 0, 0, 0);
+    }
+  }
+
   if (slot < 0) {  // padding entry of a captured step: zeros, no reads, counters untouched
     if (split == 0 && warp == 0) {
 #pragma unroll
@@ -132,7 +154,6 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
     }
     return;
   }
-  const int ctx = p.ctx_len[e];
   int posr[2], lor[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -152,18 +173,6 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
   const int tps = (ntiles + p.nsplit - 1) / p.nsplit;
   const int t_begin = t_first + split * tps;
   const int t_end = min(t_last + 1, t_begin + tps);
-
-  // ---- Q fragments ----
-  uint4 qa[KS], qb[KS];
-  {
-    const bf16* qra = p.q + (size_t)(tok0 + tokr[0]) * p.q_stride + (size_t)headr[0] * HD + 8 * c;
-    const bf16* qrb = p.q + (size_t)(tok0 + tokr[1]) * p.q_stride + (size_t)headr[1] * HD + 8 * c;
-#pragma unroll
-    for (int s = 0; s < KS; ++s) {
-      qa[s] = validr[0] ? ldg16(qra + 32 * s) : make_uint4(0, 0, 0, 0);
-      qb[s] = validr[1] ? ldg16(qrb + 32 * s) : make_uint4(0, 0, 0, 0);
-    }
-  }
 
   float o_acc[NT][4];
 #pragma unroll
@@ -389,15 +398,16 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
   float Lg = 0.f;
 #pragma unroll
   for (int d = 0; d < DPT; ++d) acc[d] = 0.f;
-  for (int s0 = 0; s0 < p.nsplit; s0 += 2) {
-    float v[2][DPT], ms[2], ls[2];
+  for (int s0 = 0; s0 < p.nsplit; s0 += 4) {
+    float v[4][DPT], ms[4], ls[4];
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < 4; ++k) {
       const int s = min(s0 + k, p.nsplit - 1);
       const float* sml = p.scratch_ml + ((item * p.nsplit + s) * AM_ROWS + row) * 2;
       const float* po = p.scratch_o + ((item * p.nsplit + s) * AM_ROWS + row) * HD + dbase;
-      ms[k] = __ldcg(sml);
-      ls[k] = __ldcg(sml + 1);
+      const float2 mlv = __ldcg(reinterpret_cast<const float2*>(sml));
+      ms[k] = mlv.x;
+      ls[k] = mlv.y;
 #pragma unroll
       for (int d = 0; d < DPT; d += 4) {
         const float4 x = __ldcg(reinterpret_cast<const float4*>(po + d));
@@ -408,7 +418,7 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
       }
     }
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < 4; ++k) {
       if (s0 + k < p.nsplit) {
         const float ws = fast_exp2(ms[k] - Mgs);
         Lg += ls[k] * ws;
@@ -431,6 +441,12 @@ extern "C" long ll_attn_mma_scratch_floats(int row_blocks, int nkv, int nsplit, 
   return (long)row_blocks * nkv * nsplit * AM_ROWS * (hd + 2);
 }
 
+extern "C" int ll_attn_mma_ex(void* out, long out_stride, const void* q, long q_stride, const void* k_cache,
+                              const void* v_cache, const int* block_table, int bt_stride, const int* cu_q,
+                              const int* ctx_len, const int* req_slot, int n_entries, int row_blocks, int nh, int nkv,
+                              int hd, int page_size, int num_pages, int window, float scale, int nsplit,
+                              int all_single, float* scratch, int* counters, int* status, cudaStream_t stream);
+
 // q: query rows, head h of token t at q + t*q_stride + h*hd (bfloat16); out likewise.
 // cu_q / ctx_len / req_slot describe the entries; row_blocks = sum over entries of
 // ceil(q_len * group / 16), counted by the caller.  scratch: float32, at least
@@ -441,6 +457,18 @@ extern "C" int ll_attn_mma(void* out, long out_stride, const void* q, long q_str
                            const int* ctx_len, const int* req_slot, int n_entries, int row_blocks, int nh, int nkv,
                            int hd, int page_size, int num_pages, int window, float scale, int nsplit, float* scratch,
                            int* counters, int* status, cudaStream_t stream) {
+  return ll_attn_mma_ex(out, out_stride, q, q_stride, k_cache, v_cache, block_table, bt_stride, cu_q, ctx_len, req_slot,
+                        n_entries, row_blocks, nh, nkv, hd, page_size, num_pages, window, scale, nsplit, 0, scratch,
+                        counters, status, stream);
+}
+
+// The same with a promise: all_single != 0 says that every entry brings exactly one token (a decode
+// step), which saves the kernel the search for its entry.
+extern "C" int ll_attn_mma_ex(void* out, long out_stride, const void* q, long q_stride, const void* k_cache,
+                              const void* v_cache, const int* block_table, int bt_stride, const int* cu_q,
+                              const int* ctx_len, const int* req_slot, int n_entries, int row_blocks, int nh, int nkv,
+                              int hd, int page_size, int num_pages, int window, float scale, int nsplit,
+                              int all_single, float* scratch, int* counters, int* status, cudaStream_t stream) {
   if (row_blocks <= 0 || n_entries <= 0) return 0;
   if ((hd != 64 && hd != 128) || page_size % AM_TILE != 0 || nkv <= 0 || nh % nkv != 0 || nsplit < 1 ||
       nsplit > 65535 || nkv > 65535)
@@ -467,6 +495,7 @@ extern "C" int ll_attn_mma(void* out, long out_stride, const void* q, long q_str
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.nsplit = nsplit;
+  p.all_single = (row_blocks == n_entries && p.group <= AM_ROWS && all_single) ? 1 : 0;
   p.scratch_o = scratch;
   p.scratch_ml = scratch ? scratch + (long)row_blocks * nkv * nsplit * AM_ROWS * hd : nullptr;
   p.counters = counters;

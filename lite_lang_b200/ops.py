@@ -209,13 +209,14 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
              block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
              num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
              window: Optional[int], scale: float, nsplit: int, scratch: Optional[torch.Tensor],
-             counters: Optional[torch.Tensor], status: Optional[torch.Tensor]) -> None:
+             counters: Optional[torch.Tensor], status: Optional[torch.Tensor], all_single: bool = False) -> None:
     """Tensor-core paged attention (bfloat16) of the step's entries: decode and prompt portions.
 
     ``row_blocks`` is the sum over entries of ceil(q_len * group / 16).  With ``nsplit`` > 1 the
     keys of every row block are split over that many CTAs, which park partial results in
     ``scratch`` (float32, ``attn_mma_scratch_floats`` elements); ``counters`` (int32
-    [row_blocks * num_kv_heads]) must be zero and are left zero.
+    [row_blocks * num_kv_heads]) must be zero and are left zero.  ``all_single`` promises that
+    every entry brings exactly one token (a decode step).
     """
     _need_cuda(out, q, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot, scratch, counters)
     for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot"),
@@ -238,11 +239,11 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
               "attn_mma: scratch too small")
         _need(counters.numel() >= row_blocks * num_kv_heads, "attn_mma: counters too small")
     load_library("attn_mma").call(
-        "ll_attn_mma", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), _ptr(k_cache), _ptr(v_cache),
+        "ll_attn_mma_ex", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), _ptr(k_cache), _ptr(v_cache),
         _ptr(block_table), c_int(block_table.stride(0)), _ptr(cu_q), _ptr(ctx_len), _ptr(req_slot),
         c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
-        c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), c_int(nsplit), _ptr(scratch),
-        _ptr(counters), _ptr(status), _stream())
+        c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), c_int(nsplit),
+        c_int(1 if all_single else 0), _ptr(scratch), _ptr(counters), _ptr(status), _stream())
 
 
 _sample_scratch = {}

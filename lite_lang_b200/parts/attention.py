@@ -137,7 +137,10 @@ class GQAttention(Mixer):
         blocks += (step.num_entries - len(step.entries)) * ((group + 15) // 16)     # padding entries
         ctas = blocks * self.num_kv_heads
         max_tiles = (step.max_kv_len + 15) // 16
-        nsplit = max(1, min((2 * self.SM_COUNT) // ctas, max(1, max_tiles // 4)))    # one wave of CTAs
+        # one wave of CTAs at most, and at least 8 tiles (128 keys) a split: with less, merging the
+        # splits costs more than the split saves
+        nsplit = max(1, min((2 * self.SM_COUNT) // ctas, max(1, max_tiles // 8)))
+        single = step.max_q_len == 1 and group <= 16
         scratch = counters = None
         if nsplit > 1:
             # a captured step keeps its own buffers alive for as long as its graph exists
@@ -145,17 +148,17 @@ class GQAttention(Mixer):
             scratch, counters = self._workspace(
                 wkey, ops.attn_mma_scratch_floats(blocks, self.num_kv_heads, nsplit, self.head_dim),
                 blocks * self.num_kv_heads, step.token_ids.device)
-        plan = (blocks, nsplit, scratch, counters)
+        plan = (blocks, nsplit, scratch, counters, single)
         step.scratch[key] = plan
         return plan
 
     def attend(self, out, qkv, step, cache) -> None:
         """Attention of the step's tokens over the cache plane; picks the kernel by shape."""
         if ops.attn_mma_supported(qkv.dtype, self.head_dim, cache.page_size, qkv.stride(0)):
-            blocks, nsplit, scratch, counters = self._plan_mma(step, cache.page_size)
+            blocks, nsplit, scratch, counters, single = self._plan_mma(step, cache.page_size)
             ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q, step.ctx_len,
                          step.req_slot, step.num_entries, blocks, self.num_heads, self.num_kv_heads, self.head_dim,
-                         cache.page_size, self.window, self.scale, nsplit, scratch, counters, step.status)
+                         cache.page_size, self.window, self.scale, nsplit, scratch, counters, step.status, single)
             return
         ops.paged_attention_generic(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.token_req,
                                     step.req_slot, step.positions, qkv.shape[0], self.num_heads, self.num_kv_heads,

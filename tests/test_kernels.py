@@ -248,9 +248,10 @@ def _run_mma(c, nh, nkv, hd, ps, window, nsplit):
         counters = torch.zeros(blocks * nkv, dtype=torch.int32, device=d)
     out = torch.full_like(c["q"], 3.0)
     status = torch.zeros(1, dtype=torch.int32, device=d)
+    single = all(ql == 1 for ql in q_lens) and group <= 16     # the decode fast path when it applies
     for _ in range(2):          # twice: the counters must come back to zero
         ops.attn_mma(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], cu_q, ctx, c["req_slot"], len(lens),
-                     blocks, nh, nkv, hd, ps, window, hd ** -0.5, nsplit, scratch, counters, status)
+                     blocks, nh, nkv, hd, ps, window, hd ** -0.5, nsplit, scratch, counters, status, single)
     assert status.item() == 0
     if counters is not None:
         assert int(counters.abs().sum()) == 0
