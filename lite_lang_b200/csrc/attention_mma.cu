@@ -54,6 +54,7 @@ struct AttnMmaParams {
   float scale_log2;  // softmax scale times log2(e)
   int nsplit;
   int all_single;  // every entry brings one token and a group fits a row block: entry = blockIdx.x
+  int cluster;     // the nsplit CTAs of a (row block, kv head) are one thread-block cluster (nsplit 2, 4 or 8)
   float* scratch_o;   // [row blocks * nkv * nsplit][16][HD]
   float* scratch_ml;  // [row blocks * nkv * nsplit][16][2]
   int* counters;      // [row blocks * nkv], zero before and after every launch
@@ -81,6 +82,25 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 __device__ __forceinline__ uint4 ldg16(const bf16* p) { return *reinterpret_cast<const uint4*>(p); }
 
+// ---- thread-block cluster: hardware barrier and reads of another CTA's shared memory ----
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float ld_peer(const float* local, unsigned rank) {
+  unsigned la = (unsigned)__cvta_generic_to_shared(local), ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+
+#define AM_BT_CACHE 256
+
 template <int HD>
 __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParams p) {
   constexpr int KS = HD / 32;  // 16-byte key loads per thread and key row
@@ -90,6 +110,7 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
   __shared__ float sm_m[AM_WARPS][AM_ROWS];
   __shared__ float sm_l[AM_WARPS][AM_ROWS];
   __shared__ int sm_last;
+  __shared__ int sm_bt[AM_BT_CACHE];
 
   LL_PDL_WAIT();
   LL_PDL_TRIGGER();
@@ -182,9 +203,18 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
   const int* bt = p.block_table + (size_t)slot * p.bt_stride;
   uint4 kk[2][KS], vv[VS][4];
 
+  // the block-table entries of this CTA's tiles, fetched in one go: the tile loop then depends on
+  // one memory round trip per tile (the keys), not two
+  const int nt_split = t_end - t_begin;
+  const bool bt_cached = nt_split <= AM_BT_CACHE;
+  if (bt_cached) {
+    for (int i = tid; i < nt_split; i += AM_THREADS) sm_bt[i] = bt[((t_begin + i) * AM_TILE) / p.page_size];
+    __syncthreads();
+  }
+
   auto tile_base = [&](int t) -> long {  // element offset of key 0 of tile t for this kv head, or -1
     const int key0 = t * AM_TILE;
-    const int page = bt[key0 / p.page_size];
+    const int page = bt_cached ? sm_bt[t - t_begin] : bt[key0 / p.page_size];
     if (page < 0 || page >= p.num_pages) {
       if (lane == 0) set_status(p.status, LL_ERR_PAGE_RANGE);
       return -1;
@@ -361,6 +391,59 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
     }
     return;
   }
+  if (p.cluster) {
+    // ---- several splits as one cluster: every CTA parks its result in its own shared memory and
+    // finishes a slice of the head dimensions of all rows from its peers' shared memory ----
+    __syncthreads();  // sm_o, sm_m, sm_l have been read by everyone
+#pragma unroll
+    for (int d = 0; d < DPT; ++d) sm_o[0][row][dbase + d] = acc[d];
+    if ((tid & 7) == 0) {
+      sm_m[0][row] = M;
+      sm_l[0][row] = L;
+    }
+    cluster_sync_all();
+    const int cs = p.nsplit;
+    const unsigned rank = cluster_rank();
+    const int slice = HD / cs;                      // dims this CTA finishes
+    const int per = AM_ROWS * slice / AM_THREADS;   // outputs a thread: 1..8, consecutive dims of one row
+    const int o0 = tid * per;
+    const int row2 = o0 / slice, d0 = (int)rank * slice + (o0 - row2 * slice);
+    float ms[8], ls[8], Mg = -INFINITY;
+#pragma unroll
+    for (int sI = 0; sI < 8; ++sI) {
+      if (sI < cs) {
+        ms[sI] = ld_peer(&sm_m[0][row2], sI);
+        ls[sI] = ld_peer(&sm_l[0][row2], sI);
+        Mg = fmaxf(Mg, ms[sI]);
+      }
+    }
+    const float Mgs = (Mg == -INFINITY) ? 0.f : Mg;
+    float Lg = 0.f, fin[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) fin[k] = 0.f;
+#pragma unroll
+    for (int sI = 0; sI < 8; ++sI) {
+      if (sI < cs) {
+        const float ws = fast_exp2(ms[sI] - Mgs);
+        Lg += ls[sI] * ws;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (k < per) fin[k] += ld_peer(&sm_o[0][row2][d0 + k], sI) * ws;
+      }
+    }
+    const int r2 = r0 + row2;
+    if (r2 < total_rows) {
+      const int tok2 = r2 / p.group;
+      const int head2 = kvh * p.group + (r2 - tok2 * p.group);
+      bf16* o2 = p.out + (size_t)(tok0 + tok2) * p.out_stride + (size_t)head2 * HD + d0;
+      const float inv = Lg > 0.f ? 1.0f / Lg : 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (k < per) o2[k] = __float2bfloat16_rn(fin[k] * inv);
+    }
+    cluster_sync_all();  // nobody leaves while its shared memory may still be read
+    return;
+  }
   // ---- several splits: park the partial result, the last CTA to arrive merges ----
   const size_t item = ((size_t)blockIdx.x * p.nkv + kvh);
   float* so = p.scratch_o + ((item * p.nsplit + split) * AM_ROWS + row) * HD + dbase;
@@ -445,7 +528,8 @@ extern "C" int ll_attn_mma_ex(void* out, long out_stride, const void* q, long q_
                               const void* v_cache, const int* block_table, int bt_stride, const int* cu_q,
                               const int* ctx_len, const int* req_slot, int n_entries, int row_blocks, int nh, int nkv,
                               int hd, int page_size, int num_pages, int window, float scale, int nsplit,
-                              int all_single, float* scratch, int* counters, int* status, cudaStream_t stream);
+                              int all_single, int use_cluster, float* scratch, int* counters, int* status,
+                              cudaStream_t stream);
 
 // q: query rows, head h of token t at q + t*q_stride + h*hd (bfloat16); out likewise.
 // cu_q / ctx_len / req_slot describe the entries; row_blocks = sum over entries of
@@ -458,17 +542,20 @@ extern "C" int ll_attn_mma(void* out, long out_stride, const void* q, long q_str
                            int hd, int page_size, int num_pages, int window, float scale, int nsplit, float* scratch,
                            int* counters, int* status, cudaStream_t stream) {
   return ll_attn_mma_ex(out, out_stride, q, q_stride, k_cache, v_cache, block_table, bt_stride, cu_q, ctx_len, req_slot,
-                        n_entries, row_blocks, nh, nkv, hd, page_size, num_pages, window, scale, nsplit, 0, scratch,
+                        n_entries, row_blocks, nh, nkv, hd, page_size, num_pages, window, scale, nsplit, 0, 0, scratch,
                         counters, status, stream);
 }
 
-// The same with a promise: all_single != 0 says that every entry brings exactly one token (a decode
-// step), which saves the kernel the search for its entry.
+// The same with a promise and a choice.  all_single != 0 says that every entry brings exactly one
+// token (a decode step), which saves the kernel the search for its entry.  use_cluster != 0 (nsplit
+// 2, 4 or 8) launches the splits of a row block as one thread-block cluster that merges them through
+// distributed shared memory; scratch and counters are then not used.
 extern "C" int ll_attn_mma_ex(void* out, long out_stride, const void* q, long q_stride, const void* k_cache,
                               const void* v_cache, const int* block_table, int bt_stride, const int* cu_q,
                               const int* ctx_len, const int* req_slot, int n_entries, int row_blocks, int nh, int nkv,
                               int hd, int page_size, int num_pages, int window, float scale, int nsplit,
-                              int all_single, float* scratch, int* counters, int* status, cudaStream_t stream) {
+                              int all_single, int use_cluster, float* scratch, int* counters, int* status,
+                              cudaStream_t stream) {
   if (row_blocks <= 0 || n_entries <= 0) return 0;
   if ((hd != 64 && hd != 128) || page_size % AM_TILE != 0 || nkv <= 0 || nh % nkv != 0 || nsplit < 1 ||
       nsplit > 65535 || nkv > 65535)
@@ -496,15 +583,18 @@ extern "C" int ll_attn_mma_ex(void* out, long out_stride, const void* q, long q_
   p.scale_log2 = scale * 1.4426950408889634f;
   p.nsplit = nsplit;
   p.all_single = (row_blocks == n_entries && p.group <= AM_ROWS && all_single) ? 1 : 0;
+  if (use_cluster && !(nsplit == 2 || nsplit == 4 || nsplit == 8)) return (int)cudaErrorInvalidValue;
+  p.cluster = use_cluster ? 1 : 0;
   p.scratch_o = scratch;
   p.scratch_ml = scratch ? scratch + (long)row_blocks * nkv * nsplit * AM_ROWS * hd : nullptr;
   p.counters = counters;
   p.status = status;
-  if (nsplit > 1 && (scratch == nullptr || counters == nullptr)) return (int)cudaErrorInvalidValue;
+  if (nsplit > 1 && !use_cluster && (scratch == nullptr || counters == nullptr)) return (int)cudaErrorInvalidValue;
   dim3 grid(row_blocks, nkv, nsplit);
+  const int cz = use_cluster ? nsplit : 1;
   if (hd == 64)
-    ll_launch(attn_mma_kernel<64>, grid, dim3(AM_THREADS), 0, stream, p);
+    ll_launch_cluster(attn_mma_kernel<64>, grid, dim3(AM_THREADS), 0, stream, cz, p);
   else
-    ll_launch(attn_mma_kernel<128>, grid, dim3(AM_THREADS), 0, stream, p);
+    ll_launch_cluster(attn_mma_kernel<128>, grid, dim3(AM_THREADS), 0, stream, cz, p);
   return LL_LAUNCH_RESULT();
 }

@@ -116,19 +116,33 @@ static inline bool ll_pdl_enabled() {
 // Launch with the programmatic-serialization attribute when the grid is small enough to be
 // resident at once (a dependent kernel that waits on an SM must not keep CTAs of a grid of
 // many waves from running).
+// cluster_z > 1 makes every cluster_z consecutive CTAs along z one thread-block cluster.
 template <typename... KArgs, typename... Args>
-static inline void ll_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                             Args&&... args) {
+static inline void ll_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, int cluster_z, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   const unsigned long long ctas = (unsigned long long)grid.x * grid.y * grid.z;
   attr[0].val.programmaticStreamSerializationAllowed = (ll_pdl_enabled() && ctas <= 1024) ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (cluster_z > 1) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = (unsigned)cluster_z;
+    cfg.numAttrs = 2;
+  }
   cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
+
+template <typename... KArgs, typename... Args>
+static inline void ll_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  ll_launch_cluster(kernel, grid, block, smem, stream, 1, std::forward<Args>(args)...);
 }

@@ -209,14 +209,17 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
              block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
              num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
              window: Optional[int], scale: float, nsplit: int, scratch: Optional[torch.Tensor],
-             counters: Optional[torch.Tensor], status: Optional[torch.Tensor], all_single: bool = False) -> None:
+             counters: Optional[torch.Tensor], status: Optional[torch.Tensor], all_single: bool = False,
+             cluster: bool = False) -> None:
     """Tensor-core paged attention (bfloat16) of the step's entries: decode and prompt portions.
 
     ``row_blocks`` is the sum over entries of ceil(q_len * group / 16).  With ``nsplit`` > 1 the
     keys of every row block are split over that many CTAs, which park partial results in
     ``scratch`` (float32, ``attn_mma_scratch_floats`` elements); ``counters`` (int32
     [row_blocks * num_kv_heads]) must be zero and are left zero.  ``all_single`` promises that
-    every entry brings exactly one token (a decode step).
+    every entry brings exactly one token (a decode step).  ``cluster`` (nsplit 2, 4 or 8) makes the
+    splits of a row block one thread-block cluster that merges through distributed shared memory;
+    scratch and counters are then not needed.
     """
     _need_cuda(out, q, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot, scratch, counters)
     for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot"),
@@ -233,7 +236,9 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
     _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache plane shape")
     _need(cu_q.numel() >= num_entries + 1 and ctx_len.numel() >= num_entries and req_slot.numel() >= num_entries,
           "attn_mma: entry arrays too short")
-    if nsplit > 1:
+    if cluster:
+        _need(nsplit in (2, 4, 8), "attn_mma: a cluster has 2, 4 or 8 splits")
+    if nsplit > 1 and not cluster:
         _need(scratch is not None and counters is not None, "attn_mma: splits need scratch and counters")
         _need(scratch.numel() >= attn_mma_scratch_floats(row_blocks, num_kv_heads, nsplit, head_dim),
               "attn_mma: scratch too small")
@@ -243,7 +248,8 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
         _ptr(block_table), c_int(block_table.stride(0)), _ptr(cu_q), _ptr(ctx_len), _ptr(req_slot),
         c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
         c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), c_int(nsplit),
-        c_int(1 if all_single else 0), _ptr(scratch), _ptr(counters), _ptr(status), _stream())
+        c_int(1 if all_single else 0), c_int(1 if cluster else 0), _ptr(scratch), _ptr(counters), _ptr(status),
+        _stream())
 
 
 _sample_scratch = {}

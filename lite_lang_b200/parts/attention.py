@@ -139,15 +139,12 @@ class GQAttention(Mixer):
         max_tiles = (step.max_kv_len + 15) // 16
         # one wave of CTAs at most, and at least 8 tiles (128 keys) a split: with less, merging the
         # splits costs more than the split saves
-        nsplit = max(1, min((2 * self.SM_COUNT) // ctas, max(1, max_tiles // 8)))
+        want = max(1, min((2 * self.SM_COUNT) // ctas, max(1, max_tiles // 8)))
+        nsplit = 8 if want >= 8 else 4 if want >= 4 else 2 if want >= 2 else 1
+        # the splits of a row block form a thread-block cluster and merge through distributed shared
+        # memory: no scratch memory, no counters
         single = step.max_q_len == 1 and group <= 16
         scratch = counters = None
-        if nsplit > 1:
-            # a captured step keeps its own buffers alive for as long as its graph exists
-            wkey = (key, blocks, nsplit) if getattr(step, "captured", False) else (key, "eager")
-            scratch, counters = self._workspace(
-                wkey, ops.attn_mma_scratch_floats(blocks, self.num_kv_heads, nsplit, self.head_dim),
-                blocks * self.num_kv_heads, step.token_ids.device)
         plan = (blocks, nsplit, scratch, counters, single)
         step.scratch[key] = plan
         return plan
@@ -158,7 +155,8 @@ class GQAttention(Mixer):
             blocks, nsplit, scratch, counters, single = self._plan_mma(step, cache.page_size)
             ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q, step.ctx_len,
                          step.req_slot, step.num_entries, blocks, self.num_heads, self.num_kv_heads, self.head_dim,
-                         cache.page_size, self.window, self.scale, nsplit, scratch, counters, step.status, single)
+                         cache.page_size, self.window, self.scale, nsplit, scratch, counters, step.status, single,
+                         cluster=nsplit > 1)
             return
         ops.paged_attention_generic(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.token_req,
                                     step.req_slot, step.positions, qkv.shape[0], self.num_heads, self.num_kv_heads,

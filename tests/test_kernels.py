@@ -228,10 +228,13 @@ MMA_SHAPES = [
     (40, 2, 64, 16, [99, 50], [2, 1], None, 4),                  # group 20: a token's heads span row blocks
     (4, 4, 128, 16, [200, 77], [5, 1], 50, 2),                   # window
     (8, 2, 64, 16, [160], [160], 33, 1),                         # window inside a whole prompt
+    (12, 2, 128, 16, [2100, 33, 1, 640], [1, 1, 1, 1], None, 8),  # decode, splits of 2, 4, 8 also as clusters
+    (8, 2, 64, 16, [500, 90], [1, 30], None, 4),
+    (3, 1, 128, 32, [257, 300], [100, 1], 120, 2),
 ]
 
 
-def _run_mma(c, nh, nkv, hd, ps, window, nsplit):
+def _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster=False):
     from lite_lang_b200 import ops
     d = dev()
     lens, q_lens = c["lens"], c["q_lens"]
@@ -243,7 +246,7 @@ def _run_mma(c, nh, nkv, hd, ps, window, nsplit):
     ctx = torch.tensor([l - ql for l, ql in zip(lens, q_lens)], dtype=torch.int32, device=d)
     blocks = sum((ql * group + 15) // 16 for ql in q_lens)
     scratch = counters = None
-    if nsplit > 1:
+    if nsplit > 1 and not cluster:
         scratch = torch.full((ops.attn_mma_scratch_floats(blocks, nkv, nsplit, hd),), float("nan"), device=d)
         counters = torch.zeros(blocks * nkv, dtype=torch.int32, device=d)
     out = torch.full_like(c["q"], 3.0)
@@ -251,7 +254,7 @@ def _run_mma(c, nh, nkv, hd, ps, window, nsplit):
     single = all(ql == 1 for ql in q_lens) and group <= 16     # the decode fast path when it applies
     for _ in range(2):          # twice: the counters must come back to zero
         ops.attn_mma(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], cu_q, ctx, c["req_slot"], len(lens),
-                     blocks, nh, nkv, hd, ps, window, hd ** -0.5, nsplit, scratch, counters, status, single)
+                     blocks, nh, nkv, hd, ps, window, hd ** -0.5, nsplit, scratch, counters, status, single, cluster)
     assert status.item() == 0
     if counters is not None:
         assert int(counters.abs().sum()) == 0
@@ -263,11 +266,14 @@ def test_attn_mma(nh, nkv, hd, ps, lens, q_lens, window, nsplit):
     c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, lens, q_lens, window, seed=15)
     out = _run_mma(c, nh, nkv, hd, ps, window, nsplit)
     assert_close(out, c["ref"], torch.bfloat16, "attn_mma")
+    if nsplit in (2, 4, 8):     # the same splits as one thread-block cluster, merged through shared memory
+        out = _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster=True)
+        assert_close(out, c["ref"], torch.bfloat16, "attn_mma as clusters")
 
 
-@pytest.mark.parametrize("nsplit", [1, 5])
+@pytest.mark.parametrize("nsplit,cluster", [(1, False), (5, False), (8, True)])
 @pytest.mark.parametrize("where", ["first", "page_edge", "last_of_page", "window_in", "window_out"])
-def test_attn_mma_finds_one_far_key(where, nsplit):
+def test_attn_mma_finds_one_far_key(where, nsplit, cluster):
     nh, nkv, hd, ps, L, window = 12, 2, 128, 16, 1000, None
     if where == "first":
         peak = lambda l: 0
@@ -279,7 +285,7 @@ def test_attn_mma_finds_one_far_key(where, nsplit):
         window = 300
         peak = (lambda l: l - 300) if where == "window_in" else (lambda l: l - 301)
     c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, [L], [1], window, seed=16, peak=peak)
-    out = _run_mma(c, nh, nkv, hd, ps, window, nsplit)
+    out = _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster)
     assert_close(out, c["ref"], torch.bfloat16, where)
     assert (float(c["ref"].mean()) > 4.5) == (where != "window_out")
 
