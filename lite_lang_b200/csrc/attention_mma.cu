@@ -30,8 +30,9 @@
 // any number of heads.  Other shapes, and float32, go to the generic kernel.
 #include "common.cuh"
 
-#define AM_THREADS 128
-#define AM_WARPS 4
+// 4 or 8 warps a CTA (template parameter NW): 8 when the step has so few row blocks that four warps
+// an SM could not hide instruction latency (a lone warp per scheduler spends about as long on the
+// arithmetic of a tile as on waiting for its keys).
 #define AM_ROWS 16
 #define AM_TILE 16
 
@@ -80,7 +81,15 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-__device__ __forceinline__ uint4 ldg16(const bf16* p) { return *reinterpret_cast<const uint4*>(p); }
+// volatile: the loads stay where they are written, between the MMAs (also volatile), so that the
+// next tile's keys really are requested before the softmax of this one
+__device__ __forceinline__ uint4 ldg16(const bf16* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
 
 // ---- thread-block cluster: hardware barrier and reads of another CTA's shared memory ----
 __device__ __forceinline__ void cluster_sync_all() {
@@ -101,14 +110,16 @@ __device__ __forceinline__ float ld_peer(const float* local, unsigned rank) {
 
 #define AM_BT_CACHE 256
 
-template <int HD>
-__global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParams p) {
+template <int HD, int NW>
+__global__ void __launch_bounds__(NW * 32) attn_mma_kernel(const AttnMmaParams p) {
+  constexpr int AM_WARPS = NW, AM_THREADS = NW * 32;
   constexpr int KS = HD / 32;  // 16-byte key loads per thread and key row
   constexpr int VS = HD / 64;  // 16-byte value loads per thread and key row
   constexpr int NT = HD / 8;   // MMA column tiles of the output
-  __shared__ float sm_o[AM_WARPS][AM_ROWS][HD + 4];
-  __shared__ float sm_m[AM_WARPS][AM_ROWS];
-  __shared__ float sm_l[AM_WARPS][AM_ROWS];
+  extern __shared__ float sm_dyn[];
+  float (*sm_o)[AM_ROWS][HD + 4] = reinterpret_cast<float (*)[AM_ROWS][HD + 4]>(sm_dyn);
+  float (*sm_m)[AM_ROWS] = reinterpret_cast<float (*)[AM_ROWS]>(sm_dyn + AM_WARPS * AM_ROWS * (HD + 4));
+  float (*sm_l)[AM_ROWS] = sm_m + AM_WARPS;
   __shared__ int sm_last;
   __shared__ int sm_bt[AM_BT_CACHE];
 
@@ -255,16 +266,23 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
       continue;
     }
     // ---- S = Q K^T ----
-    float s_acc[2][4];
+    float s_acc[2][4], s_odd[2][4];  // two chains per column tile: an MMA waits ~30 cycles for the one before
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       s_acc[u][0] = s_acc[u][1] = s_acc[u][2] = s_acc[u][3] = 0.f;
-#pragma unroll
-      for (int s = 0; s < KS; ++s) {
-        mma_bf16_16816(s_acc[u], qa[s].x, qb[s].x, qa[s].y, qb[s].y, kk[u][s].x, kk[u][s].y);
-        mma_bf16_16816(s_acc[u], qa[s].z, qb[s].z, qa[s].w, qb[s].w, kk[u][s].z, kk[u][s].w);
-      }
+      s_odd[u][0] = s_odd[u][1] = s_odd[u][2] = s_odd[u][3] = 0.f;
     }
+#pragma unroll
+    for (int s = 0; s < KS; ++s)
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        mma_bf16_16816(s_acc[u], qa[s].x, qb[s].x, qa[s].y, qb[s].y, kk[u][s].x, kk[u][s].y);
+        mma_bf16_16816(s_odd[u], qa[s].z, qb[s].z, qa[s].w, qb[s].w, kk[u][s].z, kk[u][s].w);
+      }
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) s_acc[u][x] += s_odd[u][x];
     if (tb_next >= 0) load_k(tb_next);  // the key registers are free again: fetch the next tile's keys
     // ---- scale, mask, online softmax ----
     const int key0 = t * AM_TILE;
@@ -356,8 +374,9 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
   }
   __syncthreads();
   // thread -> (row, HD/8 contiguous dims)
-  constexpr int DPT = HD / 8;
-  const int row = tid >> 3, dbase = (tid & 7) * DPT;
+  constexpr int CPR = AM_THREADS / AM_ROWS;  // threads per row: 8 or 16
+  constexpr int DPT = HD / CPR;
+  const int row = tid / CPR, dbase = (tid % CPR) * DPT;
   float M = -INFINITY;
 #pragma unroll
   for (int w = 0; w < AM_WARPS; ++w) M = fmaxf(M, sm_m[w][row]);
@@ -397,7 +416,7 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
     __syncthreads();  // sm_o, sm_m, sm_l have been read by everyone
 #pragma unroll
     for (int d = 0; d < DPT; ++d) sm_o[0][row][dbase + d] = acc[d];
-    if ((tid & 7) == 0) {
+    if ((tid % CPR) == 0) {
       sm_m[0][row] = M;
       sm_l[0][row] = L;
     }
@@ -405,8 +424,9 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
     const int cs = p.nsplit;
     const unsigned rank = cluster_rank();
     const int slice = HD / cs;                      // dims this CTA finishes
-    const int per = AM_ROWS * slice / AM_THREADS;   // outputs a thread: 1..8, consecutive dims of one row
-    const int o0 = tid * per;
+    const int outputs = AM_ROWS * slice;
+    const int per = max(1, outputs / AM_THREADS);   // outputs a thread: 1..8, consecutive dims of one row
+    const int o0 = min(tid * per, outputs - per);   // (with more threads than outputs the last ones repeat)
     const int row2 = o0 / slice, d0 = (int)rank * slice + (o0 - row2 * slice);
     float ms[8], ls[8], Mg = -INFINITY;
 #pragma unroll
@@ -449,7 +469,7 @@ __global__ void __launch_bounds__(AM_THREADS) attn_mma_kernel(const AttnMmaParam
   float* so = p.scratch_o + ((item * p.nsplit + split) * AM_ROWS + row) * HD + dbase;
 #pragma unroll
   for (int d = 0; d < DPT; ++d) so[d] = acc[d];
-  if ((tid & 7) == 0) {
+  if ((tid % CPR) == 0) {
     float* sml = p.scratch_ml + ((item * p.nsplit + split) * AM_ROWS + row) * 2;
     sml[0] = M;
     sml[1] = L;
@@ -528,8 +548,8 @@ extern "C" int ll_attn_mma_ex(void* out, long out_stride, const void* q, long q_
                               const void* v_cache, const int* block_table, int bt_stride, const int* cu_q,
                               const int* ctx_len, const int* req_slot, int n_entries, int row_blocks, int nh, int nkv,
                               int hd, int page_size, int num_pages, int window, float scale, int nsplit,
-                              int all_single, int use_cluster, float* scratch, int* counters, int* status,
-                              cudaStream_t stream);
+                              int all_single, int use_cluster, int warps, float* scratch, int* counters,
+                              int* status, cudaStream_t stream);
 
 // q: query rows, head h of token t at q + t*q_stride + h*hd (bfloat16); out likewise.
 // cu_q / ctx_len / req_slot describe the entries; row_blocks = sum over entries of
@@ -542,20 +562,21 @@ extern "C" int ll_attn_mma(void* out, long out_stride, const void* q, long q_str
                            int hd, int page_size, int num_pages, int window, float scale, int nsplit, float* scratch,
                            int* counters, int* status, cudaStream_t stream) {
   return ll_attn_mma_ex(out, out_stride, q, q_stride, k_cache, v_cache, block_table, bt_stride, cu_q, ctx_len, req_slot,
-                        n_entries, row_blocks, nh, nkv, hd, page_size, num_pages, window, scale, nsplit, 0, 0, scratch,
+                        n_entries, row_blocks, nh, nkv, hd, page_size, num_pages, window, scale, nsplit, 0, 0, 4, scratch,
                         counters, status, stream);
 }
 
 // The same with a promise and a choice.  all_single != 0 says that every entry brings exactly one
 // token (a decode step), which saves the kernel the search for its entry.  use_cluster != 0 (nsplit
 // 2, 4 or 8) launches the splits of a row block as one thread-block cluster that merges them through
-// distributed shared memory; scratch and counters are then not used.
+// distributed shared memory; scratch and counters are then not used.  warps: 4 or 8 warps a CTA.
 extern "C" int ll_attn_mma_ex(void* out, long out_stride, const void* q, long q_stride, const void* k_cache,
                               const void* v_cache, const int* block_table, int bt_stride, const int* cu_q,
                               const int* ctx_len, const int* req_slot, int n_entries, int row_blocks, int nh, int nkv,
                               int hd, int page_size, int num_pages, int window, float scale, int nsplit,
-                              int all_single, int use_cluster, float* scratch, int* counters, int* status,
-                              cudaStream_t stream) {
+                              int all_single, int use_cluster, int warps, float* scratch, int* counters,
+                              int* status, cudaStream_t stream) {
+  if (warps != 4 && warps != 8) return (int)cudaErrorInvalidValue;
   if (row_blocks <= 0 || n_entries <= 0) return 0;
   if ((hd != 64 && hd != 128) || page_size % AM_TILE != 0 || nkv <= 0 || nh % nkv != 0 || nsplit < 1 ||
       nsplit > 65535 || nkv > 65535)
@@ -592,9 +613,16 @@ extern "C" int ll_attn_mma_ex(void* out, long out_stride, const void* q, long q_
   if (nsplit > 1 && !use_cluster && (scratch == nullptr || counters == nullptr)) return (int)cudaErrorInvalidValue;
   dim3 grid(row_blocks, nkv, nsplit);
   const int cz = use_cluster ? nsplit : 1;
-  if (hd == 64)
-    ll_launch_cluster(attn_mma_kernel<64>, grid, dim3(AM_THREADS), 0, stream, cz, p);
-  else
-    ll_launch_cluster(attn_mma_kernel<128>, grid, dim3(AM_THREADS), 0, stream, cz, p);
+  const size_t smem = sizeof(float) * ((size_t)warps * AM_ROWS * (hd + 4) + 2 * warps * AM_ROWS);
+  if (hd == 64 && warps == 4) {
+    ll_launch_cluster(attn_mma_kernel<64, 4>, grid, dim3(128), smem, stream, cz, p);
+  } else if (hd == 64) {
+    ll_launch_cluster(attn_mma_kernel<64, 8>, grid, dim3(256), smem, stream, cz, p);
+  } else if (warps == 4) {
+    ll_launch_cluster(attn_mma_kernel<128, 4>, grid, dim3(128), smem, stream, cz, p);
+  } else {
+    cudaFuncSetAttribute(attn_mma_kernel<128, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ll_launch_cluster(attn_mma_kernel<128, 8>, grid, dim3(256), smem, stream, cz, p);
+  }
   return LL_LAUNCH_RESULT();
 }

@@ -210,7 +210,7 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
              num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
              window: Optional[int], scale: float, nsplit: int, scratch: Optional[torch.Tensor],
              counters: Optional[torch.Tensor], status: Optional[torch.Tensor], all_single: bool = False,
-             cluster: bool = False) -> None:
+             cluster: bool = False, warps: int = 4) -> None:
     """Tensor-core paged attention (bfloat16) of the step's entries: decode and prompt portions.
 
     ``row_blocks`` is the sum over entries of ceil(q_len * group / 16).  With ``nsplit`` > 1 the
@@ -219,7 +219,8 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
     [row_blocks * num_kv_heads]) must be zero and are left zero.  ``all_single`` promises that
     every entry brings exactly one token (a decode step).  ``cluster`` (nsplit 2, 4 or 8) makes the
     splits of a row block one thread-block cluster that merges through distributed shared memory;
-    scratch and counters are then not needed.
+    scratch and counters are then not needed.  ``warps``: 4 or 8 warps a CTA (8 pays when the step
+    has few row blocks).
     """
     _need_cuda(out, q, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot, scratch, counters)
     for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot"),
@@ -248,8 +249,8 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
         _ptr(block_table), c_int(block_table.stride(0)), _ptr(cu_q), _ptr(ctx_len), _ptr(req_slot),
         c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
         c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), c_int(nsplit),
-        c_int(1 if all_single else 0), c_int(1 if cluster else 0), _ptr(scratch), _ptr(counters), _ptr(status),
-        _stream())
+        c_int(1 if all_single else 0), c_int(1 if cluster else 0), c_int(warps), _ptr(scratch), _ptr(counters),
+        _ptr(status), _stream())
 
 
 _sample_scratch = {}

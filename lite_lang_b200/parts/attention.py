@@ -145,18 +145,22 @@ class GQAttention(Mixer):
         # memory: no scratch memory, no counters
         single = step.max_q_len == 1 and group <= 16
         scratch = counters = None
-        plan = (blocks, nsplit, scratch, counters, single)
+        # 8 warps a CTA when the step has very few row blocks: more warps to hide instruction latency
+        # behind.  Not beyond half the SMs: 8-warp CTAs fit one an SM, and clusters of 8 of them then
+        # no longer find room in one wave (measured: batch 8 got slower, batch 1 faster)
+        warps = 8 if ctas * nsplit <= self.SM_COUNT // 2 and max_tiles >= 16 * nsplit else 4
+        plan = (blocks, nsplit, scratch, counters, single, warps)
         step.scratch[key] = plan
         return plan
 
     def attend(self, out, qkv, step, cache) -> None:
         """Attention of the step's tokens over the cache plane; picks the kernel by shape."""
         if ops.attn_mma_supported(qkv.dtype, self.head_dim, cache.page_size, qkv.stride(0)):
-            blocks, nsplit, scratch, counters, single = self._plan_mma(step, cache.page_size)
+            blocks, nsplit, scratch, counters, single, warps = self._plan_mma(step, cache.page_size)
             ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q, step.ctx_len,
                          step.req_slot, step.num_entries, blocks, self.num_heads, self.num_kv_heads, self.head_dim,
                          cache.page_size, self.window, self.scale, nsplit, scratch, counters, step.status, single,
-                         cluster=nsplit > 1)
+                         cluster=nsplit > 1, warps=warps)
             return
         ops.paged_attention_generic(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.token_req,
                                     step.req_slot, step.positions, qkv.shape[0], self.num_heads, self.num_kv_heads,

@@ -234,7 +234,7 @@ MMA_SHAPES = [
 ]
 
 
-def _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster=False):
+def _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster=False, warps=4):
     from lite_lang_b200 import ops
     d = dev()
     lens, q_lens = c["lens"], c["q_lens"]
@@ -254,7 +254,8 @@ def _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster=False):
     single = all(ql == 1 for ql in q_lens) and group <= 16     # the decode fast path when it applies
     for _ in range(2):          # twice: the counters must come back to zero
         ops.attn_mma(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], cu_q, ctx, c["req_slot"], len(lens),
-                     blocks, nh, nkv, hd, ps, window, hd ** -0.5, nsplit, scratch, counters, status, single, cluster)
+                     blocks, nh, nkv, hd, ps, window, hd ** -0.5, nsplit, scratch, counters, status, single, cluster,
+                     warps)
     assert status.item() == 0
     if counters is not None:
         assert int(counters.abs().sum()) == 0
@@ -269,6 +270,10 @@ def test_attn_mma(nh, nkv, hd, ps, lens, q_lens, window, nsplit):
     if nsplit in (2, 4, 8):     # the same splits as one thread-block cluster, merged through shared memory
         out = _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster=True)
         assert_close(out, c["ref"], torch.bfloat16, "attn_mma as clusters")
+        out = _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster=True, warps=8)
+        assert_close(out, c["ref"], torch.bfloat16, "attn_mma as clusters of 8-warp CTAs")
+    out = _run_mma(c, nh, nkv, hd, ps, window, nsplit, warps=8)
+    assert_close(out, c["ref"], torch.bfloat16, "attn_mma with 8 warps")
 
 
 @pytest.mark.parametrize("nsplit,cluster", [(1, False), (5, False), (8, True)])

@@ -1,0 +1,67 @@
+"""The engine at the layer sizes of the benchmark model (Qwen2-1.5B: hidden 1536, 12/2 heads of 128,
+intermediate 8960, vocabulary 151936, tied), with two layers, against the plain implementation (GPU).
+
+The tiny configurations never reach the kernels that serving uses at real sizes (the TMA weight-streaming
+product, the tensor-core attention with clusters, the wide lm_head); this test does, in bfloat16 and in
+float32, whole and decoded token by token.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, rel_err, random_tokens
+from plain import qwen2_plain as P
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(architectures=["Qwen2ForCausalLM"], hidden_size=1536, num_hidden_layers=2, num_attention_heads=12,
+           num_key_value_heads=2, intermediate_size=8960, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
+           tie_word_embeddings=True, max_position_embeddings=4096, use_sliding_window=False, torch_dtype="bfloat16")
+
+
+@pytest.fixture(scope="module")
+def model(tmp_path_factory):
+    from lite_lang_b200.config import config_from_dict
+    from lite_lang_b200.weights import write_random_model
+    folder = str(tmp_path_factory.mktemp("real_shape"))
+    write_random_model(folder, config_from_dict(CFG), seed=21, scales={"matrix": 0.03, "bias": 0.05, "norm": 0.05})
+    cfg, w = P.read_model_folder(folder)
+    toks = random_tokens(56, cfg["vocab_size"], 77)
+    ref = P.forward_logits(cfg, w, toks).numpy()
+    return folder, toks, ref
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_whole_then_token_by_token(model, dtype):
+    from lite_lang_b200.cache import CacheManager
+    from lite_lang_b200.config import load_config
+    from lite_lang_b200.engine.batch import StepEntry
+    from lite_lang_b200.engine.model import CausalLM
+    from lite_lang_b200.engine.runner import ModelRunner
+    from lite_lang_b200.weights import load_weights
+
+    folder, toks, ref = model
+    dev = torch.device("cuda:0")
+    m = CausalLM(load_config(folder).model_spec())
+    load_weights(m, folder, torch.bfloat16 if dtype == "bfloat16" else torch.float32, dev)
+    mgr = CacheManager(m.cache_groups, [32], 16, 8, 256)
+    runner = ModelRunner(m, mgr, dev, 128, cuda_graphs=True)
+    a, b = mgr.open(), mgr.open()
+    # request a: 40 tokens at once, then 16 one by one (captured steps), request b beside it from step 2 on
+    assert runner.reserve(a, 40)
+    lg = runner.step([StepEntry(a, toks[:40], tuple(range(40)))]).float().cpu().numpy()
+    assert rel_err(lg, ref[:40]) <= TOL[dtype]
+    for i in range(40, 56):
+        entries = [StepEntry(a, [toks[i]], (0,))]
+        want = [ref[i:i + 1]]
+        assert runner.reserve(a, 1)
+        if i >= 42:
+            j = i - 42
+            assert runner.reserve(b, 1)
+            entries.append(StepEntry(b, [toks[j]], (0,)))
+            want.append(ref[j:j + 1])
+        lg = runner.step(entries).float().cpu().numpy()
+        err = rel_err(lg, np.concatenate(want))
+        assert err <= TOL[dtype], (i, err)
+    runner.check_status()
+    assert runner.graph_replays == 16
