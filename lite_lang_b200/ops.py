@@ -253,6 +253,34 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
         _ptr(status), _stream())
 
 
+def attn_prefill(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
+                 num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 page_size: int, window: Optional[int], scale: float, status: Optional[torch.Tensor]) -> None:
+    """Tensor-core paged attention (bfloat16) for portions of prompts: 128 query rows a CTA share the
+    keys and values through shared memory.  ``row_blocks`` is the sum over the entries of
+    ceil(q_len * group / 128).  Same shapes as ``attn_mma``."""
+    _need_cuda(out, q, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot)
+    for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot")):
+        _i32(t, nm)
+    _need(attn_mma_supported(q.dtype, head_dim, page_size, q_stride),
+          f"attn_prefill takes bfloat16, head_dim 64 or 128 and pages of a multiple of 16 tokens, "
+          f"not {q.dtype}, {head_dim}, {page_size}")
+    _need(out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16,
+          "attn_prefill: dtypes differ")
+    _need(out.stride(1) == 1 and out.shape[1] == num_heads * head_dim and out.stride(0) % 8 == 0,
+          "attn_prefill: out")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache plane must be contiguous")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache plane shape")
+    _need(cu_q.numel() >= num_entries + 1 and ctx_len.numel() >= num_entries and req_slot.numel() >= num_entries,
+          "attn_prefill: entry arrays too short")
+    load_library("attn_mma").call(
+        "ll_attn_prefill", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), _ptr(k_cache), _ptr(v_cache),
+        _ptr(block_table), c_int(block_table.stride(0)), _ptr(cu_q), _ptr(ctx_len), _ptr(req_slot),
+        c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(status), _stream())
+
+
 _sample_scratch = {}
 
 

@@ -113,54 +113,54 @@ class GQAttention(Mixer):
         self.attend(attn, qkv, step, cache)
         return ops.linear(attn, self.w_o, partial_ok=True)
 
-    # scratch memory of the split kernel, shared by all layers (they run one after the other)
-    _workspaces: Dict[tuple, tuple] = {}
     SM_COUNT = 148
 
-    @classmethod
-    def _workspace(cls, key, floats: int, counters: int, device):
-        ws = cls._workspaces.get(key)
-        if ws is None or ws[0].numel() < floats or ws[1].numel() < counters:
-            ws = (torch.empty(max(floats, 1), dtype=torch.float32, device=device),
-                  torch.zeros(max(counters, 1), dtype=torch.int32, device=device))
-            cls._workspaces[key] = ws
-        return ws
-
-    def _plan_mma(self, step, page_size):
-        """Row blocks, splits and scratch of the tensor-core kernel for this step (once per step)."""
-        key = ("attn_mma", self.num_heads, self.num_kv_heads, self.head_dim, self.window)
-        plan = step.scratch.get(key)
-        if plan is not None:
-            return plan
+    def _plan_mma(self, step, entries, max_kv_len):
+        """Row blocks, splits and warps of the decode kernel for ``entries`` single-token entries."""
         group = self.num_heads // self.num_kv_heads
-        blocks = sum((len(e.tokens) * group + 15) // 16 for e in step.entries)
-        blocks += (step.num_entries - len(step.entries)) * ((group + 15) // 16)     # padding entries
+        blocks = entries * ((group + 15) // 16)
         ctas = blocks * self.num_kv_heads
-        max_tiles = (step.max_kv_len + 15) // 16
+        max_tiles = (max_kv_len + 15) // 16
         # one wave of CTAs at most, and at least 8 tiles (128 keys) a split: with less, merging the
-        # splits costs more than the split saves
+        # splits costs more than the split saves.  The splits of a row block form a thread-block cluster
+        # (2, 4 or 8 CTAs) and merge through distributed shared memory: no scratch memory, no counters.
         want = max(1, min((2 * self.SM_COUNT) // ctas, max(1, max_tiles // 8)))
         nsplit = 8 if want >= 8 else 4 if want >= 4 else 2 if want >= 2 else 1
-        # the splits of a row block form a thread-block cluster and merge through distributed shared
-        # memory: no scratch memory, no counters
-        single = step.max_q_len == 1 and group <= 16
-        scratch = counters = None
         # 8 warps a CTA when the step has very few row blocks: more warps to hide instruction latency
         # behind.  Not beyond half the SMs: 8-warp CTAs fit one an SM, and clusters of 8 of them then
         # no longer find room in one wave (measured: batch 8 got slower, batch 1 faster)
         warps = 8 if ctas * nsplit <= self.SM_COUNT // 2 and max_tiles >= 16 * nsplit else 4
-        plan = (blocks, nsplit, scratch, counters, single, warps)
-        step.scratch[key] = plan
-        return plan
+        return blocks, nsplit, group <= 16, warps
 
     def attend(self, out, qkv, step, cache) -> None:
-        """Attention of the step's tokens over the cache plane; picks the kernel by shape."""
+        """Attention of the step's tokens over the cache plane; picks the kernels by shape.
+
+        Single-token entries come first in a step: they go to the decode kernel (keys split over a
+        cluster of CTAs), the portions of prompts after them to the prefill kernel (128 query rows a
+        CTA share the keys through shared memory)."""
         if ops.attn_mma_supported(qkv.dtype, self.head_dim, cache.page_size, qkv.stride(0)):
-            blocks, nsplit, scratch, counters, single, warps = self._plan_mma(step, cache.page_size)
-            ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q, step.ctx_len,
-                         step.req_slot, step.num_entries, blocks, self.num_heads, self.num_kv_heads, self.head_dim,
-                         cache.page_size, self.window, self.scale, nsplit, scratch, counters, step.status, single,
-                         cluster=nsplit > 1, warps=warps)
+            n_single = step.num_single
+            n_rest = step.num_entries - n_single
+            args = (self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, self.window, self.scale)
+            if n_single > 0:
+                key = ("attn_mma", self.num_heads, self.num_kv_heads, self.head_dim)
+                plan = step.scratch.get(key)
+                if plan is None:
+                    plan = step.scratch[key] = self._plan_mma(step, n_single, step.max_kv_len)
+                blocks, nsplit, single, warps = plan
+                ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q, step.ctx_len,
+                             step.req_slot, n_single, blocks, *args, nsplit, None, None, step.status,
+                             all_single=single, cluster=nsplit > 1, warps=warps)
+            if n_rest > 0:
+                key = ("attn_prefill", self.num_heads, self.num_kv_heads)
+                blocks = step.scratch.get(key)
+                if blocks is None:
+                    group = self.num_heads // self.num_kv_heads
+                    blocks = sum((len(e.tokens) * group + 127) // 128 for e in step.entries[n_single:])
+                    step.scratch[key] = blocks
+                ops.attn_prefill(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table,
+                                 step.cu_q[n_single:], step.ctx_len[n_single:], step.req_slot[n_single:], n_rest,
+                                 blocks, *args, step.status)
             return
         ops.paged_attention_generic(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.token_req,
                                     step.req_slot, step.positions, qkv.shape[0], self.num_heads, self.num_kv_heads,

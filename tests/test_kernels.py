@@ -276,6 +276,64 @@ def test_attn_mma(nh, nkv, hd, ps, lens, q_lens, window, nsplit):
     assert_close(out, c["ref"], torch.bfloat16, "attn_mma with 8 warps")
 
 
+PREFILL_SHAPES = [
+    # nh, nkv, hd, page, lens, q_lens, window
+    (12, 2, 128, 16, [300], [300], None),                       # a whole prompt, group 6
+    (12, 2, 128, 16, [700, 33, 1, 129], [150, 33, 1, 2], None),   # portions behind a context, short entries
+    (8, 2, 64, 16, [130, 64, 65, 17], [130, 1, 20, 17], None),
+    (8, 2, 64, 32, [300, 90], [37, 90], None),
+    (3, 1, 128, 64, [257], [100], None),
+    (40, 2, 64, 16, [99, 50], [7, 3], None),                    # group 20
+    (4, 4, 128, 16, [200, 77], [120, 1], 50),                   # window
+    (8, 2, 64, 16, [400], [400], 33),
+    (12, 2, 128, 16, [1500], [1500], None),                     # many stages, many row blocks
+]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,lens,q_lens,window", PREFILL_SHAPES)
+def test_attn_prefill(nh, nkv, hd, ps, lens, q_lens, window):
+    from lite_lang_b200 import ops
+    c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, lens, q_lens, window, seed=18)
+    d = dev()
+    group = nh // nkv
+    cu = [0]
+    for ql in q_lens:
+        cu.append(cu[-1] + ql)
+    cu_q = torch.tensor(cu, dtype=torch.int32, device=d)
+    ctx = torch.tensor([l - ql for l, ql in zip(lens, q_lens)], dtype=torch.int32, device=d)
+    blocks = sum((ql * group + 127) // 128 for ql in q_lens)
+    out = torch.full_like(c["q"], 3.0)
+    status = torch.zeros(1, dtype=torch.int32, device=d)
+    ops.attn_prefill(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], cu_q, ctx, c["req_slot"], len(lens),
+                     blocks, nh, nkv, hd, ps, window, hd ** -0.5, status)
+    assert status.item() == 0
+    assert_close(out, c["ref"], torch.bfloat16, "attn_prefill")
+
+
+@pytest.mark.parametrize("where", ["first", "stage_edge", "last_of_stage", "window_in", "window_out"])
+def test_attn_prefill_finds_one_far_key(where):
+    from lite_lang_b200 import ops
+    nh, nkv, hd, ps, L, window = 12, 2, 128, 16, 1000, None
+    if where == "first":
+        peak = lambda l: 0
+    elif where == "stage_edge":
+        peak = lambda l: 64 * 7
+    elif where == "last_of_stage":
+        peak = lambda l: 64 * 7 + 63
+    else:
+        window = 300
+        peak = (lambda l: l - 300) if where == "window_in" else (lambda l: l - 301)
+    c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, [L], [40], window, seed=19, peak=peak)
+    d = dev()
+    cu_q = torch.tensor([0, 40], dtype=torch.int32, device=d)
+    ctx = torch.tensor([L - 40], dtype=torch.int32, device=d)
+    out = torch.full_like(c["q"], 3.0)
+    ops.attn_prefill(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], cu_q, ctx, c["req_slot"], 1,
+                     (40 * 6 + 127) // 128, nh, nkv, hd, ps, window, hd ** -0.5, None)
+    assert_close(out, c["ref"], torch.bfloat16, where)
+    assert (float(c["ref"][-1].mean()) > 4.5) == (where != "window_out")
+
+
 @pytest.mark.parametrize("nsplit,cluster", [(1, False), (5, False), (8, True)])
 @pytest.mark.parametrize("where", ["first", "page_edge", "last_of_page", "window_in", "window_out"])
 def test_attn_mma_finds_one_far_key(where, nsplit, cluster):
