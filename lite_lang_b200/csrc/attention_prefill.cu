@@ -7,8 +7,10 @@
 // head's group) pair, token-major, as in the decode kernel); every warp owns 16 of them.  The CTA walks
 // the keys in stages of 64: all threads copy the stage's keys and values from the pages into shared
 // memory with cp.async (double buffered, zero-filled beyond the request's length), and each warp takes
-// its MMA operands from there, so a key is fetched once per 128 rows.  A warp skips 16-key pieces that
-// lie entirely after its rows' positions (causal) or before their window.
+// its MMA operands from there, so a key is fetched once per 128 rows.  A warp works on 32 keys at a time (four
+// independent score tiles in flight, one softmax update per 32 keys) and skips 32-key pieces that lie
+// entirely after its rows' positions (causal) or before their window.  (64-row CTAs, two an SM, were
+// tried against the causal tail and were slower.)
 //
 // Shared-memory layout: row = key, 16-byte chunk q of a row stored at chunk q ^ (4 * (key & 1)) for
 // keys and q ^ (key & 6) for values, which makes the 16-byte reads of the two fragment patterns
@@ -22,7 +24,7 @@
 
 #define AP_WARPS 8
 #define AP_THREADS (AP_WARPS * 32)
-#define AP_ROWS 128
+#define AP_ROWS (16 * AP_WARPS)
 #define AP_TK 64
 
 struct AttnPrefillParams {
@@ -199,32 +201,32 @@ __global__ void __launch_bounds__(AP_THREADS) attn_prefill_kernel(const AttnPref
     __syncthreads();
     if (warp_active) {
 #pragma unroll 1
-      for (int sub = 0; sub < AP_TK / 16; ++sub) {
-        const int key0 = T * AP_TK + 16 * sub;
-        if (key0 > w_hi || key0 + 15 < w_lo) continue;  // nothing of this piece is visible to the warp's rows
-        const unsigned kt = k_base + buf * TILE_BYTES + (16 * sub) * ROW_BYTES;
-        const unsigned vt = v_base + buf * TILE_BYTES + (16 * sub) * ROW_BYTES;
-        // ---- S = Q K^T ----
-        float s_acc[2][4], s_odd[2][4];
+      for (int sub = 0; sub < AP_TK / 32; ++sub) {
+        const int key0 = T * AP_TK + 32 * sub;
+        if (key0 > w_hi || key0 + 31 < w_lo) continue;  // nothing of this piece is visible to the warp's rows
+        const unsigned kt = k_base + buf * TILE_BYTES + (32 * sub) * ROW_BYTES;
+        const unsigned vt = v_base + buf * TILE_BYTES + (32 * sub) * ROW_BYTES;
+        // ---- S = Q K^T for 32 keys: four column tiles, two accumulation chains each ----
+        float s_acc[4][4], s_odd[4][4];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < 4; ++u) {
           s_acc[u][0] = s_acc[u][1] = s_acc[u][2] = s_acc[u][3] = 0.f;
           s_odd[u][0] = s_odd[u][1] = s_odd[u][2] = s_odd[u][3] = 0.f;
         }
 #pragma unroll
         for (int s = 0; s < KS; ++s)
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int key = 8 * u + g;   // row inside the 16-key piece; 16 * sub is even, so key & 1 == g & 1
+          for (int u = 0; u < 4; ++u) {
+            const int key = 8 * u + g;   // row inside the piece; 32 * sub and 8 u are even, so key & 1 == g & 1
             const uint4 kk = ap_lds16(kt + key * ROW_BYTES + (((4 * s + c) ^ ((g & 1) << 2)) << 4));
             ap_mma(s_acc[u], qa[s].x, qb[s].x, qa[s].y, qb[s].y, kk.x, kk.y);
             ap_mma(s_odd[u], qa[s].z, qb[s].z, qa[s].w, qb[s].w, kk.z, kk.w);
           }
         // ---- scale, mask, online softmax ----
-        const bool boundary = (key0 + 15 > w_pmin) || (key0 < w_lo_max);
+        const bool boundary = (key0 + 31 > w_pmin) || (key0 < w_lo_max);
         float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
+        for (int u = 0; u < 4; ++u)
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
             const int i = x >> 1;
@@ -248,7 +250,7 @@ __global__ void __launch_bounds__(AP_THREADS) attn_prefill_kernel(const AttnPref
         }
         float psum[2] = {0.f, 0.f};
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
+        for (int u = 0; u < 4; ++u)
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
             const int i = x >> 1;
@@ -258,37 +260,51 @@ __global__ void __launch_bounds__(AP_THREADS) attn_prefill_kernel(const AttnPref
           }
 #pragma unroll
         for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * alpha[i] + psum[i];
-        const unsigned pa0 = ap_pack(s_acc[0][0], s_acc[0][1]);
-        const unsigned pa1 = ap_pack(s_acc[0][2], s_acc[0][3]);
-        const unsigned pa2 = ap_pack(s_acc[1][0], s_acc[1][1]);
-        const unsigned pa3 = ap_pack(s_acc[1][2], s_acc[1][3]);
+        unsigned pa[2][4];  // P as the A operand of the two 16-key steps
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          pa[ks][0] = ap_pack(s_acc[2 * ks][0], s_acc[2 * ks][1]);
+          pa[ks][1] = ap_pack(s_acc[2 * ks][2], s_acc[2 * ks][3]);
+          pa[ks][2] = ap_pack(s_acc[2 * ks + 1][0], s_acc[2 * ks + 1][1]);
+          pa[ks][3] = ap_pack(s_acc[2 * ks + 1][2], s_acc[2 * ks + 1][3]);
+        }
         // ---- O = O * alpha + P V ----
-        const bool rescale = (alpha[0] != 1.f) || (alpha[1] != 1.f);
+        if ((alpha[0] != 1.f) || (alpha[1] != 1.f)) {
+#pragma unroll
+          for (int Tn = 0; Tn < NT; ++Tn) {
+            o_acc[Tn][0] *= alpha[0];
+            o_acc[Tn][1] *= alpha[0];
+            o_acc[Tn][2] *= alpha[1];
+            o_acc[Tn][3] *= alpha[1];
+          }
+        }
 #pragma unroll
         for (int h = 0; h < VS; ++h) {
-          // the four keys of this thread: 2c, 2c+1, 2c+8, 2c+9; for all of them key & 6 == (2c) & 6
+          // the keys of this thread in a 16-key step: 2c, 2c+1, 2c+8, 2c+9; for all of them key & 6 == (2c) & 6
           const unsigned chunk = (((unsigned)(8 * h + g)) ^ (unsigned)((2 * c) & 6)) << 4;
-          const uint4 v0 = ap_lds16(vt + (2 * c) * ROW_BYTES + chunk);
-          const uint4 v1 = ap_lds16(vt + (2 * c + 1) * ROW_BYTES + chunk);
-          const uint4 v2 = ap_lds16(vt + (2 * c + 8) * ROW_BYTES + chunk);
-          const uint4 v3 = ap_lds16(vt + (2 * c + 9) * ROW_BYTES + chunk);
-          const unsigned* w0 = reinterpret_cast<const unsigned*>(&v0);
-          const unsigned* w1 = reinterpret_cast<const unsigned*>(&v1);
-          const unsigned* w2 = reinterpret_cast<const unsigned*>(&v2);
-          const unsigned* w3 = reinterpret_cast<const unsigned*>(&v3);
+          uint4 vv[2][4];
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            const unsigned vk = vt + (16 * ks) * ROW_BYTES + chunk;
+            vv[ks][0] = ap_lds16(vk + (2 * c) * ROW_BYTES);
+            vv[ks][1] = ap_lds16(vk + (2 * c + 1) * ROW_BYTES);
+            vv[ks][2] = ap_lds16(vk + (2 * c + 8) * ROW_BYTES);
+            vv[ks][3] = ap_lds16(vk + (2 * c + 9) * ROW_BYTES);
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int Tn = h * 8 + j;
             const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;
-            const unsigned b0 = __byte_perm(w0[j >> 1], w1[j >> 1], sel);
-            const unsigned b1 = __byte_perm(w2[j >> 1], w3[j >> 1], sel);
-            if (rescale) {
-              o_acc[Tn][0] *= alpha[0];
-              o_acc[Tn][1] *= alpha[0];
-              o_acc[Tn][2] *= alpha[1];
-              o_acc[Tn][3] *= alpha[1];
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+              const unsigned* w0 = reinterpret_cast<const unsigned*>(&vv[ks][0]);
+              const unsigned* w1 = reinterpret_cast<const unsigned*>(&vv[ks][1]);
+              const unsigned* w2 = reinterpret_cast<const unsigned*>(&vv[ks][2]);
+              const unsigned* w3 = reinterpret_cast<const unsigned*>(&vv[ks][3]);
+              const unsigned b0 = __byte_perm(w0[j >> 1], w1[j >> 1], sel);
+              const unsigned b1 = __byte_perm(w2[j >> 1], w3[j >> 1], sel);
+              ap_mma(o_acc[Tn], pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b0, b1);
             }
-            ap_mma(o_acc[Tn], pa0, pa1, pa2, pa3, b0, b1);
           }
         }
       }
