@@ -69,6 +69,86 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ out, T* __restrict__ residual
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(row[i] * inv * w[i]);
 }
 
+// bfloat16 rows whose length is a multiple of 8 and at most 8 * 1024: every thread keeps 8 values in
+// registers (one 16-byte load per operand), so the row is read once and nothing goes through shared
+// memory.  Same arithmetic and the same roundings as the generic kernel.
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_bf16x8_kernel(bf16* __restrict__ out, bf16* __restrict__ residual, const bf16* __restrict__ delta,
+                          const float* __restrict__ partial, int parts, long part_stride,
+                          const float* __restrict__ w, float eps, int hidden, const int* __restrict__ rows,
+                          int write_residual) {
+  __shared__ float scratch[32];
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
+  const int i_out = blockIdx.x;
+  const int r = rows ? rows[i_out] : i_out;
+  const int i0 = threadIdx.x * 8;
+  const bool active = i0 < hidden;
+  float v[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = 0.f;
+  if (active) {
+    bf16* res = residual + (size_t)r * hidden + i0;
+    const uint4 rv = *reinterpret_cast<const uint4*>(res);
+    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(r2[k]);
+      v[2 * k] = f.x;
+      v[2 * k + 1] = f.y;
+    }
+    bool changed = false;
+    if (delta) {
+      const uint4 dv = *reinterpret_cast<const uint4*>(delta + (size_t)r * hidden + i0);
+      const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(d2[k]);
+        v[2 * k] = round_to<bf16>(v[2 * k] + f.x);
+        v[2 * k + 1] = round_to<bf16>(v[2 * k + 1] + f.y);
+      }
+      changed = true;
+    } else if (partial) {
+      float d[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) d[k] = 0.f;
+      const float* par = partial + (size_t)r * hidden + i0;
+      for (int q = 0; q < parts; ++q) {
+        const float4 a = *reinterpret_cast<const float4*>(par + (size_t)q * part_stride);
+        const float4 b = *reinterpret_cast<const float4*>(par + (size_t)q * part_stride + 4);
+        d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
+        d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = round_to<bf16>(v[k] + round_to<bf16>(d[k]));
+      changed = true;
+    }
+    if (changed && write_residual) {
+      uint4 ov;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) o2[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+      *reinterpret_cast<uint4*>(res) = ov;
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) ss += v[k] * v[k];
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  if (active) {
+    const float4 wa = *reinterpret_cast<const float4*>(w + i0);
+    const float4 wb = *reinterpret_cast<const float4*>(w + i0 + 4);
+    const float ww[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      o2[k] = __floats2bfloat162_rn(v[2 * k] * inv * ww[2 * k], v[2 * k + 1] * inv * ww[2 * k + 1]);
+    *reinterpret_cast<uint4*>(out + (size_t)i_out * hidden + i0) = ov;
+  }
+}
+
 static int norm_threads(int hidden) {
   int t = 32;
   while (t < 512 && t * 4 < hidden) t <<= 1;
@@ -97,6 +177,12 @@ extern "C" int ll_add_rmsnorm(int dtype, void* out, void* residual, const void* 
                               int parts, long part_stride, const float* w, float eps, int n_out, int hidden,
                               const int* rows, int write_residual, cudaStream_t stream) {
   if (n_out <= 0) return 0;
+  if (dtype == LL_DTYPE_BF16 && (hidden % 8) == 0 && hidden <= 8 * 1024 && (part_stride % 4) == 0) {
+    const int threads = ((hidden / 8 + 31) / 32) * 32;
+    ll_launch(add_rmsnorm_bf16x8_kernel, dim3(n_out), dim3(threads), 0, stream, (bf16*)out, (bf16*)residual,
+              (const bf16*)delta, partial, parts, part_stride, w, eps, hidden, rows, write_residual);
+    return LL_LAUNCH_RESULT();
+  }
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   LL_DISPATCH_DTYPE(dtype, {

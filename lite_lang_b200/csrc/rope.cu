@@ -103,6 +103,95 @@ __global__ void bias_rope_store_kernel(T* __restrict__ qkv, long qkv_stride, con
   }
 }
 
+// bfloat16, whole-head rotation (rot_dim == hd), hd a multiple of 16: a thread takes 8 consecutive
+// values of the first half of a head and their 8 partners from the second half (16-byte accesses), or
+// 8 values of a v head.  Same arithmetic and roundings as the generic kernel.
+__global__ void __launch_bounds__(256)
+bias_rope_store_bf16x8_kernel(bf16* __restrict__ qkv, long qkv_stride, const float* __restrict__ bias,
+                              const int* __restrict__ positions, const float* __restrict__ cos_sin, int max_pos, int nh,
+                              int nkv, int hd, const int* __restrict__ slot_map, bf16* __restrict__ k_cache,
+                              bf16* __restrict__ v_cache, int page_size, long num_slots, int* status) {
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
+  const int t = blockIdx.x;
+  bf16* row = qkv + (size_t)t * qkv_stride;
+  int pos = positions[t];
+  if (pos < 0 || pos >= max_pos) {
+    if (threadIdx.x == 0) set_status(status, LL_ERR_POSITION_RANGE);
+    pos = 0;
+  }
+  long slot = slot_map ? (long)slot_map[t] : -1;
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) set_status(status, LL_ERR_SLOT_RANGE);
+    slot = -1;
+  }
+  const long page = slot >= 0 ? slot / page_size : 0;
+  const int off = slot >= 0 ? (int)(slot - page * page_size) : 0;
+  const int half = hd >> 1;
+  const int cph = half / 8;                   // 8-value pieces in half a head
+  const float* cs = cos_sin + (size_t)pos * hd;
+  const int n_rot = (nh + nkv) * cph, n_v = nkv * (hd / 8);
+  for (int w = threadIdx.x; w < n_rot + n_v; w += blockDim.x) {
+    if (w < n_rot) {
+      const int h = w / cph, i0 = (w - h * cph) * 8;
+      bf16* head = row + (size_t)h * hd;
+      const uint4 a = *reinterpret_cast<const uint4*>(head + i0);
+      const uint4 b = *reinterpret_cast<const uint4*>(head + i0 + half);
+      const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+      float x0[8], x1[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 fa = __bfloat1622float2(a2[k]), fb = __bfloat1622float2(b2[k]);
+        x0[2 * k] = fa.x; x0[2 * k + 1] = fa.y;
+        x1[2 * k] = fb.x; x1[2 * k + 1] = fb.y;
+      }
+      if (bias) {
+        const float* bb = bias + (size_t)h * hd + i0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          x0[k] += bb[k];
+          x1[k] += bb[k + half];
+        }
+      }
+      uint4 o0, o1;
+      __nv_bfloat162* p0 = reinterpret_cast<__nv_bfloat162*>(&o0);
+      __nv_bfloat162* p1 = reinterpret_cast<__nv_bfloat162*>(&o1);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float c0 = cs[i0 + 2 * k], c1 = cs[i0 + 2 * k + 1];
+        const float s0 = cs[half + i0 + 2 * k], s1 = cs[half + i0 + 2 * k + 1];
+        p0[k] = __floats2bfloat162_rn(x0[2 * k] * c0 - x1[2 * k] * s0, x0[2 * k + 1] * c1 - x1[2 * k + 1] * s1);
+        p1[k] = __floats2bfloat162_rn(x0[2 * k] * s0 + x1[2 * k] * c0, x0[2 * k + 1] * s1 + x1[2 * k + 1] * c1);
+      }
+      *reinterpret_cast<uint4*>(head + i0) = o0;
+      *reinterpret_cast<uint4*>(head + i0 + half) = o1;
+      if (h >= nh && slot >= 0) {
+        bf16* dst = k_cache + (((size_t)page * nkv + (h - nh)) * page_size + off) * hd;
+        *reinterpret_cast<uint4*>(dst + i0) = o0;
+        *reinterpret_cast<uint4*>(dst + i0 + half) = o1;
+      }
+    } else {
+      const int wv = w - n_rot;
+      const int h = wv / (hd / 8), j0 = (wv - h * (hd / 8)) * 8;
+      bf16* head = row + (size_t)(nh + nkv + h) * hd;
+      uint4 a = *reinterpret_cast<const uint4*>(head + j0);
+      if (bias) {
+        __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&a);
+        const float* bb = bias + (size_t)(nh + nkv + h) * hd + j0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(a2[k]);
+          a2[k] = __floats2bfloat162_rn(f.x + bb[2 * k], f.y + bb[2 * k + 1]);
+        }
+        *reinterpret_cast<uint4*>(head + j0) = a;
+      }
+      if (slot >= 0)
+        *reinterpret_cast<uint4*>(v_cache + (((size_t)page * nkv + h) * page_size + off) * hd + j0) = a;
+    }
+  }
+}
+
 // qkv: [num_tokens, (nh + 2 nkv) * hd] with row stride qkv_stride (elements).
 // bias: float32 [(nh + 2 nkv) * hd] or null.  positions: int32 [num_tokens].
 // cos_sin: float32 [max_pos, rot_dim] or null (no rotation).
@@ -114,6 +203,15 @@ extern "C" int ll_bias_rope_store(int dtype, void* qkv, long qkv_stride, const f
   if (num_tokens <= 0) return 0;
   const int do_rope = cos_sin != nullptr;
   if (do_rope && (rot_dim <= 0 || (rot_dim & 1) || rot_dim > hd)) return (int)cudaErrorInvalidValue;
+  if (dtype == LL_DTYPE_BF16 && do_rope && rot_dim == hd && (hd % 16) == 0 && (qkv_stride % 8) == 0 &&
+      positions != nullptr) {
+    const int work = (nh + nkv) * (hd / 16) + nkv * (hd / 8);
+    const int threads = work >= 256 ? 256 : ((work + 31) / 32) * 32;
+    ll_launch(bias_rope_store_bf16x8_kernel, dim3(num_tokens), dim3(threads), 0, stream, (bf16*)qkv, qkv_stride, bias,
+              positions, cos_sin, max_pos, nh, nkv, hd, slot_map, (bf16*)k_cache, (bf16*)v_cache, page_size,
+              num_slots, status);
+    return LL_LAUNCH_RESULT();
+  }
   if (!do_rope) rot_dim = 0;
   const int write_q = (bias != nullptr) || do_rope;
   LL_DISPATCH_DTYPE(dtype, ll_launch(bias_rope_store_kernel<T>, dim3(num_tokens), dim3(256), 0, stream, (T*)qkv,
