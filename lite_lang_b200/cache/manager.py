@@ -113,6 +113,7 @@ class CacheManager:
             g: np.full((self.max_requests, self.max_blocks), -1, dtype=np.int32) for g in self.paged_ids
         }
         self.dirty_rows: Dict[int, Set[int]] = {g: set() for g in self.paged_ids}
+        self.lengths = np.zeros(self.max_requests, dtype=np.int32)   # tokens cached per slot (0 if closed)
         self._free_slots: List[int] = list(range(self.max_requests - 1, -1, -1))
         self._requests: Dict[int, _Request] = {}
         self.opened_slots: List[int] = []     # slots opened since the storage last looked (state to be zeroed)
@@ -145,6 +146,7 @@ class CacheManager:
                 self.block_tables[g][slot, :n] = -1
                 self.dirty_rows[g].add(slot)
         del self._requests[slot]
+        self.lengths[slot] = 0
         self._free_slots.append(slot)
 
     def _get(self, slot: int) -> _Request:
@@ -206,6 +208,7 @@ class CacheManager:
                 raise CacheError(f"slot {slot}: {new_length} tokens were written but pages were reserved for "
                                  f"{len(req.pages[g]) * self.page_size}")
         req.length = new_length
+        self.lengths[slot] = new_length
         for g in self.paged_ids:
             w = self.groups[g].window
             if w is None:

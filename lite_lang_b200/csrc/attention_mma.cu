@@ -55,7 +55,7 @@ struct AttnMmaParams {
   float scale_log2;  // softmax scale times log2(e)
   int nsplit;
   int all_single;  // every entry brings one token and a group fits a row block: entry = blockIdx.x
-  int cluster;     // the nsplit CTAs of a (row block, kv head) are one thread-block cluster (nsplit 2, 4 or 8)
+  int cluster;     // the nsplit CTAs of a (row block, kv head) are one thread-block cluster (nsplit 2, 4, 8 or 16)
   float* scratch_o;   // [row blocks * nkv * nsplit][16][HD]
   float* scratch_ml;  // [row blocks * nkv * nsplit][16][2]
   int* counters;      // [row blocks * nkv], zero before and after every launch
@@ -428,9 +428,9 @@ __global__ void __launch_bounds__(NW * 32) attn_mma_kernel(const AttnMmaParams p
     const int per = max(1, outputs / AM_THREADS);   // outputs a thread: 1..8, consecutive dims of one row
     const int o0 = min(tid * per, outputs - per);   // (with more threads than outputs the last ones repeat)
     const int row2 = o0 / slice, d0 = (int)rank * slice + (o0 - row2 * slice);
-    float ms[8], ls[8], Mg = -INFINITY;
+    float ms[16], ls[16], Mg = -INFINITY;
 #pragma unroll
-    for (int sI = 0; sI < 8; ++sI) {
+    for (int sI = 0; sI < 16; ++sI) {
       if (sI < cs) {
         ms[sI] = ld_peer(&sm_m[0][row2], sI);
         ls[sI] = ld_peer(&sm_l[0][row2], sI);
@@ -442,7 +442,7 @@ __global__ void __launch_bounds__(NW * 32) attn_mma_kernel(const AttnMmaParams p
 #pragma unroll
     for (int k = 0; k < 8; ++k) fin[k] = 0.f;
 #pragma unroll
-    for (int sI = 0; sI < 8; ++sI) {
+    for (int sI = 0; sI < 16; ++sI) {
       if (sI < cs) {
         const float ws = fast_exp2(ms[sI] - Mgs);
         Lg += ls[sI] * ws;
@@ -568,7 +568,7 @@ extern "C" int ll_attn_mma(void* out, long out_stride, const void* q, long q_str
 
 // The same with a promise and a choice.  all_single != 0 says that every entry brings exactly one
 // token (a decode step), which saves the kernel the search for its entry.  use_cluster != 0 (nsplit
-// 2, 4 or 8) launches the splits of a row block as one thread-block cluster that merges them through
+// 2, 4, 8 or 16) launches the splits of a row block as one thread-block cluster that merges them through
 // distributed shared memory; scratch and counters are then not used.  warps: 4 or 8 warps a CTA.
 extern "C" int ll_attn_mma_ex(void* out, long out_stride, const void* q, long q_stride, const void* k_cache,
                               const void* v_cache, const int* block_table, int bt_stride, const int* cu_q,
@@ -604,7 +604,7 @@ extern "C" int ll_attn_mma_ex(void* out, long out_stride, const void* q, long q_
   p.scale_log2 = scale * 1.4426950408889634f;
   p.nsplit = nsplit;
   p.all_single = (row_blocks == n_entries && p.group <= AM_ROWS && all_single) ? 1 : 0;
-  if (use_cluster && !(nsplit == 2 || nsplit == 4 || nsplit == 8)) return (int)cudaErrorInvalidValue;
+  if (use_cluster && !(nsplit == 2 || nsplit == 4 || nsplit == 8 || nsplit == 16)) return (int)cudaErrorInvalidValue;
   p.cluster = use_cluster ? 1 : 0;
   p.scratch_o = scratch;
   p.scratch_ml = scratch ? scratch + (long)row_blocks * nkv * nsplit * AM_ROWS * hd : nullptr;
@@ -614,6 +614,12 @@ extern "C" int ll_attn_mma_ex(void* out, long out_stride, const void* q, long q_
   dim3 grid(row_blocks, nkv, nsplit);
   const int cz = use_cluster ? nsplit : 1;
   const size_t smem = sizeof(float) * ((size_t)warps * AM_ROWS * (hd + 4) + 2 * warps * AM_ROWS);
+  if (cz > 8) {  // clusters of 16 are beyond the portable size: allowed per kernel
+    if (hd == 64 && warps == 4) cudaFuncSetAttribute(attn_mma_kernel<64, 4>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (hd == 64 && warps == 8) cudaFuncSetAttribute(attn_mma_kernel<64, 8>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (hd == 128 && warps == 4) cudaFuncSetAttribute(attn_mma_kernel<128, 4>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (hd == 128 && warps == 8) cudaFuncSetAttribute(attn_mma_kernel<128, 8>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  }
   if (hd == 64 && warps == 4) {
     ll_launch_cluster(attn_mma_kernel<64, 4>, grid, dim3(128), smem, stream, cz, p);
   } else if (hd == 64) {

@@ -135,7 +135,28 @@ class BatchBuilder:
         t = 0
         max_q, max_kv = 1, 1
         starts = []
-        for i, e in enumerate(arranged):
+        if num_single == n_real and n_real > 0:
+            # a decode step: every entry brings one token; filled with array operations, no loop
+            slots = np.fromiter((e.slot for e in arranged), dtype=np.int64, count=n_real)
+            ctx = m.lengths[slots]
+            cu_q[:n_real] = np.arange(n_real, dtype=np.int32)
+            ctx_len[:n_real] = ctx
+            req_slot[:n_real] = slots
+            token_ids[:n_real] = np.fromiter((e.tokens[0] for e in arranged), dtype=np.int32, count=n_real)
+            positions[:n_real] = ctx
+            token_req[:n_real] = cu_q[:n_real]
+            for g in m.paged_ids:
+                pages = m.block_tables[g][slots, ctx // ps]
+                if (pages < 0).any():
+                    raise RuntimeError("a decode step without reserved pages")
+                slot_maps[g][:n_real] = pages * ps + ctx % ps
+            starts = list(range(n_real))
+            t = n_real
+            max_kv = int(ctx.max()) + 1
+            arranged_loop = ()
+        else:
+            arranged_loop = arranged
+        for i, e in enumerate(arranged_loop):
             q = len(e.tokens)
             if q == 0:
                 raise ValueError("an entry without tokens")

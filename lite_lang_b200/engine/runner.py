@@ -84,12 +84,7 @@ class ModelRunner:
         nothing is wanted).  The tensor is valid until the next step."""
         entries = list(entries)
         m = self.manager
-        for e in entries:
-            c = m.length(e.slot)
-            for g in m.paged_ids:
-                if (c + len(e.tokens) + m.page_size - 1) // m.page_size > len(m._requests[e.slot].pages[g]):
-                    raise RuntimeError(f"step without reserved pages for slot {e.slot}")
-        self.storage.sync()
+        self.storage.sync()      # (the batch builder refuses tokens whose pages were not reserved)
         single = all(len(e.tokens) == 1 for e in entries)
         if single and self.use_graphs and allow_graph:
             logits = self._step_graph(entries)

@@ -238,7 +238,7 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
     _need(cu_q.numel() >= num_entries + 1 and ctx_len.numel() >= num_entries and req_slot.numel() >= num_entries,
           "attn_mma: entry arrays too short")
     if cluster:
-        _need(nsplit in (2, 4, 8), "attn_mma: a cluster has 2, 4 or 8 splits")
+        _need(nsplit in (2, 4, 8, 16), "attn_mma: a cluster has 2, 4, 8 or 16 splits")
     if nsplit > 1 and not cluster:
         _need(scratch is not None and counters is not None, "attn_mma: splits need scratch and counters")
         _need(scratch.numel() >= attn_mma_scratch_floats(row_blocks, num_kv_heads, nsplit, head_dim),

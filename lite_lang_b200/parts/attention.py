@@ -123,8 +123,10 @@ class GQAttention(Mixer):
         max_tiles = (max_kv_len + 15) // 16
         # one wave of CTAs at most, and at least 8 tiles (128 keys) a split: with less, merging the
         # splits costs more than the split saves.  The splits of a row block form a thread-block cluster
-        # (2, 4 or 8 CTAs) and merge through distributed shared memory: no scratch memory, no counters.
+        # (2, 4, 8 or 16 CTAs) and merge through distributed shared memory: no scratch memory, no counters.
         want = max(1, min((2 * self.SM_COUNT) // ctas, max(1, max_tiles // 8)))
+        # (clusters of 16, the non-portable size, were measured slower than 8: placement costs more
+        # than the shorter key ranges save)
         nsplit = 8 if want >= 8 else 4 if want >= 4 else 2 if want >= 2 else 1
         # 8 warps a CTA when the step has very few row blocks: more warps to hide instruction latency
         # behind.  Not beyond half the SMs: 8-warp CTAs fit one an SM, and clusters of 8 of them then

@@ -228,7 +228,9 @@ MMA_SHAPES = [
     (40, 2, 64, 16, [99, 50], [2, 1], None, 4),                  # group 20: a token's heads span row blocks
     (4, 4, 128, 16, [200, 77], [5, 1], 50, 2),                   # window
     (8, 2, 64, 16, [160], [160], 33, 1),                         # window inside a whole prompt
-    (12, 2, 128, 16, [2100, 33, 1, 640], [1, 1, 1, 1], None, 8),  # decode, splits of 2, 4, 8 also as clusters
+    (12, 2, 128, 16, [2100, 33, 1, 640], [1, 1, 1, 1], None, 8),  # decode, splits of 2, 4, 8, 16 also as clusters
+    (12, 2, 128, 16, [4000, 700], [1, 1], None, 16),
+    (8, 2, 64, 16, [3000], [1], None, 16),
     (8, 2, 64, 16, [500, 90], [1, 30], None, 4),
     (3, 1, 128, 32, [257, 300], [100, 1], 120, 2),
 ]
@@ -267,7 +269,7 @@ def test_attn_mma(nh, nkv, hd, ps, lens, q_lens, window, nsplit):
     c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, lens, q_lens, window, seed=15)
     out = _run_mma(c, nh, nkv, hd, ps, window, nsplit)
     assert_close(out, c["ref"], torch.bfloat16, "attn_mma")
-    if nsplit in (2, 4, 8):     # the same splits as one thread-block cluster, merged through shared memory
+    if nsplit in (2, 4, 8, 16):     # the same splits as one thread-block cluster, merged through shared memory
         out = _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster=True)
         assert_close(out, c["ref"], torch.bfloat16, "attn_mma as clusters")
         out = _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster=True, warps=8)
