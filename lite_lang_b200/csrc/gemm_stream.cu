@@ -350,6 +350,7 @@ static int gt_launch(const GtParams& p, const void* w, int sm_count, cudaStream_
   const size_t smem = 1024 + (size_t)S::STAGES * S::ROWS * S::KC * 2 + 2 * S::STAGES * 8 +
                       (MODE == GT_MODE_NARROW ? sizeof(float) * GT_CONSUMERS * 16 * 8 * MT : 0);
   cudaFuncSetAttribute(gemm_stream_kernel<MODE, MT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  // two CTAs an SM (one an SM, so that the next product's CTAs could move in early, was measured slower)
   const int grid = p.units < 2 * sm_count ? p.units : 2 * sm_count;
   ll_launch(gemm_stream_kernel<MODE, MT, OutT>, dim3(grid), dim3(GT_THREADS), smem, stream, p, map);
   return LL_LAUNCH_RESULT();
