@@ -241,6 +241,52 @@ def prefill_once(engine, repeats=3):
     return best
 
 
+def kernel_times(engine, batch, steps):
+    """Mean duration of every kernel of a decode step, measured while the step's graph replays."""
+    import collections
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from lite_lang_b200.engine.batch import StepEntry
+
+    m, runner = engine.manager, engine.runner
+    vocab = engine.model.spec.vocab_size
+    slots = []
+    for p in random_prompts(batch, PROMPT_LEN, vocab, 7):
+        s = m.open()
+        assert runner.reserve(s, PROMPT_LEN)
+        runner.step([StepEntry(s, p, ())])
+        slots.append(s)
+
+    def one(i):
+        for s in slots:
+            assert runner.reserve(s, 1)
+        logits = runner.step([StepEntry(s, [5 + i], (0,)) for s in slots])
+        engine.sampler.sample(logits, [0.0] * batch, [0.0] * batch)
+
+    for i in range(5):
+        one(i)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for i in range(steps):
+            one(5 + i)
+        torch.cuda.synchronize()
+    agg = collections.OrderedDict()
+    for e in prof.events():
+        if e.device_type == torch.autograd.DeviceType.CUDA:
+            a = agg.setdefault(e.name[:72], [0, 0.0])
+            a[0] += 1
+            a[1] += e.device_time
+    lines = [f"decode step of batch {batch}, mean over {steps} graph replays "
+             f"(LITE_LANG_B200_PDL={os.environ.get('LITE_LANG_B200_PDL', '1')}; with 1 kernels overlap and their "
+             "times include waiting for the kernel before)"]
+    for k, (n, t) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+        lines.append(f"{t / steps:9.1f} us/step {n / steps:6.1f} calls {t / n:8.2f} us each  {k}")
+    lines.append(f"sum {sum(v[1] for v in agg.values()) / steps:.1f} us/step")
+    for s in slots:
+        m.close(s)
+    return "\n".join(lines)
+
+
 def run_ours(args):
     import torch
     from lite_lang_b200.csrc import build as kbuild
@@ -257,6 +303,9 @@ def run_ours(args):
         ms, ctx = device_decode(engine, batch, args.steps, args.warmup)
         print(json.dumps({"only": "decode", "batch": batch, "layers": layers, "ms_per_step": round(ms, 4),
                           "mean_context": ctx}))
+        return 0
+    if args.only == "kernels":
+        print(kernel_times(engine, batch, max(4, min(args.steps, 20))))
         return 0
     if args.only == "prefill":
         ms = prefill_once(engine, repeats=max(1, args.steps))
@@ -335,8 +384,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (reported in config)")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
-                    help="a small case for profilers: only the decode steps or only the prefill; prints a short line")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "kernels"],
+                    help="a small case for profilers: only the decode steps or only the prefill (prints a short "
+                         "line), or 'kernels': the decode step's kernels timed inside its graph by torch.profiler")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not built (this engine has no multi-GPU path)")
