@@ -1,0 +1,405 @@
+// Decode attention on tensor cores, transposed: one new token per request, bfloat16.
+//
+// attention_mma.cu puts the (token, head) rows on the M side of mma.sync.m16n8k16; with one token a
+// request only `group` of its 16 rows carry a query head.  Here the product is transposed: the 16 keys
+// of a tile are the M side and the group's query heads (at most 8) the N side,
+//     S^T[16 keys x 8 heads] = K[16 x hd] Q^T[hd x 8],      O^T[hd x 8 heads] += V^T[hd x 16 keys] P^T[16 x 8],
+// which halves the MMAs, the accumulator registers and the softmax work per tile (8 columns instead of
+// 16 rows) and leaves room for three CTAs an SM.  P^T moves from the accumulator layout to the B-operand
+// layout with two movmatrix transposes.  Keys and values go straight from global memory into the MMA
+// registers with 16-byte loads, by the same freedom as in attention_mma.cu: the contraction index is
+// mapped to 8 contiguous head dimensions per thread (Q K^T), and the output rows of an MMA tile are mapped
+// so that a thread's eight values of a key row serve four tiles (P V; two keys are paired by a byte
+// permute).
+//
+// One CTA (4 warps) works on one (entry, kv head, split of the keys); its warps take the split's 16-key
+// tiles in turn and are merged through shared memory.  The splits of an (entry, kv head) are the CTAs of
+// one thread-block cluster (1, 2, 4 or 8) and merge through distributed shared memory: every CTA
+// finishes a slice of the head dimensions.  No scratch memory, no counters, nothing spins (the cluster
+// barrier is the hardware's; every CTA of a cluster reaches it, early exits are the same for all of them).
+//
+// Head sizes 64 and 128, groups of at most 8 query heads, pages of a multiple of 16 tokens.
+#include "common.cuh"
+
+#define AD_WARPS 4
+#define AD_THREADS 128
+#define AD_TILE 16
+#define AD_HEADS 8
+#define AD_BT_CACHE 256
+
+struct AttnDecodeParams {
+  const bf16* q;
+  long q_stride;
+  bf16* out;
+  long out_stride;
+  const bf16* k_cache;
+  const bf16* v_cache;
+  const int* block_table;
+  int bt_stride;
+  const int* ctx_len;
+  const int* req_slot;
+  int n_entries;
+  int nh, nkv, group;
+  int page_size, num_pages;
+  int window;
+  float scale_log2;
+  int nsplit;
+  int* status;
+};
+
+__device__ __forceinline__ void ad_mma(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                       unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ad_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ unsigned ad_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ uint4 ad_ldg16(const bf16* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// transpose of an 8x8 matrix of 16-bit values held one row-pair per thread
+__device__ __forceinline__ unsigned ad_movmatrix(unsigned x) {
+  unsigned y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ void ad_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned ad_cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float ad_ld_peer(const float* local, unsigned rank) {
+  unsigned la = (unsigned)__cvta_generic_to_shared(local), ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const AttnDecodeParams p) {
+  constexpr int KS = HD / 32;   // 16-byte loads per key row and thread for Q K^T
+  constexpr int VS = HD / 64;   // 16-byte loads per value row and thread
+  constexpr int MT = HD / 16;   // MMA row tiles of O^T
+  __shared__ float sm_o[AD_WARPS][AD_HEADS][HD + 4];
+  __shared__ float sm_m[AD_WARPS][AD_HEADS];
+  __shared__ float sm_l[AD_WARPS][AD_HEADS];
+  __shared__ int sm_bt[AD_BT_CACHE];
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const int e = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  if (e >= p.n_entries) return;
+  const int slot = p.req_slot[e];
+  const int ctx = p.ctx_len[e];
+  // ---- Q^T fragments: thread (g, c) holds head g, dims 32 s + 8 c .. + 7 ----
+  uint4 qf[KS];
+  {
+    const bool hv = g < p.group;
+    const bf16* qr = p.q + (size_t)e * p.q_stride + (size_t)(kvh * p.group + (hv ? g : 0)) * HD + 8 * c;
+#pragma unroll
+    for (int s = 0; s < KS; ++s) qf[s] = hv ? ad_ldg16(qr + 32 * s) : make_uint4(0, 0, 0, 0);
+  }
+  if (slot < 0) {  // padding entry of a captured step: zeros, no reads (the same for the whole cluster)
+    if (split == 0)
+      for (int i = tid; i < p.group * HD; i += AD_THREADS)
+        p.out[(size_t)e * p.out_stride + (size_t)kvh * p.group * HD + i] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int pos = ctx;  // position of the new token; it looks at keys lo..pos
+  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int t_first = lo / AD_TILE, t_last = pos / AD_TILE;
+  const int ntiles = t_last - t_first + 1;
+  const int tps = (ntiles + p.nsplit - 1) / p.nsplit;
+  const int t_begin = t_first + split * tps;
+  const int t_end = min(t_last + 1, t_begin + tps);
+
+  const int* bt = p.block_table + (size_t)slot * p.bt_stride;
+  const int nt_split = t_end - t_begin;
+  const bool bt_cached = nt_split <= AD_BT_CACHE;
+  if (bt_cached) {
+    for (int i = tid; i < nt_split; i += AD_THREADS) sm_bt[i] = bt[((t_begin + i) * AD_TILE) / p.page_size];
+    __syncthreads();
+  }
+  auto tile_base = [&](int t) -> long {
+    const int key0 = t * AD_TILE;
+    const int page = bt_cached ? sm_bt[t - t_begin] : bt[key0 / p.page_size];
+    if (page < 0 || page >= p.num_pages) {
+      if (lane == 0) set_status(p.status, LL_ERR_PAGE_RANGE);
+      return -1;
+    }
+    return (((long)page * p.nkv + kvh) * p.page_size + (key0 % p.page_size)) * HD;
+  };
+  uint4 ka[KS], kb[KS], vv[VS][4];
+  auto load_k = [&](long tb) {
+#pragma unroll
+    for (int s = 0; s < KS; ++s) {
+      ka[s] = ad_ldg16(p.k_cache + tb + (long)g * HD + 32 * s + 8 * c);        // key g
+      kb[s] = ad_ldg16(p.k_cache + tb + (long)(g + 8) * HD + 32 * s + 8 * c);  // key g + 8
+    }
+  };
+  auto load_v = [&](long tb) {
+#pragma unroll
+    for (int h = 0; h < VS; ++h) {
+      vv[h][0] = ad_ldg16(p.v_cache + tb + (long)(2 * c) * HD + 64 * h + 8 * g);
+      vv[h][1] = ad_ldg16(p.v_cache + tb + (long)(2 * c + 1) * HD + 64 * h + 8 * g);
+      vv[h][2] = ad_ldg16(p.v_cache + tb + (long)(2 * c + 8) * HD + 64 * h + 8 * g);
+      vv[h][3] = ad_ldg16(p.v_cache + tb + (long)(2 * c + 9) * HD + 64 * h + 8 * g);
+    }
+  };
+
+  float o_acc[MT][4];  // O^T tile (h, jj): rows = dims 64 h + 8 g + jj and + 4, columns = heads 2c, 2c + 1
+#pragma unroll
+  for (int t = 0; t < MT; ++t) o_acc[t][0] = o_acc[t][1] = o_acc[t][2] = o_acc[t][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // heads 2c and 2c + 1
+
+  int t = t_begin + warp;
+  long tb = (t < t_end) ? tile_base(t) : -1;
+  if (t < t_end && tb >= 0) {
+    load_k(tb);
+    load_v(tb);
+  }
+  for (; t < t_end; t += AD_WARPS) {
+    const int t_next = t + AD_WARPS;
+    const long tb_next = (t_next < t_end) ? tile_base(t_next) : -1;
+    if (tb < 0) {
+      tb = tb_next;
+      if (tb >= 0) {
+        load_k(tb);
+        load_v(tb);
+      }
+      continue;
+    }
+    // ---- S^T = K Q^T: rows = keys g and g + 8, columns = heads 2c, 2c + 1 ----
+    float s_acc[4] = {0.f, 0.f, 0.f, 0.f}, s_odd[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < KS; ++s) {
+      ad_mma(s_acc, ka[s].x, kb[s].x, ka[s].y, kb[s].y, qf[s].x, qf[s].y);
+      ad_mma(s_odd, ka[s].z, kb[s].z, ka[s].w, kb[s].w, qf[s].z, qf[s].w);
+    }
+    if (tb_next >= 0) load_k(tb_next);
+    // ---- scale, mask, online softmax per head (column) ----
+    const int key0 = t * AD_TILE;
+    const bool boundary = (key0 + AD_TILE - 1 > pos) || (key0 < lo);
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      float v = (s_acc[x] + s_odd[x]) * p.scale_log2;
+      if (boundary) {
+        const int j = key0 + g + 8 * (x >> 1);
+        if (j > pos || j < lo) v = -INFINITY;
+      }
+      s_acc[x] = v;
+      tmax[x & 1] = fmaxf(tmax[x & 1], v);
+    }
+    float alpha[2], msafe[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 4));
+      tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 8));
+      tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 16));
+      const float m_new = fmaxf(m_run[i], tmax[i]);
+      msafe[i] = (m_new == -INFINITY) ? 0.f : m_new;
+      alpha[i] = ad_exp2(m_run[i] - msafe[i]);
+      m_run[i] = m_new;
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const float pv = ad_exp2(s_acc[x] - msafe[x & 1]);
+      s_acc[x] = pv;
+      psum[x & 1] += pv;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * alpha[i] + psum[i];
+    // P^T as the B operand: (keys 2c, 2c+1 | 2c+8, 2c+9; head g) from (key g | g+8; heads 2c, 2c+1)
+    const unsigned b0 = ad_movmatrix(ad_pack(s_acc[0], s_acc[1]));
+    const unsigned b1 = ad_movmatrix(ad_pack(s_acc[2], s_acc[3]));
+    // ---- O^T = O^T * alpha + V^T P^T ----
+    const bool rescale = (alpha[0] != 1.f) || (alpha[1] != 1.f);
+#pragma unroll
+    for (int h = 0; h < VS; ++h) {
+      const unsigned* w0 = reinterpret_cast<const unsigned*>(&vv[h][0]);
+      const unsigned* w1 = reinterpret_cast<const unsigned*>(&vv[h][1]);
+      const unsigned* w2 = reinterpret_cast<const unsigned*>(&vv[h][2]);
+      const unsigned* w3 = reinterpret_cast<const unsigned*>(&vv[h][3]);
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int T = h * 4 + jj;
+        // element jj of a 16-byte load is word jj / 2, half jj % 2; element 4 + jj is word 2 + jj / 2
+        const unsigned sel = (jj & 1) ? 0x7632u : 0x5410u;
+        const unsigned a0 = __byte_perm(w0[jj >> 1], w1[jj >> 1], sel);          // dim 8g+jj,   keys 2c, 2c+1
+        const unsigned a1 = __byte_perm(w0[2 + (jj >> 1)], w1[2 + (jj >> 1)], sel);  // dim 8g+4+jj, keys 2c, 2c+1
+        const unsigned a2 = __byte_perm(w2[jj >> 1], w3[jj >> 1], sel);          // dim 8g+jj,   keys 2c+8, 2c+9
+        const unsigned a3 = __byte_perm(w2[2 + (jj >> 1)], w3[2 + (jj >> 1)], sel);
+        if (rescale) {
+          o_acc[T][0] *= alpha[0];
+          o_acc[T][1] *= alpha[1];
+          o_acc[T][2] *= alpha[0];
+          o_acc[T][3] *= alpha[1];
+        }
+        ad_mma(o_acc[T], a0, a1, a2, a3, b0, b1);
+      }
+    }
+    if (tb_next >= 0) load_v(tb_next);
+    tb = tb_next;
+  }
+
+  // ---- merge the four warps (rows of the merge = heads) ----
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 4);
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 8);
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 16);
+  }
+  if (g == 0) {
+    sm_m[warp][2 * c] = m_run[0];
+    sm_m[warp][2 * c + 1] = m_run[1];
+    sm_l[warp][2 * c] = l_run[0];
+    sm_l[warp][2 * c + 1] = l_run[1];
+  }
+#pragma unroll
+  for (int T = 0; T < MT; ++T) {
+    const int h = T >> 2, jj = T & 3;
+    const int d0 = 64 * h + 8 * g + jj, d1 = d0 + 4;
+    sm_o[warp][2 * c][d0] = o_acc[T][0];
+    sm_o[warp][2 * c + 1][d0] = o_acc[T][1];
+    sm_o[warp][2 * c][d1] = o_acc[T][2];
+    sm_o[warp][2 * c + 1][d1] = o_acc[T][3];
+  }
+  __syncthreads();
+  constexpr int CPR = AD_THREADS / AD_HEADS;  // 16 threads per head
+  constexpr int DPT = HD / CPR;               // 8 or 4 dims per thread
+  const int row = tid / CPR, dbase = (tid % CPR) * DPT;
+  float M = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, sm_m[w][row]);
+  const float Ms = (M == -INFINITY) ? 0.f : M;
+  float L = 0.f, wgt[AD_WARPS];
+#pragma unroll
+  for (int w = 0; w < AD_WARPS; ++w) {
+    wgt[w] = ad_exp2(sm_m[w][row] - Ms);
+    L += sm_l[w][row] * wgt[w];
+  }
+  float acc[DPT];
+#pragma unroll
+  for (int d = 0; d < DPT; ++d) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < AD_WARPS; ++w) a += sm_o[w][row][dbase + d] * wgt[w];
+    acc[d] = a;
+  }
+  if (p.nsplit == 1) {
+    if (row < p.group) {
+      bf16* orow = p.out + (size_t)e * p.out_stride + (size_t)(kvh * p.group + row) * HD + dbase;
+      const float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+      for (int d = 0; d < DPT; d += 2)
+        *reinterpret_cast<unsigned*>(orow + d) = ad_pack(acc[d] * inv, acc[d + 1] * inv);
+    }
+    return;
+  }
+  // ---- the splits are the CTAs of one cluster: each finishes a slice of the dims of all heads ----
+  __syncthreads();
+#pragma unroll
+  for (int d = 0; d < DPT; ++d) sm_o[0][row][dbase + d] = acc[d];
+  if ((tid % CPR) == 0) {
+    sm_m[0][row] = M;
+    sm_l[0][row] = L;
+  }
+  ad_cluster_sync();
+  const int cs = p.nsplit;
+  const unsigned rank = ad_cluster_rank();
+  const int slice = HD / cs;                     // dims this CTA finishes: 8 .. 64
+  const int outputs = AD_HEADS * slice;          // 64 .. 512
+  const int per = max(1, outputs / AD_THREADS);  // 1 .. 4 consecutive dims of one head per thread
+  const bool worker = tid * per < outputs;
+  const int o0 = worker ? tid * per : 0;
+  const int row2 = o0 / slice, d0 = (int)rank * slice + (o0 - row2 * slice);
+  float ms[8], ls[8], Mg = -INFINITY;
+#pragma unroll
+  for (int sI = 0; sI < 8; ++sI)
+    if (sI < cs) {
+      ms[sI] = ad_ld_peer(&sm_m[0][row2], sI);
+      ls[sI] = ad_ld_peer(&sm_l[0][row2], sI);
+      Mg = fmaxf(Mg, ms[sI]);
+    }
+  const float Mgs = (Mg == -INFINITY) ? 0.f : Mg;
+  float Lg = 0.f, fin[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int sI = 0; sI < 8; ++sI)
+    if (sI < cs) {
+      const float ws = ad_exp2(ms[sI] - Mgs);
+      Lg += ls[sI] * ws;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (k < per) fin[k] += ad_ld_peer(&sm_o[0][row2][d0 + k], sI) * ws;
+    }
+  if (worker && row2 < p.group) {
+    bf16* o2 = p.out + (size_t)e * p.out_stride + (size_t)(kvh * p.group + row2) * HD + d0;
+    const float inv = Lg > 0.f ? 1.0f / Lg : 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (k < per) o2[k] = __float2bfloat16_rn(fin[k] * inv);
+  }
+  ad_cluster_sync();  // nobody leaves while its shared memory may still be read
+}
+
+// One new token per entry: q row e (head h at q + e*q_stride + h*hd) attends to the cached keys of
+// the request in req_slot[e] up to position ctx_len[e] (its own key is already in the cache).
+// nsplit in {1, 2, 4, 8}: CTAs per (entry, kv head), launched as one cluster.
+extern "C" int ll_attn_decode(void* out, long out_stride, const void* q, long q_stride, const void* k_cache,
+                              const void* v_cache, const int* block_table, int bt_stride, const int* ctx_len,
+                              const int* req_slot, int n_entries, int nh, int nkv, int hd, int page_size,
+                              int num_pages, int window, float scale, int nsplit, int* status, cudaStream_t stream) {
+  if (n_entries <= 0) return 0;
+  if ((hd != 64 && hd != 128) || page_size % AD_TILE != 0 || nkv <= 0 || nh % nkv != 0 || nkv > 65535)
+    return (int)cudaErrorInvalidValue;
+  if (nh / nkv > AD_HEADS || !(nsplit == 1 || nsplit == 2 || nsplit == 4 || nsplit == 8))
+    return (int)cudaErrorInvalidValue;
+  if ((q_stride % 8) != 0 || (out_stride % 2) != 0) return (int)cudaErrorInvalidValue;
+  AttnDecodeParams p;
+  p.q = (const bf16*)q;
+  p.q_stride = q_stride;
+  p.out = (bf16*)out;
+  p.out_stride = out_stride;
+  p.k_cache = (const bf16*)k_cache;
+  p.v_cache = (const bf16*)v_cache;
+  p.block_table = block_table;
+  p.bt_stride = bt_stride;
+  p.ctx_len = ctx_len;
+  p.req_slot = req_slot;
+  p.n_entries = n_entries;
+  p.nh = nh;
+  p.nkv = nkv;
+  p.group = nh / nkv;
+  p.page_size = page_size;
+  p.num_pages = num_pages;
+  p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.nsplit = nsplit;
+  p.status = status;
+  dim3 grid(n_entries, nkv, nsplit);
+  if (hd == 64)
+    ll_launch_cluster(attn_decode_kernel<64>, grid, dim3(AD_THREADS), 0, stream, nsplit, p);
+  else
+    ll_launch_cluster(attn_decode_kernel<128>, grid, dim3(AD_THREADS), 0, stream, nsplit, p);
+  return LL_LAUNCH_RESULT();
+}

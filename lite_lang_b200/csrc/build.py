@@ -35,7 +35,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
 # name -> (sources, definitions)
 LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "core": (("embedding.cu", "norm.cu", "rope.cu", "activation.cu", "sampling.cu", "attention_generic.cu"), ()),
-    "attn_mma": (("attention_mma.cu", "attention_prefill.cu"), ()),
+    "attn_mma": (("attention_mma.cu", "attention_prefill.cu", "attention_decode.cu"), ()),
     "gemm_smallm": (("gemm_smallm.cu",), ()),
     "gemm_stream": (("gemm_stream.cu",), ()),
     "attn_mma_static": (("attention_mma_static.cu",), ()),

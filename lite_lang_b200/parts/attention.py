@@ -150,9 +150,14 @@ class GQAttention(Mixer):
                 if plan is None:
                     plan = step.scratch[key] = self._plan_mma(step, n_single, step.max_kv_len)
                 blocks, nsplit, single, warps = plan
-                ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q, step.ctx_len,
-                             step.req_slot, n_single, blocks, *args, nsplit, None, None, step.status,
-                             all_single=single, cluster=nsplit > 1, warps=warps)
+                if self.num_heads // self.num_kv_heads <= 8:
+                    # keys on the M side, the group's heads on the N side of the MMA: half the work a tile
+                    ops.attn_decode(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.ctx_len,
+                                    step.req_slot, n_single, *args, nsplit, step.status)
+                else:
+                    ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q,
+                                 step.ctx_len, step.req_slot, n_single, blocks, *args, nsplit, None, None,
+                                 step.status, all_single=single, cluster=nsplit > 1, warps=warps)
             if n_rest > 0:
                 key = ("attn_prefill", self.num_heads, self.num_kv_heads)
                 blocks = step.scratch.get(key)

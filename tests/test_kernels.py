@@ -278,6 +278,71 @@ def test_attn_mma(nh, nkv, hd, ps, lens, q_lens, window, nsplit):
     assert_close(out, c["ref"], torch.bfloat16, "attn_mma with 8 warps")
 
 
+DECODE_SHAPES = [
+    # nh, nkv, hd, page, lens, window
+    (12, 2, 128, 16, [700, 33, 1, 2100], None),      # group 6
+    (8, 1, 64, 16, [130, 64, 65, 17, 1000], None),   # group 8: every MMA column used
+    (3, 3, 128, 32, [257, 16, 15], None),            # group 1
+    (14, 2, 64, 64, [300, 900], None),               # group 7, page 64
+    (12, 2, 128, 16, [500, 77, 3000], 120),          # window
+]
+
+
+@pytest.mark.parametrize("nsplit", [1, 2, 4, 8])
+@pytest.mark.parametrize("nh,nkv,hd,ps,lens,window", DECODE_SHAPES)
+def test_attn_decode(nh, nkv, hd, ps, lens, window, nsplit):
+    from lite_lang_b200 import ops
+    c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, lens, [1] * len(lens), window, seed=27)
+    d = dev()
+    ctx = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=d)
+    out = torch.full_like(c["q"], 3.0)
+    status = torch.zeros(1, dtype=torch.int32, device=d)
+    ops.attn_decode(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], ctx, c["req_slot"], len(lens), nh, nkv,
+                    hd, ps, window, hd ** -0.5, nsplit, status)
+    assert status.item() == 0
+    assert_close(out, c["ref"], torch.bfloat16, "attn_decode")
+
+
+@pytest.mark.parametrize("nsplit", [1, 8])
+@pytest.mark.parametrize("where", ["first", "page_edge", "last_of_page", "window_in", "window_out"])
+def test_attn_decode_finds_one_far_key(where, nsplit):
+    from lite_lang_b200 import ops
+    nh, nkv, hd, ps, L, window = 12, 2, 128, 16, 1000, None
+    if where == "first":
+        peak = lambda l: 0
+    elif where == "page_edge":
+        peak = lambda l: 16 * 31
+    elif where == "last_of_page":
+        peak = lambda l: 16 * 31 + 15
+    else:
+        window = 300
+        peak = (lambda l: l - 300) if where == "window_in" else (lambda l: l - 301)
+    c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, [L], [1], window, seed=28, peak=peak)
+    ctx = torch.tensor([L - 1], dtype=torch.int32, device=dev())
+    out = torch.full_like(c["q"], 3.0)
+    ops.attn_decode(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], ctx, c["req_slot"], 1, nh, nkv, hd, ps,
+                    window, hd ** -0.5, nsplit, None)
+    assert_close(out, c["ref"], torch.bfloat16, where)
+    assert (float(c["ref"].mean()) > 4.5) == (where != "window_out")
+
+
+def test_attn_decode_padding_and_refusals():
+    from lite_lang_b200 import ops
+    c = _paged_case(torch.bfloat16, 8, 2, 64, 16, [50], [1], None, seed=29)
+    d = dev()
+    q = torch.cat([c["q"], c["q"], c["q"]])
+    ctx = torch.tensor([49, 0, 0], dtype=torch.int32, device=d)
+    req_slot = torch.tensor([int(c["req_slot"][0]), -1, -1], dtype=torch.int32, device=d)
+    out = torch.full_like(q, 9.0)
+    ops.attn_decode(out, q, q.stride(0), c["kc"], c["vc"], c["bt"], ctx, req_slot, 3, 8, 2, 64, 16, None, 64 ** -0.5, 4,
+                    None)
+    assert_close(out[:1], c["ref"], torch.bfloat16)
+    assert float(out[1:].float().abs().max()) == 0.0
+    with pytest.raises(ValueError, match="groups of at most 8"):
+        ops.attn_decode(out, q, q.stride(0), c["kc"], c["vc"], c["bt"], ctx, req_slot, 3, 32, 2, 64, 16, None, 1.0, 1,
+                        None)
+
+
 PREFILL_SHAPES = [
     # nh, nkv, hd, page, lens, q_lens, window
     (12, 2, 128, 16, [300], [300], None),                       # a whole prompt, group 6
