@@ -25,6 +25,12 @@
 //           Warp w's tile has 8 gate rows and, as rows 8..15, the up rows of the same 8
 //           features, so the thread that holds gate(f, token) also holds up(f, token)
 //           and writes silu(gate) * up: the [M, 2 I] intermediate never exists.
+//   QKV_ROPE  the fused q|k|v projection of an attention layer with everything that follows it: a unit
+//           is 8 features of the first half of a head and their 8 rotation partners from the second half
+//           (two TMA boxes of 8 rows), k split over the warps as in NARROW.  After the warps' partial
+//           tiles are added, bias and rotary position encoding are applied in float32 and the results
+//           go where they belong: q into the output rows, k and v into the pages of the cache.  The
+//           [M, (nh + 2 nkv) hd] projection is never written and the rope/store kernel is not launched.
 //   NARROW  16 features x all of K; a stage is 16 rows x 256 k (four boxes) and warp w takes
 //           one box; the four partial tiles are added through shared memory.  For
 //           products with few output features (q|k|v, o, down), where units, not k, are scarce.
@@ -45,6 +51,7 @@
 #define GT_MODE_WIDE 0
 #define GT_MODE_GATED 1
 #define GT_MODE_NARROW 2
+#define GT_MODE_QKV_ROPE 3
 
 template <int MODE> struct GtShape;
 // ROWS x KC elements a stage, made of boxes of BOX_ROWS rows x 64 k (128 bytes a row).
@@ -56,6 +63,10 @@ template <> struct GtShape<GT_MODE_GATED> {
 };
 template <> struct GtShape<GT_MODE_NARROW> {
   static constexpr int ROWS = 16, KC = 256, BOX_ROWS = 16, STAGES = 12;
+};
+// two boxes of 8 rows land exactly where the 16-row box of NARROW does, so the consumers are the same
+template <> struct GtShape<GT_MODE_QKV_ROPE> {
+  static constexpr int ROWS = 16, KC = 256, BOX_ROWS = 8, STAGES = 12;
 };
 
 __device__ __forceinline__ unsigned gt_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -123,6 +134,17 @@ struct GtParams {
   int units;    // feature units times ksplit
   int ksplit;   // parts the k range is cut into; > 1: out is float32 [ksplit, M, N] partial sums
   int cpp;      // k chunks (stages) per part
+  // QKV_ROPE only: what follows the projection
+  const float* bias;       // float32 [(nh + 2 nkv) hd] or null
+  const int* positions;    // int32 [M]
+  const float* cos_sin;    // float32 [max_pos, hd]: cos half, sin half
+  int max_pos;
+  int nh, nkv, hd;
+  const int* slot_map;     // int32 [M]: cache slot of each token (-1: none)
+  bf16* k_cache;
+  bf16* v_cache;
+  int page_size;
+  long num_slots;
   int* status;
 };
 
@@ -168,6 +190,11 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
         } else if (MODE == GT_MODE_GATED) {
           y[0] = u * 32;                 // gate rows of the unit's 32 features
           y[RBOXES - 1] = p.N + u * 32;  // their up rows
+        } else if (MODE == GT_MODE_QKV_ROPE) {
+          const int upr = p.hd / 16;                  // units per head
+          const int head = u / upr, i0 = (u - head * upr) * 8;
+          y[0] = head * p.hd + i0;                    // 8 features of the first half of the head
+          y[RBOXES - 1] = y[0] + p.hd / 2;            // their partners in the second half
         } else {
           y[0] = u * 16;
         }
@@ -199,8 +226,9 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
   LL_PDL_WAIT();
 
   // k boxes of a stage this warp works on, and where its two A rows sit inside a box
-  constexpr int MYBOXES = (MODE == GT_MODE_NARROW) ? 1 : KBOXES;
-  const int kb0 = (MODE == GT_MODE_NARROW) ? warp : 0;
+  constexpr bool KSPLIT_WARPS = (MODE == GT_MODE_NARROW || MODE == GT_MODE_QKV_ROPE);  // warps split k
+  constexpr int MYBOXES = KSPLIT_WARPS ? 1 : KBOXES;
+  const int kb0 = KSPLIT_WARPS ? warp : 0;
   unsigned row_off[2];  // byte offset of row g / row g + 8 of this warp's tile inside a k box
   if (MODE == GT_MODE_WIDE) {
     row_off[0] = (16 * warp + g) * 128;
@@ -296,13 +324,71 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
         r[(g + 8) * TOK + 8 * j + 2 * c + 1] = acc[j][3];
       }
       gt_consumer_sync();
-      for (int idx = tid; idx < 16 * TOK; idx += GT_CONSUMERS * 32) {
-        const int t = idx >> 4, f = idx & 15;
-        if (t < p.M && u * 16 + f < p.N) {
-          float sum = 0.f;
+      if (MODE == GT_MODE_QKV_ROPE) {
+        // rows 0..7: features i0 + j of the head, rows 8..15: their partners i0 + j + hd/2
+        const int upr = p.hd / 16, half = p.hd / 2;
+        const int head = u / upr, i0 = (u - head * upr) * 8;
+        for (int idx = tid; idx < 8 * TOK; idx += GT_CONSUMERS * 32) {
+          const int t = idx >> 3, j = idx & 7;
+          if (t >= p.M) continue;
+          float x0 = 0.f, x1 = 0.f;
 #pragma unroll
-          for (int wi = 0; wi < GT_CONSUMERS; ++wi) sum += red[((size_t)wi * 16 + f) * TOK + t];
-          out[(size_t)t * p.out_stride + u * 16 + f] = gt_out<OutT>(sum);
+          for (int wi = 0; wi < GT_CONSUMERS; ++wi) {
+            x0 += red[((size_t)wi * 16 + j) * TOK + t];
+            x1 += red[((size_t)wi * 16 + j + 8) * TOK + t];
+          }
+          // the unfused path rounds the projection to bfloat16 before bias and rotation: the same here
+          x0 = __bfloat162float(__float2bfloat16_rn(x0));
+          x1 = __bfloat162float(__float2bfloat16_rn(x1));
+          const int f0 = head * p.hd + i0 + j;
+          if (p.bias) {
+            x0 += p.bias[f0];
+            x1 += p.bias[f0 + half];
+          }
+          if (head < p.nh + p.nkv) {
+            int pos = p.positions[t];
+            if (pos < 0 || pos >= p.max_pos) {
+              set_status(p.status, LL_ERR_POSITION_RANGE);
+              pos = 0;
+            }
+            const float cs = p.cos_sin[(size_t)pos * p.hd + i0 + j];
+            const float sn = p.cos_sin[(size_t)pos * p.hd + half + i0 + j];
+            const float r0v = x0 * cs - x1 * sn, r1v = x0 * sn + x1 * cs;
+            x0 = r0v;
+            x1 = r1v;
+          }
+          const bf16 o0 = __float2bfloat16_rn(x0), o1 = __float2bfloat16_rn(x1);
+          if (head < p.nh) {
+            bf16* q = reinterpret_cast<bf16*>(p.out) + (size_t)t * p.out_stride + f0;
+            q[0] = o0;
+            q[half] = o1;
+          } else {
+            long slot = p.slot_map ? (long)p.slot_map[t] : -1;
+            if (slot >= p.num_slots) {
+              set_status(p.status, LL_ERR_SLOT_RANGE);
+              slot = -1;
+            }
+            if (slot >= 0) {
+              const bool is_k = head < p.nh + p.nkv;
+              const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+              const long page = slot / p.page_size;
+              const int off = (int)(slot - page * p.page_size);
+              bf16* dst = (is_k ? p.k_cache : p.v_cache) + (((size_t)page * p.nkv + kvh) * p.page_size + off) * p.hd +
+                          i0 + j;
+              dst[0] = o0;
+              dst[half] = o1;
+            }
+          }
+        }
+      } else {
+        for (int idx = tid; idx < 16 * TOK; idx += GT_CONSUMERS * 32) {
+          const int t = idx >> 4, f = idx & 15;
+          if (t < p.M && u * 16 + f < p.N) {
+            float sum = 0.f;
+#pragma unroll
+            for (int wi = 0; wi < GT_CONSUMERS; ++wi) sum += red[((size_t)wi * 16 + f) * TOK + t];
+            out[(size_t)t * p.out_stride + u * 16 + f] = gt_out<OutT>(sum);
+          }
         }
       }
       gt_consumer_sync();
@@ -348,7 +434,7 @@ static int gt_launch(const GtParams& p, const void* w, int sm_count, cudaStream_
   const int rc = gt_make_map(&map, w, w_rows, p.K, S::BOX_ROWS);
   if (rc != 0) return rc;
   const size_t smem = 1024 + (size_t)S::STAGES * S::ROWS * S::KC * 2 + 2 * S::STAGES * 8 +
-                      (MODE == GT_MODE_NARROW ? sizeof(float) * GT_CONSUMERS * 16 * 8 * MT : 0);
+                      ((MODE == GT_MODE_NARROW || MODE == GT_MODE_QKV_ROPE) ? sizeof(float) * GT_CONSUMERS * 16 * 8 * MT : 0);
   cudaFuncSetAttribute(gemm_stream_kernel<MODE, MT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   // two CTAs an SM (one an SM, so that the next product's CTAs could move in early, was measured slower)
   const int grid = p.units < 2 * sm_count ? p.units : 2 * sm_count;
@@ -376,7 +462,7 @@ extern "C" int ll_gemm_stream(void* out, long out_stride, int out_f32, const voi
   if (M <= 0 || N <= 0) return 0;
   if (M > 32 || K <= 0 || (x_stride % 8) != 0 || sm_count <= 0 || ksplit < 1) return (int)cudaErrorInvalidValue;
   if (ksplit > 1 && (!out_f32 || mode == GT_MODE_GATED)) return (int)cudaErrorInvalidValue;
-  GtParams p;
+  GtParams p = {};
   p.x = (const bf16*)x;
   p.out = out;
   p.x_stride = x_stride;
@@ -411,4 +497,44 @@ extern "C" int ll_gemm_stream(void* out, long out_stride, int out_f32, const voi
                    : gt_dispatch_m<GT_MODE_NARROW, bf16>(p, w, sm_count, stream);
   }
   return (int)cudaErrorInvalidValue;
+}
+
+// The fused q|k|v projection of an attention layer (mode QKV_ROPE): qkv = x W^T (+ bias), q and k
+// rotated by the token's position (half-split pairs over the whole head), q written to
+// out[t, head * hd + i] (out: bfloat16 [M, >= nh * hd], row stride out_stride), k and v written into the
+// cache plane at slot_map[t].  w: bfloat16 [(nh + 2 nkv) hd, K]; K % 256 == 0; hd % 16 == 0; M <= 32.
+extern "C" int ll_gemm_stream_qkv_rope(void* out, long out_stride, const void* x, long x_stride, const void* w, int M,
+                                       int K, const float* bias, const int* positions, const float* cos_sin,
+                                       int max_pos, int nh, int nkv, int hd, const int* slot_map, void* k_cache,
+                                       void* v_cache, int page_size, long num_slots, int sm_count, int* status,
+                                       cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (M > 32 || K <= 0 || (K % 256) != 0 || (x_stride % 8) != 0 || sm_count <= 0 || hd <= 0 || (hd % 16) != 0 ||
+      nh <= 0 || nkv <= 0 || positions == nullptr || cos_sin == nullptr)
+    return (int)cudaErrorInvalidValue;
+  GtParams p = {};
+  p.x = (const bf16*)x;
+  p.out = out;
+  p.x_stride = x_stride;
+  p.out_stride = out_stride;
+  p.M = M;
+  p.N = (nh + 2 * nkv) * hd;
+  p.K = K;
+  p.status = status;
+  p.cpp = K / 256;
+  p.ksplit = 1;
+  p.units = (nh + 2 * nkv) * (hd / 16);
+  p.bias = bias;
+  p.positions = positions;
+  p.cos_sin = cos_sin;
+  p.max_pos = max_pos;
+  p.nh = nh;
+  p.nkv = nkv;
+  p.hd = hd;
+  p.slot_map = slot_map;
+  p.k_cache = (bf16*)k_cache;
+  p.v_cache = (bf16*)v_cache;
+  p.page_size = page_size;
+  p.num_slots = num_slots;
+  return gt_dispatch_m<GT_MODE_QKV_ROPE, bf16>(p, w, sm_count, stream);
 }

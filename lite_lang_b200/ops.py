@@ -455,6 +455,44 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: 
     return out
 
 
+def qkv_rope_supported(x: torch.Tensor, w_qkv: torch.Tensor, head_dim: int, rot_dim: int) -> bool:
+    """Whether the fused projection + bias + rotation + cache write kernel takes this step."""
+    return (stream_mode(x, w_qkv) is not None and x.shape[1] % 256 == 0 and head_dim % 16 == 0
+            and rot_dim == head_dim)
+
+
+def gemm_stream_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor],
+                         positions: torch.Tensor, cos_sin: torch.Tensor, num_heads: int, num_kv_heads: int,
+                         head_dim: int, slot_map: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                         v_cache: Optional[torch.Tensor], page_size: int, status: Optional[torch.Tensor]) -> None:
+    """q|k|v projection of up to 32 tokens with what follows it, in one kernel: bias, half-split rotation
+    of q and k, q into ``q_out`` [tokens, num_heads * head_dim], k and v into the cache plane."""
+    _need_cuda(q_out, x, w_qkv, bias, positions, cos_sin, slot_map, k_cache, v_cache, status)
+    _f32(bias, "bias")
+    _f32(cos_sin, "cos_sin")
+    _i32(positions, "positions")
+    _i32(slot_map, "slot_map")
+    m, k = x.shape
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    _need(qkv_rope_supported(x, w_qkv, head_dim, cos_sin.shape[1]), "gemm_stream_qkv_rope: shapes")
+    _need(tuple(w_qkv.shape) == (width, k), "gemm_stream_qkv_rope: weight shape")
+    _need(q_out.dtype == torch.bfloat16 and q_out.shape[0] == m and q_out.shape[1] >= num_heads * head_dim
+          and q_out.stride(1) == 1, "gemm_stream_qkv_rope: q_out")
+    if bias is not None:
+        _need(bias.numel() == width, "bias size")
+    num_slots = 0
+    if slot_map is not None:
+        _need(k_cache is not None and v_cache is not None and k_cache.dtype == torch.bfloat16
+              and k_cache.is_contiguous() and v_cache.is_contiguous()
+              and tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache plane")
+        num_slots = k_cache.shape[0] * page_size
+    load_library("gemm_stream").call(
+        "ll_gemm_stream_qkv_rope", _ptr(q_out), c_long(q_out.stride(0)), _ptr(x), c_long(x.stride(0)), _ptr(w_qkv),
+        c_int(m), c_int(k), _ptr(bias), _ptr(positions), _ptr(cos_sin), c_int(cos_sin.shape[0]), c_int(num_heads),
+        c_int(num_kv_heads), c_int(head_dim), _ptr(slot_map), _ptr(k_cache), _ptr(v_cache), c_int(page_size),
+        c_long(num_slots), c_int(sm_count(x.device)), _ptr(status), _stream())
+
+
 def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x @ Wg.T) * (x @ Wu.T) with W = [Wg; Wu]: fused for few tokens, else product + kernel."""
     inter = w_gate_up.shape[0] // 2

@@ -95,8 +95,18 @@ class GQAttention(Mixer):
     # ------------------------------------------------------------------
     def forward(self, x, step, cache):
         n = x.shape[0]
-        qkv = ops.linear(x, self.w_qkv)
         slot_map = cache.slot_map if cache.writable else None
+        if (self.position is not None and self.position.fuses_with_store
+                and ops.qkv_rope_supported(x, self.w_qkv, self.head_dim, self.position.fused_table().shape[1])):
+            # decode: projection, bias, rotation and cache write in one kernel; only q is materialised
+            q = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
+            ops.gemm_stream_qkv_rope(q, x, self.w_qkv, self.b_qkv, step.positions, self.position.fused_table(),
+                                     self.num_heads, self.num_kv_heads, self.head_dim, slot_map, cache.k, cache.v,
+                                     cache.page_size, step.status)
+            attn = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
+            self.attend(attn, q, step, cache)
+            return ops.linear(attn, self.w_o, partial_ok=True)
+        qkv = ops.linear(x, self.w_qkv)
         if self.position is None or self.position.fuses_with_store:
             table = self.position.fused_table() if self.position is not None else None
             ops.bias_rope_store(qkv, self.b_qkv, step.positions, table, self.num_heads, self.num_kv_heads,

@@ -601,6 +601,42 @@ def test_gemm_stream_gated(m, inter, k):
     assert status.item() == 0
 
 
+@pytest.mark.parametrize("m,hidden,nh,nkv,hd,ps", [(8, 1536, 12, 2, 128, 16), (1, 256, 3, 1, 64, 32), (19, 512, 4, 4, 32, 16),
+                                                   (32, 768, 6, 2, 128, 64)])
+def test_gemm_stream_qkv_rope_equals_the_three_kernels_it_replaces(m, hidden, nh, nkv, hd, ps):
+    from lite_lang_b200 import ops
+    from lite_lang_b200.parts.rope import rope_table
+    g = torch.Generator().manual_seed(30)
+    d = dev()
+    width = (nh + 2 * nkv) * hd
+    x = torch.randn(m, hidden, generator=g).to(torch.bfloat16).to(d)
+    w = (torch.randn(width, hidden, generator=g) / hidden ** 0.5).to(torch.bfloat16).to(d)
+    bias = (0.5 * torch.randn(width, generator=g)).to(d)
+    max_pos, num_pages = 500, 12
+    pos = torch.randint(0, max_pos, (m,), generator=g, dtype=torch.int32).to(d)
+    slots = torch.randperm(num_pages * ps, generator=g)[:m].to(torch.int32)
+    if m > 2:
+        slots[2] = -1
+    slots = slots.to(d)
+    table = rope_table(hd, 10000.0, max_pos).to(d)
+    status = torch.zeros(1, dtype=torch.int32, device=d)
+    # the unfused path: library product, then bias + rotation + store
+    ref_qkv = torch.mm(x, w.t())
+    kc_ref = torch.zeros(num_pages, nkv, ps, hd, dtype=torch.bfloat16, device=d)
+    vc_ref = torch.zeros_like(kc_ref)
+    ops.bias_rope_store(ref_qkv, bias, pos, table, nh, nkv, hd, slots, kc_ref, vc_ref, ps, status)
+    # fused
+    q = torch.full((m, nh * hd), 7.0, dtype=torch.bfloat16, device=d)
+    kc, vc = torch.zeros_like(kc_ref), torch.zeros_like(kc_ref)
+    ops.gemm_stream_qkv_rope(q, x, w, bias, pos, table, nh, nkv, hd, slots, kc, vc, ps, status)
+    assert status.item() == 0
+    scale = float(ref_qkv.float().abs().max())
+    for got, want, what in ((q, ref_qkv[:, :nh * hd], "q"), (kc, kc_ref, "k cache"), (vc, vc_ref, "v cache")):
+        err = float((got.float() - want.float()).abs().max()) / scale
+        assert err <= 1.6e-2, (what, err)       # same roundings; only the order of the float32 sums differs
+    assert float((kc.float().abs().sum(dim=(1, 3)) > 0).sum()) == float((kc_ref.float().abs().sum(dim=(1, 3)) > 0).sum())
+
+
 def test_linear_picks_the_library_for_other_shapes():
     from lite_lang_b200 import ops
     ops.configure_matmul_precision()
