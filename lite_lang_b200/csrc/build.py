@@ -38,6 +38,7 @@ LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "attn_mma": (("attention_mma.cu", "attention_prefill.cu", "attention_decode.cu"), ()),
     "gemm_smallm": (("gemm_smallm.cu",), ()),
     "gemm_stream": (("gemm_stream.cu",), ()),
+    "gemm_tc": (("gemm_tc.cu",), ()),
     "attn_mma_static": (("attention_mma_static.cu",), ()),
 }
 

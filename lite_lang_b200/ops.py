@@ -14,6 +14,7 @@ float32 path TF32 is switched off so that it is a true 32-bit product.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_long, c_void_p
 from typing import Optional
 
@@ -493,12 +494,75 @@ def gemm_stream_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w_qkv: torch.Tens
         c_long(num_slots), c_int(sm_count(x.device)), _ptr(status), _stream())
 
 
+TC_M = 128          # most tokens the tcgen05 weight-streaming kernel takes
+TC_ENABLED = os.environ.get("LITE_LANG_B200_TC", "1") != "0"   # 0: library products instead (for comparisons)
+
+
+def tc_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether ``gemm_tc`` takes this product: bfloat16, at most 128 tokens, K % 64 == 0, aligned rows."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+            and 0 < x.shape[0] <= TC_M and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.shape[1] % 64 == 0
+            and weight.is_contiguous() and weight.shape[1] == x.shape[1]
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def tc_preferred(x: torch.Tensor, weight: torch.Tensor, gated: bool = False) -> bool:
+    """Where the tcgen05 kernel was measured ahead of the library product on a B200: more tokens than
+    ``gemm_stream`` takes and few enough that the step is still bound by reading the weights.  The gated
+    feed-forward up to 64 tokens; a product with a long k (split over k, partial sums to the norm) up to 128."""
+    if not (TC_ENABLED and tc_supported(x, weight) and x.shape[0] > STREAM_M):
+        return False
+    if gated:
+        return x.shape[0] <= 64
+    return x.shape[1] >= 4096 and tc_ksplit(weight.shape[0], x.shape[1], x.device) > 1
+
+
+def tc_ksplit(n: int, k: int, device) -> int:
+    """Parts to cut k into so that a product with few output features (units of 128) has a unit for
+    every SM; every part keeps at least four 64-wide boxes.  Normalised so that no part is empty."""
+    units = (n + 127) // 128
+    boxes = k // 64
+    want = max(1, min(sm_count(device) // units, boxes // 4))
+    per = (boxes + want - 1) // want
+    return (boxes + per - 1) // per
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False,
+            status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = x @ weight.T for up to 128 bfloat16 tokens on the tcgen05 tensor cores (weights streamed
+    by TMA, accumulator in tensor memory).  ``gated``: weight is [2 I, K] and out = silu(gate) * up.
+    A float32 ``out`` of shape [parts, M, N] receives the partial sums of a k range cut into parts."""
+    _need_cuda(x, weight, out, status)
+    _need(tc_supported(x, weight), "gemm_tc: bfloat16, at most 128 tokens, K % 64 == 0, 16-byte aligned rows")
+    m, k = x.shape
+    n = weight.shape[0] // 2 if gated else weight.shape[0]
+    ksplit = 1
+    if out.dim() == 3:
+        ksplit = out.shape[0]
+        _need(out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape[1:]) == (m, n) and not gated,
+              "gemm_tc: partial sums go to a contiguous float32 [parts, M, N]")
+        per = (k // 64 + ksplit - 1) // ksplit
+        _need((k // 64 + per - 1) // per == ksplit, "gemm_tc: a part of k would be empty")
+        out_stride = n
+    else:
+        _need(out.shape[0] == m and out.shape[1] == n and out.stride(1) == 1, "gemm_tc: out shape")
+        out_stride = out.stride(0)
+    _need(out.dtype == torch.bfloat16 or (out.dtype == torch.float32 and not gated), "gemm_tc: out dtype")
+    load_library("gemm_tc").call(
+        "ll_gemm_tc", _ptr(out), c_long(out_stride), c_int(1 if out.dtype == torch.float32 else 0), _ptr(x),
+        c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(1 if gated else 0), c_int(ksplit),
+        c_int(sm_count(x.device)), _ptr(status), _stream())
+    return out
+
+
 def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x @ Wg.T) * (x @ Wu.T) with W = [Wg; Wu]: fused for few tokens, else product + kernel."""
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
     if stream_mode(x, w_gate_up, gated=True) is not None:
         return gemm_stream(x, w_gate_up, act, 1)
+    if tc_preferred(x, w_gate_up, gated=True):
+        return gemm_tc(x, w_gate_up, act, gated=True)
     if smallm_preferred(x, w_gate_up, gated=True):
         return gemm_smallm(x, w_gate_up, act, gated=True)
     gu = linear(x, w_gate_up)
@@ -530,6 +594,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
             out = torch.empty((x.shape[0], weight.shape[0]), dtype=dt, device=x.device)
         if out.dtype == dt:
             return gemm_stream(x, weight, out, mode)
+    if out is None and partial_ok and out_dtype in (None, x.dtype) and tc_preferred(x, weight):
+        parts = tc_ksplit(weight.shape[0], x.shape[1], x.device)
+        out = torch.empty((parts, x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+        return gemm_tc(x, weight, out)
     if smallm_preferred(x, weight) and (out is None or out.stride(1) == 1):
         dt = out_dtype or x.dtype
         if out is None:

@@ -601,6 +601,79 @@ def test_gemm_stream_gated(m, inter, k):
     assert status.item() == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(64, 128, 64), (33, 256, 128), (128, 128, 192), (7, 100, 64), (100, 331, 448)])
+def test_gemm_tc_is_exact_on_small_integers(m, n, k):
+    """Integer operands whose products and sums are exact in float32: a wrong swizzle, descriptor or
+    tensor-memory lane shows as a wrong integer, not as rounding."""
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(40)
+    x = torch.randint(-3, 4, (m, k), generator=g).to(torch.bfloat16)
+    w = torch.randint(-3, 4, (n, k), generator=g).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    out = torch.full((m, n), 7.0, dtype=torch.float32, device=dev())
+    for _ in range(2):
+        ops.gemm_tc(x.to(dev()), w.to(dev()), out, status=status)
+    assert status.item() == 0
+    assert torch.equal(out.double().cpu(), ref)
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 1536, 1536), (48, 2048, 1536), (128, 1000, 8960), (33, 151936 // 8, 1536)])
+def test_gemm_tc(m, n, k):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    for dt in (torch.bfloat16, torch.float32):
+        out = torch.full((m, n), 7.0, dtype=dt, device=dev())
+        for _ in range(2):
+            ops.gemm_tc(x.to(dev()), w.to(dev()), out, status=status)
+        err = float((out.double().cpu() - ref).abs().max()) / float(ref.abs().max())
+        assert err <= (8e-3 if dt == torch.bfloat16 else 2e-5), (dt, err)
+    assert status.item() == 0
+
+
+@pytest.mark.parametrize("m,n,k,parts", [(64, 1536, 8960, 12), (40, 1536, 1536, 6), (128, 200, 1024, 4)])
+def test_gemm_tc_split_over_k(m, n, k, parts):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(42)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    out = torch.full((parts, m, n), float("nan"), dtype=torch.float32, device=dev())
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    ops.gemm_tc(x.to(dev()), w.to(dev()), out, status=status)
+    assert status.item() == 0
+    total = out.double().sum(0).cpu()
+    assert float((total - ref).abs().max()) / float(ref.abs().max()) <= 2e-5
+    assert ops.tc_ksplit(1536, 8960, dev()) >= 2 and ops.tc_ksplit(17920, 1536, dev()) == 1
+
+
+@pytest.mark.parametrize("m,inter,k", [(64, 8960, 1536), (33, 203, 384), (128, 320, 256), (100, 1024, 128)])
+def test_gemm_tc_gated(m, inter, k):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(43)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(dev())
+    w = (2 * torch.randn(2 * inter, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(dev())
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    fused = ops.gemm_tc(x, w, torch.empty(m, inter, dtype=torch.bfloat16, device=dev()), gated=True, status=status)
+    ref = P.silu_and_mul(P.linear(x.float().cpu(), w[:inter].float().cpu()), P.linear(x.float().cpu(), w[inter:].float().cpu()))
+    assert_close(fused, ref, torch.bfloat16, "gated")
+    assert status.item() == 0
+
+
+def test_gemm_tc_refuses_what_it_cannot_do():
+    from lite_lang_b200 import ops
+    x = torch.zeros(129, 64, dtype=torch.bfloat16, device=dev())
+    w = torch.zeros(128, 64, dtype=torch.bfloat16, device=dev())
+    with pytest.raises((RuntimeError, ValueError)):
+        ops.gemm_tc(x, w, torch.empty(129, 128, dtype=torch.bfloat16, device=dev()))
+    with pytest.raises((RuntimeError, ValueError)):
+        ops.gemm_tc(x[:8, :32], w[:, :32].contiguous(), torch.empty(8, 128, dtype=torch.bfloat16, device=dev()))
+
+
 @pytest.mark.parametrize("m,hidden,nh,nkv,hd,ps", [(8, 1536, 12, 2, 128, 16), (1, 256, 3, 1, 64, 32), (19, 512, 4, 4, 32, 16),
                                                    (32, 768, 6, 2, 128, 64)])
 def test_gemm_stream_qkv_rope_equals_the_three_kernels_it_replaces(m, hidden, nh, nkv, hd, ps):
