@@ -1,0 +1,487 @@
+// Paged attention for portions of prompts on the fifth-generation tensor cores (tcgen05), bfloat16,
+// head size 64 or 128, pages of 8, 16, 32 or a multiple of 64 tokens.
+//
+// A CTA works on up to 128 query rows of one kv head: floor(128 / group) consecutive tokens of one entry
+// times the group's query heads (row = token * group + head), so the keys and values are read once for
+// the whole group.  It walks the keys the rows may see in blocks of 64:
+//   S  = Q K^T      tcgen05.mma 128 x 64 x head size, both operands K-major from shared memory, S in
+//                   tensor memory (two buffers);
+//   softmax         four warps, one row per thread: the row comes out of tensor memory with tcgen05.ld,
+//                   the running maximum and sum stay in registers (float32, exp2 with the scale folded in),
+//                   P goes to shared memory as bfloat16 in the 128-byte swizzled K-major form;
+//   PV = P V        tcgen05.mma 128 x head size x 64, V as the MN-major operand straight from the cache
+//                   rows, PV in tensor memory (two buffers); the row's thread adds it to its float32
+//                   output row in registers, rescaled when the maximum moved.
+// Roles: warp 0 loads (one thread: Q once through a 3-d tensor map [token, head, head size]; K and V
+// of a block page by page through 2-d maps over the cache plane, into a ring of three stages), warp 1
+// issues the MMAs (one thread; S of the next block before PV of this one, so that the tensor cores work
+// while the softmax threads do), warps 2..5 are the softmax rows.  All hand-offs are mbarriers: TMA
+// completes the "full" ones, tcgen05.commit the ones the tensor cores free, the softmax warps arrive
+// on the rest.  Every wait is bounded; one that runs out records LL_ERR_WAIT_TIMEOUT, stops waiting in
+// that thread and lets the kernel run to its end, where tensor memory is freed.
+//
+// Masked places: a key after the row's position, or before its window, gets probability 0 by selection
+// (never by arithmetic on what was read).  Pages that a window has given back (table entry -1) and pages
+// beyond the context are read from page 0 instead and are always masked.  The cache is zero-filled when
+// it is made and only ever holds finite numbers, so 0 x (stale value) stays 0 in PV.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define LL_ERR_WAIT_TIMEOUT 5
+#define AT_THREADS 192
+#define AT_KB 64  // keys a block
+#define AT_KS 3   // K/V stages
+
+__device__ __forceinline__ unsigned at_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void at_mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void at_mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void at_mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool at_mbar_try(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// `dead` is the calling thread's memory of a wait that ran out: after the first one it waits no more.
+__device__ __forceinline__ void at_mbar_wait(unsigned bar, unsigned parity, int* status, bool& dead) {
+  if (dead || at_mbar_try(bar, parity)) return;
+  const long long t0 = clock64();
+  while (!at_mbar_try(bar, parity)) {
+    if (clock64() - t0 > 4000000000ll) {
+      set_status(status, LL_ERR_WAIT_TIMEOUT);
+      dead = true;
+      return;
+    }
+  }
+}
+__device__ __forceinline__ void at_tma_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void at_tma_3d(unsigned dst, const CUtensorMap* map, int x, int y, int z, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+// K-major operand tile: rows of 128 bytes, 128-byte swizzle, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ unsigned long long at_desc_k(unsigned addr) {
+  return (unsigned long long)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand tile (V: rows are keys, 64 head-size elements = 128 bytes a row, 128-byte swizzle):
+// groups of 8 keys 1024 bytes apart (stride offset), the next 64 head-size elements `lbo_bytes` further.
+__device__ __forceinline__ unsigned long long at_desc_mn(unsigned addr, unsigned lbo_bytes) {
+  return (unsigned long long)((addr >> 4) & 0x3FFF) | ((unsigned long long)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+         (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void at_mma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
+                                       unsigned accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void at_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 consecutive float32 columns of this thread's tensor-memory lane
+__device__ __forceinline__ void at_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      " tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+#define AT_FENCE_BEFORE() asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory")
+#define AT_FENCE_AFTER() asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory")
+
+struct AttnTcParams {
+  bf16* out;
+  long out_stride;
+  const int* block_table;
+  int bt_stride;
+  const int* cu_q;
+  const int* ctx_len;
+  const int* req_slot;
+  int n_entries, nkv, group, tpb;   // tpb: tokens a CTA (floor(128 / group))
+  int page_size, num_pages, window;
+  int box_rows;                     // keys a K/V box: min(page_size, 64)
+  float scale_log2;
+  int* status;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap qmap,
+                       const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
+  constexpr int HB = HD / 64;                  // 64-wide boxes along the head size
+  constexpr int Q_BYTES = 128 * HD * 2;        // also the output rows on their way out
+  constexpr int KV_BYTES = AT_KB * HD * 2;     // K (or V) of a block
+  constexpr int STAGE_BYTES = 2 * KV_BYTES;
+  constexpr int P_BYTES = 128 * AT_KB * 2;
+  constexpr int TMEM_COLS = (HD == 128) ? 512 : 256;   // S: 2 x 64 columns, PV: 2 x HD columns
+  constexpr unsigned IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_KB >> 3) << 17) | ((128u >> 4) << 24);
+  constexpr unsigned IDESC_PV =
+      (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((128u >> 4) << 24);
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* q_s = smem;
+  unsigned char* kv_s = q_s + Q_BYTES;
+  unsigned char* p_s = kv_s + AT_KS * STAGE_BYTES;
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + 2 * P_BYTES);
+  // barriers: q_full, kv_full[KS], kv_empty[KS], s_full[2], s_empty[2], p_full[2], pv_full[2], pv_empty[2]
+  const unsigned q_full = at_smem(bars);
+  const unsigned kv_full0 = at_smem(bars + 1), kv_empty0 = at_smem(bars + 1 + AT_KS);
+  const unsigned s_full0 = at_smem(bars + 1 + 2 * AT_KS), s_empty0 = s_full0 + 16, p_full0 = s_full0 + 32;
+  const unsigned pv_full0 = s_full0 + 48, pv_empty0 = s_full0 + 64;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 1 + 2 * AT_KS + 10);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int kvh = blockIdx.y;
+
+  // ---- which rows: row block rb of the step (heavier, later blocks of an entry first) ----
+  int rb = gridDim.x - 1 - blockIdx.x;
+  int entry = -1, qlen = 0;
+  for (int e = 0; e < p.n_entries; ++e) {
+    const int ql = p.cu_q[e + 1] - p.cu_q[e];
+    const int nb = (ql + p.tpb - 1) / p.tpb;
+    if (rb < nb) {
+      entry = e;
+      qlen = ql;
+      break;
+    }
+    rb -= nb;
+  }
+  if (entry < 0) return;
+  const int slot = p.req_slot[entry];
+  if (slot < 0) return;
+  const int tok0 = p.cu_q[entry] + rb * p.tpb;              // first token (row of q and out) of this CTA
+  const int ntok = min(p.tpb, qlen - rb * p.tpb);
+  const int pos0 = p.ctx_len[entry] + rb * p.tpb;           // its position (ctx_len: tokens cached before the step)
+  const int hi = pos0 + ntok - 1;
+  const int lo_min = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int kb_lo = lo_min / AT_KB;
+  const int nblk = hi / AT_KB - kb_lo + 1;
+
+  if (tid == 32) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&qmap) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&kmap) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
+  }
+  if (tid == 0) {
+    at_mbar_init(q_full, 1);
+    for (int s = 0; s < AT_KS; ++s) {
+      at_mbar_init(kv_full0 + 8 * s, 1);
+      at_mbar_init(kv_empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      at_mbar_init(s_full0 + 8 * b, 1);
+      at_mbar_init(s_empty0 + 8 * b, 4);
+      at_mbar_init(p_full0 + 8 * b, 4);
+      at_mbar_init(pv_full0 + 8 * b, 1);
+      at_mbar_init(pv_empty0 + 8 * b, 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_smem(tmem_slot)),
+                 "r"((unsigned)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  AT_FENCE_BEFORE();
+  __syncthreads();
+  AT_FENCE_AFTER();
+  const unsigned tmem = *tmem_slot;
+  const unsigned tmem_s = tmem, tmem_pv = tmem + 2 * AT_KB;
+  LL_PDL_WAIT();   // q and the new keys and values come from the kernel before
+  LL_PDL_TRIGGER();
+  bool dead = false;
+
+  if (warp == 0) {
+    // ------------------------------ loads ------------------------------
+    if (lane == 0) {
+      at_mbar_expect_tx(q_full, (unsigned)(HB * 64 * p.group * p.tpb * 2));
+      for (int h = 0; h < HB; ++h)
+        at_tma_3d(at_smem(q_s) + h * (Q_BYTES / HB), &qmap, h * 64, kvh * p.group, tok0, q_full);
+      const int* bt = p.block_table + (size_t)slot * p.bt_stride;
+      const int boxes = AT_KB / p.box_rows;
+      for (int j = 0; j < nblk; ++j) {
+        const int s = j % AT_KS;
+        at_mbar_wait(kv_empty0 + 8 * s, (unsigned)(((j / AT_KS) & 1) ^ 1), p.status, dead);
+        at_mbar_expect_tx(kv_full0 + 8 * s, STAGE_BYTES);
+        const unsigned k_dst = at_smem(kv_s) + s * STAGE_BYTES, v_dst = k_dst + KV_BYTES;
+        for (int b = 0; b < boxes; ++b) {
+          const int kp = (kb_lo + j) * AT_KB + b * p.box_rows;
+          const int lp = kp / p.page_size;
+          int page = lp < p.bt_stride ? bt[lp] : -1;
+          if (page < 0 || page >= p.num_pages) page = 0;   // given back or beyond the context: masked below
+          const int row = (page * p.nkv + kvh) * p.page_size + kp % p.page_size;
+          for (int h = 0; h < HB; ++h) {
+            at_tma_2d(k_dst + h * (KV_BYTES / HB) + b * p.box_rows * 128, &kmap, h * 64, row, kv_full0 + 8 * s);
+            at_tma_2d(v_dst + h * (KV_BYTES / HB) + b * p.box_rows * 128, &vmap, h * 64, row, kv_full0 + 8 * s);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issue ------------------------------
+    if (lane == 0) {
+      auto mma_s = [&](int j) {   // S[j % 2] = Q K(j)^T
+        const int s = j % AT_KS, b = j & 1;
+        at_mbar_wait(kv_full0 + 8 * s, (unsigned)((j / AT_KS) & 1), p.status, dead);
+        at_mbar_wait(s_empty0 + 8 * b, (unsigned)(((j >> 1) & 1) ^ 1), p.status, dead);
+        AT_FENCE_AFTER();
+        const unsigned k_addr = at_smem(kv_s) + s * STAGE_BYTES;
+#pragma unroll
+        for (int k16 = 0; k16 < HD / 16; ++k16) {
+          const unsigned off = (k16 / 4) * (Q_BYTES / HB) + (k16 % 4) * 32;
+          const unsigned koff = (k16 / 4) * (KV_BYTES / HB) + (k16 % 4) * 32;
+          at_mma(tmem_s + b * AT_KB, at_desc_k(at_smem(q_s) + off), at_desc_k(k_addr + koff), IDESC_S, k16 > 0 ? 1u : 0u);
+        }
+        at_commit(s_full0 + 8 * b);
+      };
+      at_mbar_wait(q_full, 0, p.status, dead);
+      mma_s(0);
+      for (int j = 0; j < nblk; ++j) {
+        if (j + 1 < nblk) mma_s(j + 1);
+        const int s = j % AT_KS, b = j & 1;
+        at_mbar_wait(p_full0 + 8 * b, (unsigned)((j >> 1) & 1), p.status, dead);
+        at_mbar_wait(pv_empty0 + 8 * b, (unsigned)(((j >> 1) & 1) ^ 1), p.status, dead);
+        AT_FENCE_AFTER();
+        const unsigned v_addr = at_smem(kv_s) + s * STAGE_BYTES + KV_BYTES;
+        const unsigned p_addr = at_smem(p_s) + b * P_BYTES;
+#pragma unroll
+        for (int k16 = 0; k16 < AT_KB / 16; ++k16)   // 16 keys a step: 32 bytes along P's rows, 2048 bytes down V
+          at_mma(tmem_pv + b * HD, at_desc_k(p_addr + k16 * 32), at_desc_mn(v_addr + k16 * 2048, KV_BYTES / HB), IDESC_PV,
+                 k16 > 0 ? 1u : 0u);
+        at_commit(pv_full0 + 8 * b);
+        at_commit(kv_empty0 + 8 * s);
+      }
+    }
+  } else {
+    // ------------------------------ softmax rows (warps 2..5) ------------------------------
+    const int ew = warp & 3;                 // tensor-memory lanes 32 ew .. 32 ew + 31
+    const int r = 32 * ew + lane;            // row of the tile
+    const int t = r / p.group, g = r - t * p.group;
+    const bool row_ok = r < p.tpb * p.group && t < ntok;
+    const int prow = row_ok ? pos0 + t : -1;                                  // position of the row's token
+    const int lo_row = (p.window > 0 && prow >= 0) ? max(0, prow - p.window + 1) : 0;
+    const unsigned lane_addr = (unsigned)(32 * ew) << 16;
+    float o[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+
+    auto add_pv = [&](int j, float alpha) {   // o = o * alpha + PV(j)
+      const int b = j & 1;
+      at_mbar_wait(pv_full0 + 8 * b, (unsigned)((j >> 1) & 1), p.status, dead);
+      AT_FENCE_AFTER();
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        float v[32];
+        at_ld32(tmem_pv + lane_addr + b * HD + c0, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, v[i]);
+      }
+      AT_FENCE_BEFORE();
+      __syncwarp();
+      if (lane == 0) at_mbar_arrive(pv_empty0 + 8 * b);
+    };
+
+    for (int j = 0; j < nblk; ++j) {
+      const int b = j & 1;
+      const int k0 = (kb_lo + j) * AT_KB;
+      at_mbar_wait(s_full0 + 8 * b, (unsigned)((j >> 1) & 1), p.status, dead);
+      AT_FENCE_AFTER();
+      float sv[AT_KB];
+      {
+        float v[32];
+        at_ld32(tmem_s + lane_addr + b * AT_KB, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[i] = v[i];
+        at_ld32(tmem_s + lane_addr + b * AT_KB + 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[32 + i] = v[i];
+      }
+      AT_FENCE_BEFORE();
+      __syncwarp();
+      if (lane == 0) at_mbar_arrive(s_empty0 + 8 * b);
+      // mask by selection, scale, running maximum
+      const bool need_mask = (k0 + AT_KB - 1 > prow) || (k0 < lo_row);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < AT_KB; ++i) {
+        float x = sv[i] * p.scale_log2;
+        if (need_mask && (k0 + i > prow || k0 + i < lo_row)) x = -INFINITY;
+        sv[i] = x;
+        mx = fmaxf(mx, x);
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);   // m_run = -inf: 0
+      float sum = 0.f;
+      // P row: 64 bfloat16 = 128 bytes = 8 pieces of 16 bytes, piece c at (c ^ (r & 7)) of the swizzled row
+      unsigned char* prow_s = p_s + b * P_BYTES + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        unsigned w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float e0 = exp2f(sv[8 * c + 2 * i] - m_use), e1 = exp2f(sv[8 * c + 2 * i + 1] - m_use);
+          const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+          // the sum is of the rounded values, the ones PV is made from
+          sum += __bfloat162float(h.x) + __bfloat162float(h.y);
+          w[i] = *reinterpret_cast<const unsigned*>(&h);
+        }
+        *reinterpret_cast<uint4*>(prow_s + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l_run = l_run * alpha + sum;
+      m_run = m_new;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor cores
+      __syncwarp();
+      if (lane == 0) at_mbar_arrive(p_full0 + 8 * b);
+      // PV of the block before arrives while this block's PV is being made
+      if (j > 0) add_pv(j - 1, alpha_prev);
+      alpha_prev = alpha;
+    }
+    add_pv(nblk - 1, alpha_prev);
+    // ---- normalise; rows leave through shared memory (the Q tile is no longer read) ----
+    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+    unsigned char* orow = q_s + r * (HD * 2);
+#pragma unroll
+    for (int c = 0; c < HD / 8; ++c) {
+      unsigned w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(o[8 * c + 2 * i] * inv, o[8 * c + 2 * i + 1] * inv);
+        w[i] = *reinterpret_cast<const unsigned*>(&h);
+      }
+      *reinterpret_cast<uint4*>(orow + (((c & ~7) | ((c ^ r) & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const int e = tid - 64;
+    constexpr int CPR = HD / 8;   // 16-byte pieces a row
+    for (int idx = e; idx < 128 * CPR; idx += 128) {
+      const int rr = idx / CPR, c = idx % CPR;
+      const int tt = rr / p.group, gg = rr - tt * p.group;
+      if (rr < p.tpb * p.group && tt < ntok) {
+        const uint4 v = *reinterpret_cast<const uint4*>(q_s + rr * (HD * 2) + (((c & ~7) | ((c ^ rr) & 7)) << 4));
+        *reinterpret_cast<uint4*>(p.out + (size_t)(tok0 + tt) * p.out_stride + (size_t)(kvh * p.group + gg) * HD + 8 * c) = v;
+      }
+    }
+    (void)g;
+  }
+  // ---- everyone is done: free the tensor memory ----
+  AT_FENCE_BEFORE();
+  __syncthreads();
+  if (warp == 1) {
+    AT_FENCE_AFTER();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((unsigned)TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*at_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static at_encode_fn at_encoder() {
+  static at_encode_fn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (at_encode_fn)ptr;
+  }
+  return fn;
+}
+
+// Arguments as ll_attn_prefill (attention_prefill.cu), but the row blocks are counted differently:
+// row_blocks = sum over the entries of ceil(q_len / floor(128 / group)); num_tokens is the number of rows of q.
+extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, long q_stride, int num_tokens,
+                                  const void* k_cache, const void* v_cache, const int* block_table, int bt_stride,
+                                  const int* cu_q, const int* ctx_len, const int* req_slot, int n_entries,
+                                  int row_blocks, int nh, int nkv, int hd, int page_size, int num_pages, int window,
+                                  float scale, int* status, cudaStream_t stream) {
+  if (row_blocks <= 0 || n_entries <= 0) return 0;
+  if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0 || nkv > 65535 || nh / nkv > 128)
+    return (int)cudaErrorInvalidValue;
+  if (!(page_size == 8 || page_size == 16 || page_size == 32 || (page_size > 0 && page_size % 64 == 0)))
+    return (int)cudaErrorInvalidValue;
+  if ((q_stride % 8) != 0 || (out_stride % 8) != 0 || ((uintptr_t)q % 16) != 0 || ((uintptr_t)out % 16) != 0)
+    return (int)cudaErrorInvalidValue;
+  at_encode_fn enc = at_encoder();
+  if (enc == nullptr) return (int)cudaErrorNotSupported;
+  AttnTcParams p;
+  p.out = (bf16*)out;
+  p.out_stride = out_stride;
+  p.block_table = block_table;
+  p.bt_stride = bt_stride;
+  p.cu_q = cu_q;
+  p.ctx_len = ctx_len;
+  p.req_slot = req_slot;
+  p.n_entries = n_entries;
+  p.nkv = nkv;
+  p.group = nh / nkv;
+  p.tpb = 128 / p.group;
+  p.page_size = page_size;
+  p.num_pages = num_pages;
+  p.window = window;
+  p.box_rows = page_size < 64 ? page_size : 64;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+
+  CUtensorMap qmap, kmap, vmap;
+  const cuuint32_t estr3[3] = {1, 1, 1};
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)nh, (cuuint64_t)num_tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)q_stride * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)p.group, (cuuint32_t)p.tpb};
+    if (enc(&qmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr3,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return (int)cudaErrorInvalidValue;
+  }
+  for (int which = 0; which < 2; ++which) {
+    const cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)num_pages * nkv * page_size};
+    const cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)p.box_rows};
+    if (enc(which ? &vmap : &kmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(which ? v_cache : k_cache),
+            dims, strides, box, estr3, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return (int)cudaErrorInvalidValue;
+  }
+  const size_t smem = 1024 + (size_t)128 * hd * 2 + (size_t)AT_KS * 2 * AT_KB * hd * 2 + 2 * 128 * AT_KB * 2 + 256;
+  dim3 grid(row_blocks, nkv);
+  if (hd == 64) {
+    cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ll_launch(attn_prefill_tc_kernel<64>, grid, dim3(AT_THREADS), smem, stream, p, qmap, kmap, vmap);
+  } else {
+    cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ll_launch(attn_prefill_tc_kernel<128>, grid, dim3(AT_THREADS), smem, stream, p, qmap, kmap, vmap);
+  }
+  return LL_LAUNCH_RESULT();
+}

@@ -307,6 +307,46 @@ def attn_prefill(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: tor
         c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(status), _stream())
 
 
+def attn_prefill_tc_supported(dtype: torch.dtype, head_dim: int, page_size: int, q_stride: int, group: int) -> bool:
+    """Whether the tcgen05 prefill attention takes this shape."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and q_stride % 8 == 0 and 1 <= group <= 128
+            and (page_size in (8, 16, 32) or (page_size > 0 and page_size % 64 == 0)))
+
+
+def attn_prefill_tc_blocks(q_lens, group: int) -> int:
+    """Row blocks of a step for ``attn_prefill_tc``: a CTA takes floor(128 / group) tokens of one entry."""
+    tpb = 128 // group
+    return sum((int(n) + tpb - 1) // tpb for n in q_lens)
+
+
+def attn_prefill_tc(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
+                    num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                    page_size: int, window: Optional[int], scale: float, status: Optional[torch.Tensor]) -> None:
+    """Paged attention for portions of prompts on the tcgen05 tensor cores (TMA loads, S and PV in tensor
+    memory).  ``row_blocks`` from ``attn_prefill_tc_blocks``.  Otherwise as ``attn_prefill``."""
+    _need_cuda(out, q, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot)
+    for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot")):
+        _i32(t, nm)
+    _need(attn_prefill_tc_supported(q.dtype, head_dim, page_size, q_stride, num_heads // num_kv_heads),
+          f"attn_prefill_tc takes bfloat16, head_dim 64 or 128 and pages of 8, 16, 32 or a multiple of 64 tokens, "
+          f"not {q.dtype}, {head_dim}, {page_size}")
+    _need(out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16,
+          "attn_prefill_tc: dtypes differ")
+    _need(out.stride(1) == 1 and out.shape[1] == num_heads * head_dim and out.stride(0) % 8 == 0,
+          "attn_prefill_tc: out")
+    _need(q.stride(1) == 1 and q.shape[1] >= num_heads * head_dim and q.stride(0) == q_stride, "attn_prefill_tc: q")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache plane must be contiguous")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache plane shape")
+    _need(cu_q.numel() >= num_entries + 1 and ctx_len.numel() >= num_entries and req_slot.numel() >= num_entries,
+          "attn_prefill_tc: entry arrays too short")
+    load_library("attn_tc").call(
+        "ll_attn_prefill_tc", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), c_int(q.shape[0]),
+        _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.stride(0)), _ptr(cu_q), _ptr(ctx_len),
+        _ptr(req_slot), c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(status), _stream())
+
+
 _sample_scratch = {}
 
 

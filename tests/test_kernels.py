@@ -401,6 +401,50 @@ def test_attn_prefill_finds_one_far_key(where):
     assert (float(c["ref"][-1].mean()) > 4.5) == (where != "window_out")
 
 
+def _run_prefill_tc(c, nh, nkv, hd, ps, lens, q_lens, window, status=None):
+    from lite_lang_b200 import ops
+    d = dev()
+    cu = [0]
+    for ql in q_lens:
+        cu.append(cu[-1] + ql)
+    cu_q = torch.tensor(cu, dtype=torch.int32, device=d)
+    ctx = torch.tensor([l - ql for l, ql in zip(lens, q_lens)], dtype=torch.int32, device=d)
+    out = torch.full_like(c["q"], 3.0)
+    ops.attn_prefill_tc(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], cu_q, ctx, c["req_slot"], len(lens),
+                        ops.attn_prefill_tc_blocks(q_lens, nh // nkv), nh, nkv, hd, ps, window, hd ** -0.5, status)
+    return out
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,lens,q_lens,window", PREFILL_SHAPES + [
+    (14, 2, 64, 8, [90, 200], [90, 64], None),                  # group 7, pages of 8
+    (2, 2, 128, 128, [600], [333], 100),                        # group 1: 128 tokens a CTA; pages larger than a block
+])
+def test_attn_prefill_tc(nh, nkv, hd, ps, lens, q_lens, window):
+    c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, lens, q_lens, window, seed=18)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    out = _run_prefill_tc(c, nh, nkv, hd, ps, lens, q_lens, window, status)
+    assert status.item() == 0
+    assert_close(out, c["ref"], torch.bfloat16, "attn_prefill_tc")
+
+
+@pytest.mark.parametrize("where", ["first", "block_edge", "last_of_block", "window_in", "window_out"])
+def test_attn_prefill_tc_finds_one_far_key(where):
+    nh, nkv, hd, ps, L, window = 12, 2, 128, 16, 1000, None
+    if where == "first":
+        peak = lambda l: 0
+    elif where == "block_edge":
+        peak = lambda l: 64 * 7
+    elif where == "last_of_block":
+        peak = lambda l: 64 * 7 + 63
+    else:
+        window = 300
+        peak = (lambda l: l - 300) if where == "window_in" else (lambda l: l - 301)
+    c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, [L], [40], window, seed=19, peak=peak)
+    out = _run_prefill_tc(c, nh, nkv, hd, ps, [L], [40], window)
+    assert_close(out, c["ref"], torch.bfloat16, where)
+    assert (float(c["ref"][-1].mean()) > 4.5) == (where != "window_out")
+
+
 @pytest.mark.parametrize("nsplit,cluster", [(1, False), (5, False), (8, True)])
 @pytest.mark.parametrize("where", ["first", "page_edge", "last_of_page", "window_in", "window_out"])
 def test_attn_mma_finds_one_far_key(where, nsplit, cluster):
