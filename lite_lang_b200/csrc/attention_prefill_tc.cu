@@ -9,12 +9,17 @@
 //   softmax         four warps, one row per thread: the row comes out of tensor memory with tcgen05.ld,
 //                   the running maximum and sum stay in registers (float32, exp2 with the scale folded in),
 //                   P goes to shared memory as bfloat16 in the 128-byte swizzled K-major form;
-//   PV = P V        tcgen05.mma 128 x head size x 64, V as the MN-major operand straight from the cache
-//                   rows, PV in tensor memory (two buffers); the row's thread adds it to its float32
-//                   output row in registers, rescaled when the maximum moved.
+//   O += P V       tcgen05.mma 128 x head size x 64, V as the MN-major operand straight from the cache
+//                   rows, accumulated in tensor memory over all blocks.  The probabilities are taken
+//                   against a reference maximum per row that follows the true maximum only when that has
+//                   grown by more than 2^8: then the row's thread scales its row of O in tensor memory
+//                   (tcgen05.ld / st) and its sum.  In between, P is at most 2^8, exact enough in bfloat16
+//                   as before, and nothing has to be rescaled.
+// Two CTAs fit an SM (half of its shared memory and tensor memory each), so that one's softmax runs
+// beside the other's MMAs.
 // Roles: warp 0 loads (one thread: Q once through a 3-d tensor map [token, head, head size]; K and V
-// of a block page by page through 2-d maps over the cache plane, into a ring of three stages), warp 1
-// issues the MMAs (one thread; S of the next block before PV of this one, so that the tensor cores work
+// of a block page by page through 2-d maps over the cache plane, into a ring of two stages), warp 1
+// issues the MMAs (one thread; S of the next block before P V of this one, so that the tensor cores work
 // while the softmax threads do), warps 2..5 are the softmax rows.  All hand-offs are mbarriers: TMA
 // completes the "full" ones, tcgen05.commit the ones the tensor cores free, the softmax warps arrive
 // on the rest.  Every wait is bounded; one that runs out records LL_ERR_WAIT_TIMEOUT, stops waiting in
@@ -29,9 +34,10 @@
 #include "common.cuh"
 
 #define LL_ERR_WAIT_TIMEOUT 5
+#define LL_ERR_SMEM_ALIGN 6
 #define AT_THREADS 192
 #define AT_KB 64  // keys a block
-#define AT_KS 3   // K/V stages
+#define AT_KS 2   // stages of K and of V
 
 __device__ __forceinline__ unsigned at_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void at_mbar_init(unsigned bar, unsigned count) {
@@ -113,6 +119,21 @@ __device__ __forceinline__ void at_ld32(unsigned taddr, float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void at_st32(unsigned taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};\n"
+      " tcgen05.wait::st.sync.aligned;" ::"r"(__float_as_uint(v[0])),
+      "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])),
+      "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+      "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])),
+      "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+      "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+      "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])),
+      "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+      "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31])), "r"(taddr)
+      : "memory");
+}
 #define AT_FENCE_BEFORE() asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory")
 #define AT_FENCE_AFTER() asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory")
 
@@ -132,7 +153,7 @@ struct AttnTcParams {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __launch_bounds__(AT_THREADS, 2)
 attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap qmap,
                        const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
   constexpr int HB = HD / 64;                  // 64-wide boxes along the head size
@@ -140,23 +161,25 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
   constexpr int KV_BYTES = AT_KB * HD * 2;     // K (or V) of a block
   constexpr int STAGE_BYTES = 2 * KV_BYTES;
   constexpr int P_BYTES = 128 * AT_KB * 2;
-  constexpr int TMEM_COLS = (HD == 128) ? 512 : 256;   // S: 2 x 64 columns, PV: 2 x HD columns
+  constexpr int TMEM_COLS = 256;               // S: 2 x 64 columns, O: HD columns (half an SM's tensor memory)
   constexpr unsigned IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_KB >> 3) << 17) | ((128u >> 4) << 24);
   constexpr unsigned IDESC_PV =
       (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((128u >> 4) << 24);
 
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // the swizzled tiles need 1024-byte alignment in the shared window; there is no static shared memory
+  // in this kernel, so the dynamic part starts aligned (checked below, refused otherwise)
+  extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* q_s = smem;
   unsigned char* kv_s = q_s + Q_BYTES;
   unsigned char* p_s = kv_s + AT_KS * STAGE_BYTES;
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + 2 * P_BYTES);
-  // barriers: q_full, kv_full[KS], kv_empty[KS], s_full[2], s_empty[2], p_full[2], pv_full[2], pv_empty[2]
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + P_BYTES);
+  // barriers: q_full, k_full[KS], k_empty[KS], v_full[KS], v_empty[KS], s_full[2], s_empty[2], p_full, pv_done
   const unsigned q_full = at_smem(bars);
-  const unsigned kv_full0 = at_smem(bars + 1), kv_empty0 = at_smem(bars + 1 + AT_KS);
-  const unsigned s_full0 = at_smem(bars + 1 + 2 * AT_KS), s_empty0 = s_full0 + 16, p_full0 = s_full0 + 32;
-  const unsigned pv_full0 = s_full0 + 48, pv_empty0 = s_full0 + 64;
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 1 + 2 * AT_KS + 10);
+  const unsigned k_full0 = at_smem(bars + 1), k_empty0 = k_full0 + 8 * AT_KS;
+  const unsigned v_full0 = k_full0 + 16 * AT_KS, v_empty0 = k_full0 + 24 * AT_KS;
+  const unsigned s_full0 = k_full0 + 32 * AT_KS, s_empty0 = s_full0 + 16, p_full = s_full0 + 32;
+  const unsigned pv_done = s_full0 + 40;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 1 + 4 * AT_KS + 6);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int kvh = blockIdx.y;
@@ -175,6 +198,10 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
     rb -= nb;
   }
   if (entry < 0) return;
+  if ((at_smem(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) set_status(p.status, LL_ERR_SMEM_ALIGN);
+    return;
+  }
   const int slot = p.req_slot[entry];
   if (slot < 0) return;
   const int tok0 = p.cu_q[entry] + rb * p.tpb;              // first token (row of q and out) of this CTA
@@ -192,17 +219,13 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
   }
   if (tid == 0) {
     at_mbar_init(q_full, 1);
-    for (int s = 0; s < AT_KS; ++s) {
-      at_mbar_init(kv_full0 + 8 * s, 1);
-      at_mbar_init(kv_empty0 + 8 * s, 1);
-    }
+    for (int s = 0; s < 4 * AT_KS; ++s) at_mbar_init(k_full0 + 8 * s, 1);
     for (int b = 0; b < 2; ++b) {
       at_mbar_init(s_full0 + 8 * b, 1);
       at_mbar_init(s_empty0 + 8 * b, 4);
-      at_mbar_init(p_full0 + 8 * b, 4);
-      at_mbar_init(pv_full0 + 8 * b, 1);
-      at_mbar_init(pv_empty0 + 8 * b, 4);
     }
+    at_mbar_init(p_full, 4);
+    at_mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -215,43 +238,57 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
   __syncthreads();
   AT_FENCE_AFTER();
   const unsigned tmem = *tmem_slot;
-  const unsigned tmem_s = tmem, tmem_pv = tmem + 2 * AT_KB;
+  const unsigned tmem_s = tmem, tmem_o = tmem + 2 * AT_KB;
   LL_PDL_WAIT();   // q and the new keys and values come from the kernel before
   LL_PDL_TRIGGER();
   bool dead = false;
 
   if (warp == 0) {
     // ------------------------------ loads ------------------------------
+    // Lane b < boxes owns the b-th box (page, or part of a page) of every block: it looks its page up
+    // one block ahead and issues that box's copies; lane 0 also does the waiting and the byte counts.
     if (lane == 0) {
       at_mbar_expect_tx(q_full, (unsigned)(HB * 64 * p.group * p.tpb * 2));
       for (int h = 0; h < HB; ++h)
         at_tma_3d(at_smem(q_s) + h * (Q_BYTES / HB), &qmap, h * 64, kvh * p.group, tok0, q_full);
-      const int* bt = p.block_table + (size_t)slot * p.bt_stride;
-      const int boxes = AT_KB / p.box_rows;
-      for (int j = 0; j < nblk; ++j) {
-        const int s = j % AT_KS;
-        at_mbar_wait(kv_empty0 + 8 * s, (unsigned)(((j / AT_KS) & 1) ^ 1), p.status, dead);
-        at_mbar_expect_tx(kv_full0 + 8 * s, STAGE_BYTES);
-        const unsigned k_dst = at_smem(kv_s) + s * STAGE_BYTES, v_dst = k_dst + KV_BYTES;
-        for (int b = 0; b < boxes; ++b) {
-          const int kp = (kb_lo + j) * AT_KB + b * p.box_rows;
-          const int lp = kp / p.page_size;
-          int page = lp < p.bt_stride ? bt[lp] : -1;
-          if (page < 0 || page >= p.num_pages) page = 0;   // given back or beyond the context: masked below
-          const int row = (page * p.nkv + kvh) * p.page_size + kp % p.page_size;
-          for (int h = 0; h < HB; ++h) {
-            at_tma_2d(k_dst + h * (KV_BYTES / HB) + b * p.box_rows * 128, &kmap, h * 64, row, kv_full0 + 8 * s);
-            at_tma_2d(v_dst + h * (KV_BYTES / HB) + b * p.box_rows * 128, &vmap, h * 64, row, kv_full0 + 8 * s);
-          }
-        }
+    }
+    const int* bt = p.block_table + (size_t)slot * p.bt_stride;
+    const int boxes = AT_KB / p.box_rows;
+    auto page_of = [&](int j) -> int {   // cache row of this lane's box of block j
+      const int kp = (kb_lo + j) * AT_KB + lane * p.box_rows;
+      const int lp = kp / p.page_size;
+      int page = (lane < boxes && j < nblk && lp < p.bt_stride) ? bt[lp] : -1;
+      if (page < 0 || page >= p.num_pages) page = 0;   // given back or beyond the context: masked below
+      return (page * p.nkv + kvh) * p.page_size + kp % p.page_size;
+    };
+    // order of the copies: K(0), then K(j + 1) before V(j), the order in which the MMAs want them
+    auto load = [&](int j, int row, bool is_v) {
+      const int s = j % AT_KS;
+      const unsigned full = (is_v ? v_full0 : k_full0) + 8 * s;
+      if (lane == 0) {
+        at_mbar_wait((is_v ? v_empty0 : k_empty0) + 8 * s, (unsigned)(((j / AT_KS) & 1) ^ 1), p.status, dead);
+        at_mbar_expect_tx(full, KV_BYTES);
       }
+      __syncwarp();
+      if (lane < boxes) {
+        const unsigned dst = at_smem(kv_s) + s * STAGE_BYTES + (is_v ? KV_BYTES : 0) + lane * p.box_rows * 128;
+        for (int h = 0; h < HB; ++h) at_tma_2d(dst + h * (KV_BYTES / HB), is_v ? &vmap : &kmap, h * 64, row, full);
+      }
+    };
+    int row_cur = page_of(0);
+    load(0, row_cur, false);
+    for (int j = 0; j < nblk; ++j) {
+      const int row_next = page_of(j + 1);
+      if (j + 1 < nblk) load(j + 1, row_next, false);
+      load(j, row_cur, true);
+      row_cur = row_next;
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issue ------------------------------
     if (lane == 0) {
       auto mma_s = [&](int j) {   // S[j % 2] = Q K(j)^T
         const int s = j % AT_KS, b = j & 1;
-        at_mbar_wait(kv_full0 + 8 * s, (unsigned)((j / AT_KS) & 1), p.status, dead);
+        at_mbar_wait(k_full0 + 8 * s, (unsigned)((j / AT_KS) & 1), p.status, dead);
         at_mbar_wait(s_empty0 + 8 * b, (unsigned)(((j >> 1) & 1) ^ 1), p.status, dead);
         AT_FENCE_AFTER();
         const unsigned k_addr = at_smem(kv_s) + s * STAGE_BYTES;
@@ -262,23 +299,24 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
           at_mma(tmem_s + b * AT_KB, at_desc_k(at_smem(q_s) + off), at_desc_k(k_addr + koff), IDESC_S, k16 > 0 ? 1u : 0u);
         }
         at_commit(s_full0 + 8 * b);
+        at_commit(k_empty0 + 8 * s);   // the K stage is free once these MMAs have read it
       };
       at_mbar_wait(q_full, 0, p.status, dead);
       mma_s(0);
       for (int j = 0; j < nblk; ++j) {
         if (j + 1 < nblk) mma_s(j + 1);
-        const int s = j % AT_KS, b = j & 1;
-        at_mbar_wait(p_full0 + 8 * b, (unsigned)((j >> 1) & 1), p.status, dead);
-        at_mbar_wait(pv_empty0 + 8 * b, (unsigned)(((j >> 1) & 1) ^ 1), p.status, dead);
+        const int s = j % AT_KS;
+        at_mbar_wait(v_full0 + 8 * s, (unsigned)((j / AT_KS) & 1), p.status, dead);
+        at_mbar_wait(p_full, (unsigned)(j & 1), p.status, dead);
         AT_FENCE_AFTER();
         const unsigned v_addr = at_smem(kv_s) + s * STAGE_BYTES + KV_BYTES;
-        const unsigned p_addr = at_smem(p_s) + b * P_BYTES;
+        const unsigned p_addr = at_smem(p_s);
 #pragma unroll
         for (int k16 = 0; k16 < AT_KB / 16; ++k16)   // 16 keys a step: 32 bytes along P's rows, 2048 bytes down V
-          at_mma(tmem_pv + b * HD, at_desc_k(p_addr + k16 * 32), at_desc_mn(v_addr + k16 * 2048, KV_BYTES / HB), IDESC_PV,
-                 k16 > 0 ? 1u : 0u);
-        at_commit(pv_full0 + 8 * b);
-        at_commit(kv_empty0 + 8 * s);
+          at_mma(tmem_o, at_desc_k(p_addr + k16 * 32), at_desc_mn(v_addr + k16 * 2048, KV_BYTES / HB), IDESC_PV,
+                 (j > 0 || k16 > 0) ? 1u : 0u);
+        at_commit(pv_done);            // P may be written again; O holds the blocks up to j
+        at_commit(v_empty0 + 8 * s);
       }
     }
   } else {
@@ -290,26 +328,7 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
     const int prow = row_ok ? pos0 + t : -1;                                  // position of the row's token
     const int lo_row = (p.window > 0 && prow >= 0) ? max(0, prow - p.window + 1) : 0;
     const unsigned lane_addr = (unsigned)(32 * ew) << 16;
-    float o[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
-
-    auto add_pv = [&](int j, float alpha) {   // o = o * alpha + PV(j)
-      const int b = j & 1;
-      at_mbar_wait(pv_full0 + 8 * b, (unsigned)((j >> 1) & 1), p.status, dead);
-      AT_FENCE_AFTER();
-#pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
-        float v[32];
-        at_ld32(tmem_pv + lane_addr + b * HD + c0, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, v[i]);
-      }
-      AT_FENCE_BEFORE();
-      __syncwarp();
-      if (lane == 0) at_mbar_arrive(pv_empty0 + 8 * b);
-    };
+    float m_ref = -INFINITY, l_run = 0.f;   // reference maximum (scaled, log2 units) and sum against it
 
     for (int j = 0; j < nblk; ++j) {
       const int b = j & 1;
@@ -329,57 +348,77 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
       AT_FENCE_BEFORE();
       __syncwarp();
       if (lane == 0) at_mbar_arrive(s_empty0 + 8 * b);
-      // mask by selection, scale, running maximum
-      const bool need_mask = (k0 + AT_KB - 1 > prow) || (k0 < lo_row);
-      float mx = -INFINITY;
+      // mask by selection; maximum of the row's part
+      if ((k0 + AT_KB - 1 > prow) || (k0 < lo_row)) {
 #pragma unroll
-      for (int i = 0; i < AT_KB; ++i) {
-        float x = sv[i] * p.scale_log2;
-        if (need_mask && (k0 + i > prow || k0 + i < lo_row)) x = -INFINITY;
-        sv[i] = x;
-        mx = fmaxf(mx, x);
+        for (int i = 0; i < AT_KB; ++i)
+          if (k0 + i > prow || k0 + i < lo_row) sv[i] = -INFINITY;
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);   // m_run = -inf: 0
-      float sum = 0.f;
-      // P row: 64 bfloat16 = 128 bytes = 8 pieces of 16 bytes, piece c at (c ^ (r & 7)) of the swizzled row
-      unsigned char* prow_s = p_s + b * P_BYTES + r * 128;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        unsigned w[4];
+      for (int i = 0; i < AT_KB; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
+      const float mxs = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      const bool grow = mxs > m_ref + 8.0f;          // also the first keys a row sees (m_ref = -inf)
+      const float factor = grow ? exp2f(m_ref - mxs) : 1.0f;   // m_ref = -inf: 0 (O and the sum are 0 then)
+      if (grow) m_ref = mxs;
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      // the row of P in registers: 64 bfloat16 = 8 pieces of 16 bytes
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      unsigned pw[32];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float e0 = exp2f(sv[8 * c + 2 * i] - m_use), e1 = exp2f(sv[8 * c + 2 * i + 1] - m_use);
-          const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-          // the sum is of the rounded values, the ones PV is made from
-          sum += __bfloat162float(h.x) + __bfloat162float(h.y);
-          w[i] = *reinterpret_cast<const unsigned*>(&h);
+      for (int i = 0; i < 32; ++i) {
+        const float e0 = exp2f(fmaf(sv[2 * i], p.scale_log2, -m_use));
+        const float e1 = exp2f(fmaf(sv[2 * i + 1], p.scale_log2, -m_use));
+        sum4[i & 3] += e0 + e1;
+        const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+        pw[i] = *reinterpret_cast<const unsigned*>(&h);
+      }
+      l_run = l_run * factor + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      // the block before must be in O, and P read, before either is touched
+      if (j > 0) {
+        at_mbar_wait(pv_done, (unsigned)((j - 1) & 1), p.status, dead);
+        AT_FENCE_AFTER();
+        if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            float v[32];
+            at_ld32(tmem_o + lane_addr + c0, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= factor;
+            at_st32(tmem_o + lane_addr + c0, v);
+          }
         }
-        *reinterpret_cast<uint4*>(prow_s + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      l_run = l_run * alpha + sum;
-      m_run = m_new;
+      // piece c of the row goes to (c ^ (r & 7)) of the swizzled 128-byte row
+      unsigned char* prow_s = p_s + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(prow_s + ((c ^ (r & 7)) << 4)) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor cores
+      AT_FENCE_BEFORE();                                             // and so is the rescaled O
       __syncwarp();
-      if (lane == 0) at_mbar_arrive(p_full0 + 8 * b);
-      // PV of the block before arrives while this block's PV is being made
-      if (j > 0) add_pv(j - 1, alpha_prev);
-      alpha_prev = alpha;
+      if (lane == 0) at_mbar_arrive(p_full);
     }
-    add_pv(nblk - 1, alpha_prev);
+    at_mbar_wait(pv_done, (unsigned)((nblk - 1) & 1), p.status, dead);
+    AT_FENCE_AFTER();
     // ---- normalise; rows leave through shared memory (the Q tile is no longer read) ----
     const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
     unsigned char* orow = q_s + r * (HD * 2);
 #pragma unroll
-    for (int c = 0; c < HD / 8; ++c) {
-      unsigned w[4];
+    for (int c0 = 0; c0 < HD; c0 += 32) {
+      float v[32];
+      at_ld32(tmem_o + lane_addr + c0, v);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const __nv_bfloat162 h = __floats2bfloat162_rn(o[8 * c + 2 * i] * inv, o[8 * c + 2 * i + 1] * inv);
-        w[i] = *reinterpret_cast<const unsigned*>(&h);
+      for (int cc = 0; cc < 4; ++cc) {
+        const int c = c0 / 8 + cc;
+        unsigned w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * cc + 2 * i] * inv, v[8 * cc + 2 * i + 1] * inv);
+          w[i] = *reinterpret_cast<const unsigned*>(&h);
+        }
+        *reinterpret_cast<uint4*>(orow + (((c & ~7) | ((c ^ r) & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      *reinterpret_cast<uint4*>(orow + (((c & ~7) | ((c ^ r) & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const int e = tid - 64;
@@ -474,7 +513,7 @@ extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, lon
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return (int)cudaErrorInvalidValue;
   }
-  const size_t smem = 1024 + (size_t)128 * hd * 2 + (size_t)AT_KS * 2 * AT_KB * hd * 2 + 2 * 128 * AT_KB * 2 + 256;
+  const size_t smem = (size_t)128 * hd * 2 + (size_t)AT_KS * 2 * AT_KB * hd * 2 + 128 * AT_KB * 2 + 256;
   dim3 grid(row_blocks, nkv);
   if (hd == 64) {
     cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -32,6 +32,8 @@ _STATUS_TEXT = {
     2: "a cache slot outside the pool",
     3: "a block-table entry outside the pool",
     4: "a position outside the position table",
+    5: "a bounded wait inside a kernel (TMA or tensor-core pipeline) that ran out",
+    6: "a shared-memory window that is not aligned as the kernel needs",
 }
 
 

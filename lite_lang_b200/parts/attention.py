@@ -148,8 +148,8 @@ class GQAttention(Mixer):
         """Attention of the step's tokens over the cache plane; picks the kernels by shape.
 
         Single-token entries come first in a step: they go to the decode kernel (keys split over a
-        cluster of CTAs), the portions of prompts after them to the prefill kernel (128 query rows a
-        CTA share the keys through shared memory)."""
+        cluster of CTAs), the portions of prompts after them to a prefill kernel (128 query rows a
+        CTA share the keys: the tcgen05 one where it takes the shape, else the mma.sync one)."""
         if ops.attn_mma_supported(qkv.dtype, self.head_dim, cache.page_size, qkv.stride(0)):
             n_single = step.num_single
             n_rest = step.num_entries - n_single
@@ -169,15 +169,26 @@ class GQAttention(Mixer):
                                  step.ctx_len, step.req_slot, n_single, blocks, *args, nsplit, None, None,
                                  step.status, all_single=single, cluster=nsplit > 1, warps=warps)
             if n_rest > 0:
-                key = ("attn_prefill", self.num_heads, self.num_kv_heads)
-                blocks = step.scratch.get(key)
-                if blocks is None:
-                    group = self.num_heads // self.num_kv_heads
-                    blocks = sum((len(e.tokens) * group + 127) // 128 for e in step.entries[n_single:])
-                    step.scratch[key] = blocks
-                ops.attn_prefill(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table,
-                                 step.cu_q[n_single:], step.ctx_len[n_single:], step.req_slot[n_single:], n_rest,
-                                 blocks, *args, step.status)
+                group = self.num_heads // self.num_kv_heads
+                rest = (step.cu_q[n_single:], step.ctx_len[n_single:], step.req_slot[n_single:], n_rest)
+                if ops.TC_ENABLED and ops.attn_prefill_tc_supported(qkv.dtype, self.head_dim, cache.page_size,
+                                                                    qkv.stride(0), group):
+                    # tcgen05: S and O in tensor memory, K and V page by page through TMA
+                    key = ("attn_prefill_tc", group)
+                    blocks = step.scratch.get(key)
+                    if blocks is None:
+                        blocks = step.scratch[key] = ops.attn_prefill_tc_blocks(
+                            (len(e.tokens) for e in step.entries[n_single:]), group)
+                    ops.attn_prefill_tc(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, *rest, blocks,
+                                        *args, step.status)
+                else:
+                    key = ("attn_prefill", group)
+                    blocks = step.scratch.get(key)
+                    if blocks is None:
+                        blocks = sum((len(e.tokens) * group + 127) // 128 for e in step.entries[n_single:])
+                        step.scratch[key] = blocks
+                    ops.attn_prefill(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, *rest, blocks,
+                                     *args, step.status)
             return
         ops.paged_attention_generic(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.token_req,
                                     step.req_slot, step.positions, qkv.shape[0], self.num_heads, self.num_kv_heads,
