@@ -113,9 +113,9 @@ class CacheStorage:
                     stage[i].copy_(torch.from_numpy(host[r]))
                     dev[r].copy_(stage[i], non_blocking=True)
             if self.device.type == "cuda":
-                ev = torch.cuda.Event()
-                ev.record()
-                self._stage_events[g][turn] = ev
+                if self._stage_events[g][turn] is None:
+                    self._stage_events[g][turn] = torch.cuda.Event()
+                self._stage_events[g][turn].record()
 
     def paged_view(self, group: int, plane: int, slot_map: Optional[torch.Tensor], writable: bool) -> PagedKVView:
         return PagedKVView(self.k[group][plane], self.v[group][plane], self.block_table[group],

@@ -90,8 +90,11 @@ class BatchBuilder:
         off, size = self._off[name]
         return buf[off:off + (size if n is None else n)]
 
-    def build(self, entries: Sequence[StepEntry], pad_entries: Optional[int] = None) -> StepBatch:
+    def build(self, entries: Sequence[StepEntry], pad_entries: Optional[int] = None,
+              views: bool = True) -> StepBatch:
         """Fill the buffers for ``entries`` and start their copy to the device.
+
+        ``views=False`` leaves out the device views of the arrays (a replayed graph already holds them).
 
         Single-token entries come first in the arrays; ``logit_rows`` keeps the
         caller's order of entries and of their ``want`` lists.  ``pad_entries``
@@ -100,11 +103,14 @@ class BatchBuilder:
         """
         m = self.manager
         ps = m.page_size
-        order = sorted(range(len(entries)), key=lambda i: 0 if len(entries[i].tokens) == 1 else 1)
-        arranged = [entries[i] for i in order]
-        n_real = len(arranged)
-        t_real = sum(len(e.tokens) for e in arranged)
-        num_single = sum(1 for e in arranged if len(e.tokens) == 1)
+        n_real = len(entries)
+        num_single = sum(1 for e in entries if len(e.tokens) == 1)
+        if num_single == n_real:
+            order, arranged, t_real = range(n_real), list(entries), n_real
+        else:
+            order = sorted(range(n_real), key=lambda i: 0 if len(entries[i].tokens) == 1 else 1)
+            arranged = [entries[i] for i in order]
+            t_real = sum(len(e.tokens) for e in arranged)
         n_all, t_all = n_real, t_real
         if pad_entries is not None:
             if num_single != n_real:
@@ -177,16 +183,17 @@ class BatchBuilder:
             t += q
             max_q = max(max_q, q)
             max_kv = max(max_kv, c + q)
-        for i in range(n_real, n_all):        # padding entries
-            cu_q[i] = t
-            ctx_len[i] = 0
-            req_slot[i] = -1
-            token_ids[t] = 0
-            positions[t] = 0
-            token_req[t] = i
+        if n_all > n_real:                    # padding entries, one token each
+            pad = n_all - n_real
+            cu_q[n_real:n_all] = np.arange(t, t + pad, dtype=np.int32)
+            ctx_len[n_real:n_all] = 0
+            req_slot[n_real:n_all] = -1
+            token_ids[t:t + pad] = 0
+            positions[t:t + pad] = 0
+            token_req[t:t + pad] = np.arange(n_real, n_all, dtype=np.int32)
             for g in m.paged_ids:
-                slot_maps[g][t] = -1
-            t += 1
+                slot_maps[g][t:t + pad] = -1
+            t += pad
         cu_q[n_all] = t
 
         new_index = {orig: i for i, orig in enumerate(order)}
@@ -204,9 +211,9 @@ class BatchBuilder:
 
         self.dev.copy_(host, non_blocking=True)
         if self.device.type == "cuda":
-            ev = torch.cuda.Event()
-            ev.record()
-            self._events[turn] = ev
+            if self._events[turn] is None:
+                self._events[turn] = torch.cuda.Event()
+            self._events[turn].record()
 
         b = StepBatch()
         b.num_tokens, b.num_entries = t_all, n_all
@@ -214,6 +221,12 @@ class BatchBuilder:
         b.num_single = num_single if pad_entries is None else n_all
         b.num_logits = num_logits if pad_entries is None else n_all
         b.real_logits = num_logits
+        b.status = self.status
+        b.max_q_len, b.max_kv_len = max_q, max_kv
+        b.entries = arranged
+        b.scratch = {}
+        if not views:
+            return b
         d = self.dev
         b.token_ids = self._view(d, "token_ids", t_all)
         b.positions = self._view(d, "positions", t_all)
@@ -223,8 +236,4 @@ class BatchBuilder:
         b.req_slot = self._view(d, "req_slot", n_all)
         b.logit_rows = self._view(d, "logit_rows", b.num_logits)
         b.slot_maps = {g: self._view(d, f"slot_map{g}", t_all) for g in m.paged_ids}
-        b.status = self.status
-        b.max_q_len, b.max_kv_len = max_q, max_kv
-        b.entries = arranged
-        b.scratch = {}
         return b

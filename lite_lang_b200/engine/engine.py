@@ -126,7 +126,7 @@ class Engine:
             return []
         entries = []
         for p in plan:
-            toks = p.request.tokens[p.start:p.start + p.count]
+            toks = p.request.token_slice(p.start, p.count)
             entries.append(StepEntry(p.request.slot, toks, (p.count - 1,) if p.samples else ()))
         logits = self.runner.step(entries)
         sampled: List[Optional[int]] = [None] * len(plan)

@@ -141,7 +141,7 @@ class ModelRunner:
         if got is None:
             got = self._capture(bucket)
         graph, logits = got
-        batch = self.single_builder.build(entries, pad_entries=bucket)
+        batch = self.single_builder.build(entries, pad_entries=bucket, views=False)
         graph.replay()
         self.graph_replays += 1
         if batch.real_logits == 0:

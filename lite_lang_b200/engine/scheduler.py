@@ -48,7 +48,7 @@ from ..sampling.sampler import SamplingParams
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 
 
-@dataclass
+@dataclass(eq=False)      # a request is itself, not its field values: membership tests stay cheap
 class Request:
     id: int
     prompt: List[int]
@@ -66,6 +66,15 @@ class Request:
     @property
     def tokens(self) -> List[int]:
         return self.prompt + self.output
+
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """tokens[start:start + count] without building the whole list."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.output[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.output[:start + count - n]
 
     @property
     def length(self) -> int:
