@@ -215,7 +215,7 @@ def e2e_decode(engine, batch, steps, warmup):
             r.max_new_tokens = len(r.output) + 1
         engine.step()
     h2d = engine.runner.single_builder.total * 4
-    d2h = engine._result_host.numel() * 4
+    d2h = engine._result_hosts[0].numel() * 4
     return (n1 - n0) / dt, h2d, d2h, dt / steps * 1e3
 
 

@@ -34,3 +34,24 @@ extern "C" int ll_embed_gather(int dtype, void* out, const void* table, const in
                                      (const T*)table, ids, hidden, vocab, status));
   return LL_LAUNCH_RESULT();
 }
+
+// Token ids that are still on the device: ids[i] = results[feed[i]] where feed[i] >= 0.  A decode step that
+// is launched before the host has seen the tokens sampled by the step before takes them from that step's
+// result buffer this way.  A feed index outside [0, max_results) leaves ids[i] as the host wrote it.
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ feed, const int* __restrict__ results,
+                                   int n, int max_results) {
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const int f = feed[i];
+    if (f >= 0 && f < max_results) ids[i] = results[f];
+  }
+}
+
+extern "C" int ll_feed_tokens(int* ids, const int* feed, const int* results, int n, int max_results,
+                              cudaStream_t stream) {
+  if (n <= 0) return 0;
+  ll_launch(feed_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, feed, results, n, max_results);
+  return LL_LAUNCH_RESULT();
+}

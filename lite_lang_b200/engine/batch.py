@@ -29,6 +29,8 @@ class StepEntry:
     slot: int                          # request slot in the cache manager
     tokens: Sequence[int]              # its next tokens (at least one)
     want: Sequence[int] = ()           # places among `tokens` whose logits are asked for
+    feed: int = -1                     # >= 0 (single-token entries only): the token is not known to the host yet,
+                                       # it is the feed-th token sampled by the step before and is taken on the device
 
 
 class StepBatch(StepView):
@@ -43,6 +45,8 @@ class StepBatch(StepView):
     token_ids: torch.Tensor            # int32 [num_tokens]
     positions: torch.Tensor            # int32 [num_tokens] position of each token in its request
     token_req: torch.Tensor            # int32 [num_tokens] entry index of each token
+    feed: torch.Tensor                 # int32 [num_tokens] place in the last step's sampled tokens, or -1
+    has_feed: bool                     # some token of the step is taken from the last step's results
     cu_q: torch.Tensor                 # int32 [num_entries + 1] first token of each entry
     ctx_len: torch.Tensor              # int32 [num_entries] tokens cached before this step
     req_slot: torch.Tensor             # int32 [num_entries] request slot (-1: padding)
@@ -72,7 +76,7 @@ class BatchBuilder:
         T, R = _align(self.max_tokens), _align(self.max_entries + 1)
         self._off: Dict[str, Tuple[int, int]] = {}
         off = 0
-        for name, size in (("token_ids", T), ("positions", T), ("token_req", T), ("logit_rows", T),
+        for name, size in (("token_ids", T), ("positions", T), ("token_req", T), ("logit_rows", T), ("feed", T),
                            ("cu_q", R), ("ctx_len", R), ("req_slot", R)):
             self._off[name] = (off, size)
             off += size
@@ -137,6 +141,8 @@ class BatchBuilder:
         token_ids, positions, token_req = hv("token_ids"), hv("positions"), hv("token_req")
         cu_q, ctx_len, req_slot, logit_rows = hv("cu_q"), hv("ctx_len"), hv("req_slot"), hv("logit_rows")
         slot_maps = {g: hv(f"slot_map{g}") for g in m.paged_ids}
+        feed = hv("feed")
+        feed[:t_all] = -1
 
         t = 0
         max_q, max_kv = 1, 1
@@ -149,6 +155,7 @@ class BatchBuilder:
             ctx_len[:n_real] = ctx
             req_slot[:n_real] = slots
             token_ids[:n_real] = np.fromiter((e.tokens[0] for e in arranged), dtype=np.int32, count=n_real)
+            feed[:n_real] = np.fromiter((e.feed for e in arranged), dtype=np.int32, count=n_real)
             positions[:n_real] = ctx
             token_req[:n_real] = cu_q[:n_real]
             for g in m.paged_ids:
@@ -166,6 +173,10 @@ class BatchBuilder:
             q = len(e.tokens)
             if q == 0:
                 raise ValueError("an entry without tokens")
+            if e.feed >= 0:
+                if q != 1:
+                    raise ValueError("only a single-token entry can take its token from the step before")
+                feed[t] = e.feed
             c = m.length(e.slot)
             starts.append(t)
             cu_q[i] = t
@@ -225,12 +236,14 @@ class BatchBuilder:
         b.max_q_len, b.max_kv_len = max_q, max_kv
         b.entries = arranged
         b.scratch = {}
+        b.has_feed = bool((feed[:t_all] >= 0).any())
         if not views:
             return b
         d = self.dev
         b.token_ids = self._view(d, "token_ids", t_all)
         b.positions = self._view(d, "positions", t_all)
         b.token_req = self._view(d, "token_req", t_all)
+        b.feed = self._view(d, "feed", t_all)
         b.cu_q = self._view(d, "cu_q", n_all + 1)
         b.ctx_len = self._view(d, "ctx_len", n_all)
         b.req_slot = self._view(d, "req_slot", n_all)

@@ -26,7 +26,7 @@ from ..weights.random_init import random_fetch
 from .batch import StepEntry
 from .model import CausalLM
 from .runner import ModelRunner
-from .scheduler import PlannedEntry, Request, Scheduler
+from .scheduler import RUNNING, PlannedEntry, Request, Scheduler
 
 _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -37,6 +37,15 @@ def cache_bytes_per_page(model: CausalLM, page_size: int, elt: int) -> int:
         if g.kind == "paged":
             n += g.planes * 2 * g.num_kv_heads * page_size * g.head_dim * elt
     return n
+
+
+class _Launched:
+    """A step that is on the stream: its plan and where its results arrive."""
+
+    __slots__ = ("plan", "rows", "host", "event")
+
+    def __init__(self, plan, rows, host, event):
+        self.plan, self.rows, self.host, self.event = plan, rows, host, event
 
 
 class Engine:
@@ -87,8 +96,13 @@ class Engine:
                                    self.cfg.busy_scale, self.cfg.preempt_strategy, self.cfg.max_output_length)
         self._next_id = 0
         self._tokenizer = None
-        pinned = True
-        self._result_host = torch.zeros(self.cfg.max_batch_size + 1, dtype=torch.int32, pin_memory=pinned)
+        # results of up to two steps in flight (tokens and the status word), read one step at a time
+        self._result_hosts = [torch.zeros(self.cfg.max_batch_size + 1, dtype=torch.int32, pin_memory=True)
+                              for _ in range(3)]
+        self._result_events = [torch.cuda.Event() for _ in self._result_hosts]
+        self._result_turn = 0
+        self._ahead: Optional[_Launched] = None
+        self._pipeline = os.environ.get("LITE_LANG_B200_PIPELINE", "1") != "0"
 
     # ------------------------------------------------------------------
     def tokenizer(self):
@@ -118,18 +132,37 @@ class Engine:
         return req
 
     def step(self) -> List[Request]:
-        """One scheduler step: plan, run, sample, commit.  Returns the requests that finished."""
-        plan = self.scheduler.plan()
-        if not plan:
-            if self.scheduler.has_work():
-                raise RuntimeError("the scheduler has work but could plan nothing")
-            return []
+        """One scheduler step: plan, run, sample, commit.  Returns the requests that finished.
+
+        While the step's kernels run, the step after it is launched as well whenever the scheduler
+        can decide it without this step's tokens (``Scheduler.plan_ahead``: a pure decode step);
+        its token ids are taken on the device from this step's sampled tokens.  So the GPU does not
+        wait for the host between decode steps.  A request that ends with this step's token (an eos
+        id) is simply ignored in the step that was launched ahead."""
+        cur = self._ahead
+        self._ahead = None
+        if cur is not None and not any(p.request.status == RUNNING for p in cur.plan):
+            cur = None                       # everyone in it has ended meanwhile: nothing to collect
+        if cur is None:
+            plan = self.scheduler.plan()
+            if not plan:
+                if self.scheduler.has_work():
+                    raise RuntimeError("the scheduler has work but could plan nothing")
+                return []
+            cur = self._launch(plan, 0)
+        if self.cfg.cuda_graphs and self._pipeline:
+            nxt = self.scheduler.plan_ahead(cur.plan)
+            if nxt is not None:
+                self._ahead = self._launch(nxt, 1)
+        return self._collect(cur)
+
+    def _launch(self, plan: List[PlannedEntry], ahead: int) -> "_Launched":
+        """Put a planned step on the stream: model, sampling, copy of the results to the host."""
         entries = []
         for p in plan:
-            toks = p.request.token_slice(p.start, p.count)
-            entries.append(StepEntry(p.request.slot, toks, (p.count - 1,) if p.samples else ()))
+            toks = [0] if p.feed >= 0 else p.request.token_slice(p.start, p.count)
+            entries.append(StepEntry(p.request.slot, toks, (p.count - 1,) if p.samples else (), p.feed))
         logits = self.runner.step(entries)
-        sampled: List[Optional[int]] = [None] * len(plan)
         rows = [i for i, p in enumerate(plan) if p.samples]
         if rows:
             temps, unis = [], []
@@ -138,17 +171,26 @@ class Engine:
                 greedy = r.params.greedy
                 temps.append(0.0 if greedy else float(r.params.temperature))
                 seed = r.params.seed if r.params.seed is not None else self.cfg.seed
-                unis.append(0.0 if greedy else uniform_for(seed, r.id, len(r.output)))
+                # (a step launched ahead samples the token after the one that is still on its way)
+                unis.append(0.0 if greedy else uniform_for(seed, r.id, len(r.output) + ahead))
             self.sampler.sample(logits, temps, unis)
         # one copy brings the sampled tokens and the kernels' status word
-        self._result_host.copy_(self.runner.result_buf, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        host = self._result_host.numpy()
+        turn = self._result_turn
+        self._result_turn = (turn + 1) % len(self._result_hosts)
+        host = self._result_hosts[turn]
+        host.copy_(self.runner.result_buf, non_blocking=True)
+        self._result_events[turn].record()
+        return _Launched(plan, rows, host, self._result_events[turn])
+
+    def _collect(self, launched: "_Launched") -> List[Request]:
+        launched.event.synchronize()
+        host = launched.host.numpy()
         if host[-1] != 0:
             self.runner.check_status()
-        for k, i in enumerate(rows):
+        sampled: List[Optional[int]] = [None] * len(launched.plan)
+        for k, i in enumerate(launched.rows):
             sampled[i] = int(host[k])
-        return self.scheduler.commit(plan, sampled)
+        return self.scheduler.commit(launched.plan, sampled)
 
     def generate(self, prompts: Sequence[Union[str, Sequence[int]]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:

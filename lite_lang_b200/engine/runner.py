@@ -92,6 +92,8 @@ class ModelRunner:
             logits = self._step_graph(entries)
         else:
             batch = self.builder.build(entries)
+            if batch.has_feed:
+                ops.feed_tokens(batch.token_ids, batch.feed, self.result_buf[:m.max_requests])
             logits = self.model.forward(batch, self.storage)
         for e in entries:
             m.advance(e.slot, m.length(e.slot) + len(e.tokens))
@@ -111,8 +113,10 @@ class ModelRunner:
         batch.captured = True
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
+        results = self.result_buf[:self.manager.max_requests]
         with torch.cuda.stream(side):
             for _ in range(2):
+                ops.feed_tokens(batch.token_ids, batch.feed, results)
                 self.model.forward(batch, self.storage)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(self.device)
@@ -120,6 +124,8 @@ class ModelRunner:
         from ..csrc import build as _build
         before = _build.LAUNCHES
         with torch.cuda.graph(graph, pool=self._graph_pool):
+            # tokens that the host has not seen yet come from the last step's sampled results
+            ops.feed_tokens(batch.token_ids, batch.feed, results)
             logits = self.model.forward(batch, self.storage)
         self.graph_kernel_launches[bucket] = _build.LAUNCHES - before
         if self._graph_pool is None:

@@ -134,6 +134,7 @@ class PlannedEntry:
     start: int            # first token of the portion within request.tokens
     count: int
     samples: bool         # the portion ends the known tokens: its last logits give the next token
+    feed: int = -1        # >= 0: planned ahead; the (one) token is the feed-th token sampled by the step before
 
 
 class Scheduler:
@@ -285,6 +286,39 @@ class Scheduler:
             else:
                 self._preempt(_lifo(self.running)[0])
 
+    def plan_ahead(self, plan: Sequence[PlannedEntry]) -> Optional[List[PlannedEntry]]:
+        """The step after ``plan``, decided while ``plan`` still runs and its tokens are unknown.
+
+        Possible when the outcome of ``plan`` cannot change what comes next except by ending a
+        request: every running request samples in ``plan`` (so each will simply decode one more
+        token), nothing waits for admission, and the pages for one more token can be reserved
+        without making anyone leave.  Requests that reach their length limit with ``plan``'s token
+        are left out.  A request that ends for a reason only its token shows (an eos id) is in the
+        returned plan all the same; ``commit`` ignores it then.  None: decide after the step, as usual.
+        """
+        if self.waiting or not plan or not all(p.samples for p in plan):
+            return None
+        live = [(k, p) for k, p in enumerate(plan) if p.request.status == RUNNING]
+        if len(live) != len(self.running):
+            return None
+        m = self.manager
+        ahead: List[PlannedEntry] = []
+        for k, p in live:
+            req = p.request
+            # (the token of `plan` is not in req.output yet; one planned ahead before it may not be either)
+            known = p.start + p.count + 1 - len(req.prompt)  # output tokens once `plan` is committed
+            if known >= req.max_new_tokens or p.start + p.count + 1 >= m.max_model_len:
+                continue                  # ends with this step's token
+            ahead.append(PlannedEntry(req, p.start + p.count, 1, True, feed=k))
+        if not ahead or len(ahead) > self.budget:
+            return None
+        for q in ahead:
+            if not m.reserve(q.request.slot, q.start + 1):
+                return None               # pages already taken for others stay theirs and are used next step
+        self.counters["steps"] += 1
+        self.counters["tokens"] += len(ahead)
+        return ahead
+
     def _portion(self, req: Request, budget: int) -> Optional[PlannedEntry]:
         """The largest next portion of the request that the budget and the free pages allow."""
         m = self.manager
@@ -309,6 +343,8 @@ class Scheduler:
         done: List[Request] = []
         for p, tok in zip(plan, sampled):
             req = p.request
+            if req.status != RUNNING:
+                continue                  # planned ahead, but the request ended with the token before
             req.computed = p.start + p.count
             if not p.samples:
                 continue

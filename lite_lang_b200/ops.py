@@ -87,6 +87,16 @@ def embed_gather(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, stat
                 c_int(hidden), c_int(table.shape[0]), _ptr(status), _stream())
 
 
+def feed_tokens(ids: torch.Tensor, feed: torch.Tensor, results: torch.Tensor) -> None:
+    """ids[i] = results[feed[i]] where feed[i] >= 0: token ids sampled by the step before, taken on the device."""
+    _need_cuda(ids, feed, results)
+    for t, nm in ((ids, "ids"), (feed, "feed"), (results, "results")):
+        _i32(t, nm)
+    _need(feed.numel() >= ids.numel(), "feed_tokens: one feed index per token id")
+    core().call("ll_feed_tokens", _ptr(ids), _ptr(feed), _ptr(results), c_int(ids.numel()), c_int(results.numel()),
+                _stream())
+
+
 def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
     _need_cuda(out, x, weight)
     _f32(weight, "norm weight")

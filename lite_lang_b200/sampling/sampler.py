@@ -73,7 +73,9 @@ class Sampler:
         self.max_rows = max_rows
         self.out = out if out is not None else torch.zeros(max_rows, dtype=torch.int32, device=device)
         pinned = device.type == "cuda"
-        self._host = torch.zeros((2, max_rows), dtype=torch.float32, pin_memory=pinned)
+        # a ring of host buffers: a step may be prepared while the copy of the step before has not run yet
+        self._hosts = [torch.zeros((2, max_rows), dtype=torch.float32, pin_memory=pinned) for _ in range(4)]
+        self._turn = 0
         self._dev = torch.zeros((2, max_rows), dtype=torch.float32, device=device)
 
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float], uniforms: Sequence[float]) -> torch.Tensor:
@@ -84,9 +86,11 @@ class Sampler:
         if all(t <= 0 for t in temperatures):
             ops.sample(logits, self.out, None, None, n)
             return self.out[:n]
-        h = self._host.numpy()
+        host = self._hosts[self._turn]
+        self._turn = (self._turn + 1) % len(self._hosts)
+        h = host.numpy()
         h[0, :n] = np.asarray(temperatures, dtype=np.float32)
         h[1, :n] = np.asarray(uniforms, dtype=np.float32)
-        self._dev.copy_(self._host, non_blocking=True)
+        self._dev.copy_(host, non_blocking=True)
         ops.sample(logits, self.out, self._dev[0], self._dev[1], n)
         return self.out[:n]

@@ -142,6 +142,45 @@ def test_eos_ends_a_request():
     assert out == free
 
 
+def test_steps_launched_ahead_give_the_same_tokens_and_end_requests_on_time():
+    """Decode steps are launched before the host has seen the tokens of the step before (their token ids
+    are fed on the device).  Requests that end by length, by an eos id in the middle, and a request that
+    arrives while others decode must come out as without the pipelining."""
+    from lite_lang_b200 import SamplingParams
+    folder = make_model_folder("C", scales={"matrix": 0.08})
+    cfg, w = P.read_model_folder(folder)
+    prompts = [random_tokens(n, cfg["vocab_size"], 90 + i) for i, n in enumerate([12, 30, 5, 19])]
+    plain = [P.greedy_generate(cfg, w, p, 14) for p in prompts]
+    eos = plain[1][6]                                   # request 1 ends in the middle by this id
+    with open(os.path.join(folder, "config.json"), "w") as fh:
+        json.dump(dict(cfg, eos_token_id=eos), fh)
+    params = [SamplingParams(temperature=0.0, max_new_tokens=n) for n in (14, 14, 3, 9)]
+    late = random_tokens(8, cfg["vocab_size"], 99)
+
+    def run(pipeline):
+        eng = engine(folder, "float32", "C", max_output_length=16)
+        eng._pipeline = pipeline
+        reqs = [eng.add_request(p, sp) for p, sp in zip(prompts, params)]
+        steps = 0
+        while eng.scheduler.has_work():
+            eng.step()
+            steps += 1
+            if steps == 4:                              # arrives while the others decode
+                reqs.append(eng.add_request(late, SamplingParams(temperature=0.7, seed=5, max_new_tokens=6,
+                                                                 ignore_eos=True)))
+        assert eng.manager.num_free_pages() == eng.manager.total_pages()
+        eng.manager.check_invariants()
+        return [list(r.output) for r in reqs], [r.finish_reason for r in reqs], eng.stats()
+
+    out_a, why_a, st_a = run(True)
+    out_b, why_b, st_b = run(False)
+    assert out_a == out_b and why_a == why_b
+    assert why_a[:4] == ["length", "eos", "length", "length"] or eos in plain[0][:14] or eos in plain[3][:9]
+    assert out_a[1] == plain[1][:plain[1].index(eos) + 1]
+    assert out_a[2] == plain[2][:3]
+    assert st_a["graph_replays"] > 0
+
+
 def test_command_line():
     folder = make_model_folder("A", scales={"matrix": 0.08})
     cfg, w = P.read_model_folder(folder)

@@ -217,3 +217,64 @@ def test_random_load_always_drains(seed, strategy):
         if r.finish_reason == "length":
             assert len(r.output) == r.max_new_tokens
     assert m.num_free_pages() == m.total_pages() and m.num_free_slots == 3
+
+
+# ---------------------------------------------------------------- the step after the running one
+def _decode_state(n=3, max_new=(6, 6, 6), eos=((), (), ())):
+    m, s = make(num_pages=32, budget=8)
+    reqs = [req(i, 3 + i, max_new[i], eos[i]) for i in range(n)]
+    for r in reqs:
+        s.add(r)
+    run_step(m, s)                      # prompts; everyone has a first token
+    return m, s, reqs
+
+
+def test_plan_ahead_decides_a_decode_step_without_the_tokens():
+    m, s, reqs = _decode_state()
+    plan = s.plan()
+    ahead = s.plan_ahead(plan)
+    assert [(p.request.id, p.start, p.count, p.samples, p.feed) for p in ahead] == \
+        [(r.id, r.length, 1, True, k) for k, r in enumerate(reqs)]
+    # what the engine does: both steps advance the cache when launched, commits follow in order
+    for pl in (plan, ahead):
+        for p in pl:
+            m.advance(p.request.slot, m.length(p.request.slot) + p.count)
+    s.commit(plan, [7] * 3)
+    s.commit(ahead, [8] * 3)
+    assert all(r.output[-2:] == [7, 8] and r.computed == r.length - 1 for r in reqs)
+    m.check_invariants()
+
+
+def test_plan_ahead_leaves_out_who_ends_by_length_and_commit_ignores_who_ended_by_token():
+    m, s, reqs = _decode_state(max_new=(2, 6, 6), eos=((), (9,), ()))
+    plan = s.plan()                     # request 0 reaches its 2 tokens with this step
+    ahead = s.plan_ahead(plan)
+    assert [p.request.id for p in ahead] == [1, 2] and [p.feed for p in ahead] == [1, 2]
+    for pl in (plan, ahead):
+        for p in pl:
+            m.advance(p.request.slot, m.length(p.request.slot) + p.count)
+    done = s.commit(plan, [7, 9, 7])    # request 1 draws its eos id
+    assert {r.id for r in done} == {0, 1} and reqs[1].finish_reason == "eos"
+    done = s.commit(ahead, [5, 5])      # the token that was computed ahead for request 1 is dropped
+    assert done == [] and reqs[1].output == [7, 9] and reqs[2].output[-2:] == [7, 5]
+    m.check_invariants()
+    assert s.plan_ahead(ahead) is not None      # request 2 alone goes on
+    s2 = s.plan_ahead([p for p in ahead])       # (asking twice reserves nothing twice)
+    assert s2 is not None
+    m.check_invariants()
+
+
+def test_plan_ahead_declines_when_the_outcome_matters():
+    m, s, reqs = _decode_state()
+    s.add(req(9, 4, 2))                 # someone waits: the next step may admit it
+    assert s.plan_ahead(s.plan()) is None
+    m, s, reqs = _decode_state()
+    plan = s.plan()
+    assert s.plan_ahead(plan[:2]) is None       # not every running request is in the step
+    # no page left for one more token: the usual path decides who leaves
+    m, s = make(num_pages=2, page_size=4, budget=8)
+    a = req(0, 7, 5)
+    s.add(a)
+    run_step(m, s)                      # 7 prompt tokens: pages full after one more token
+    plan = s.plan()
+    assert plan and s.plan_ahead(plan) is None
