@@ -149,6 +149,12 @@ struct AttnTcParams {
   int page_size, num_pages, window;
   int box_rows;                     // keys a K/V box: min(page_size, 64)
   float scale_log2;
+  // the key blocks of a row block may be split over up to nsplit CTAs (long contexts, few row blocks):
+  // partial results (unnormalised O, reference maximum, sum) meet in scratch memory, the last CTA to
+  // arrive (a counter per row block and kv head, left at zero again) merges them
+  int nsplit;
+  float* scratch;      // [row blocks * nkv * nsplit][HD + 2][128]
+  int* counters;       // [row blocks * nkv], zero between launches
   int* status;
 };
 
@@ -180,12 +186,16 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
   const unsigned s_full0 = k_full0 + 32 * AT_KS, s_empty0 = s_full0 + 16, p_full = s_full0 + 32;
   const unsigned pv_done = s_full0 + 40;
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 1 + 4 * AT_KS + 6);
+  unsigned* merge_flag = tmem_slot + 1;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int kvh = blockIdx.y;
 
   // ---- which rows: row block rb of the step (heavier, later blocks of an entry first) ----
-  int rb = gridDim.x - 1 - blockIdx.x;
+  const int item = gridDim.x - 1 - blockIdx.x;
+  const int split = item % p.nsplit;
+  const int rb_step = item / p.nsplit;       // row block within the step (names its scratch and counter)
+  int rb = rb_step;
   int entry = -1, qlen = 0;
   for (int e = 0; e < p.n_entries; ++e) {
     const int ql = p.cu_q[e + 1] - p.cu_q[e];
@@ -209,8 +219,14 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
   const int pos0 = p.ctx_len[entry] + rb * p.tpb;           // its position (ctx_len: tokens cached before the step)
   const int hi = pos0 + ntok - 1;
   const int lo_min = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-  const int kb_lo = lo_min / AT_KB;
-  const int nblk = hi / AT_KB - kb_lo + 1;
+  const int nblk_all = hi / AT_KB - lo_min / AT_KB + 1;      // key blocks the rows may see
+  // splits that have work: at least eight blocks (512 keys) each, none empty; the same for every CTA of the row block
+  int eff = min(p.nsplit, max(1, nblk_all / 8));
+  const int per = (nblk_all + eff - 1) / eff;
+  eff = (nblk_all + per - 1) / per;
+  if (split >= eff) return;
+  const int kb_lo = lo_min / AT_KB + split * per;             // this CTA's first block
+  const int nblk = min(per, nblk_all - split * per);
 
   if (tid == 32) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&qmap) : "memory");
@@ -401,29 +417,84 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
     }
     at_mbar_wait(pv_done, (unsigned)((nblk - 1) & 1), p.status, dead);
     AT_FENCE_AFTER();
-    // ---- normalise; rows leave through shared memory (the Q tile is no longer read) ----
-    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-    unsigned char* orow = q_s + r * (HD * 2);
+    // ---- the splits of a row block meet in scratch memory; the last one to arrive goes on ----
+    bool finish = true;
+    float m_all = m_ref, inv;
+    const size_t part0 = ((size_t)rb_step * p.nkv + kvh) * p.nsplit;     // this row block's first partial
+    constexpr int PSTRIDE = (HD + 2) * 128;   // floats a partial: column-major [HD + 2][128 rows] (O, maximum, sum),
+                                              // so that a warp's 32 rows read and write 128 contiguous bytes
+    if (eff > 1) {
+      float* mine = p.scratch + (part0 + split) * PSTRIDE + r;
 #pragma unroll
-    for (int c0 = 0; c0 < HD; c0 += 32) {
-      float v[32];
-      at_ld32(tmem_o + lane_addr + c0, v);
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        float v[32];
+        at_ld32(tmem_o + lane_addr + c0, v);
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        const int c = c0 / 8 + cc;
-        unsigned w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * cc + 2 * i] * inv, v[8 * cc + 2 * i + 1] * inv);
-          w[i] = *reinterpret_cast<const unsigned*>(&h);
+        for (int i = 0; i < 32; ++i) mine[(size_t)(c0 + i) * 128] = v[i];
+      }
+      mine[(size_t)HD * 128] = m_ref;
+      mine[(size_t)(HD + 1) * 128] = l_run;
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (tid == 64) {
+        const int old = atomicAdd(p.counters + rb_step * p.nkv + kvh, 1);
+        const bool last = old == eff - 1;
+        if (last) p.counters[rb_step * p.nkv + kvh] = 0;     // ready for the next launch
+        *merge_flag = last ? 1u : 0u;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      finish = *merge_flag != 0u;
+      if (finish) {
+        __threadfence();
+        float l_all = 0.f;
+        m_all = -INFINITY;
+        for (int q = 0; q < eff; ++q) m_all = fmaxf(m_all, p.scratch[(part0 + q) * PSTRIDE + (size_t)HD * 128 + r]);
+        for (int q = 0; q < eff; ++q) {
+          const float* part = p.scratch + (part0 + q) * PSTRIDE + r;
+          const float mq = part[(size_t)HD * 128];
+          l_all += (mq == -INFINITY) ? 0.f : part[(size_t)(HD + 1) * 128] * exp2f(mq - m_all);
         }
-        *reinterpret_cast<uint4*>(orow + (((c & ~7) | ((c ^ r) & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+      }
+    } else {
+      inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+    }
+    // ---- normalise; rows leave through shared memory (the Q tile is no longer read) ----
+    if (finish) {
+      unsigned char* orow = q_s + r * (HD * 2);
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        float v[32];
+        if (eff > 1) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0.f;
+          for (int q = 0; q < eff; ++q) {
+            const float* part = p.scratch + (part0 + q) * PSTRIDE + r;
+            const float mq = part[(size_t)HD * 128];
+            const float wq = (mq == -INFINITY) ? 0.f : exp2f(mq - m_all);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = fmaf(part[(size_t)(c0 + i) * 128], wq, v[i]);
+          }
+        } else {
+          at_ld32(tmem_o + lane_addr + c0, v);
+        }
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const int c = c0 / 8 + cc;
+          unsigned w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * cc + 2 * i] * inv, v[8 * cc + 2 * i + 1] * inv);
+            w[i] = *reinterpret_cast<const unsigned*>(&h);
+          }
+          *reinterpret_cast<uint4*>(orow + (((c & ~7) | ((c ^ r) & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
       }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const int e = tid - 64;
     constexpr int CPR = HD / 8;   // 16-byte pieces a row
-    for (int idx = e; idx < 128 * CPR; idx += 128) {
+    for (int idx = e; finish && idx < 128 * CPR; idx += 128) {
       const int rr = idx / CPR, c = idx % CPR;
       const int tt = rr / p.group, gg = rr - tt * p.group;
       if (rr < p.tpb * p.group && tt < ntok) {
@@ -460,17 +531,23 @@ static at_encode_fn at_encoder() {
 
 // Arguments as ll_attn_prefill (attention_prefill.cu), but the row blocks are counted differently:
 // row_blocks = sum over the entries of ceil(q_len / floor(128 / group)); num_tokens is the number of rows of q.
+// nsplit in 1..8: CTAs a row block's key blocks may be split over; with nsplit > 1, scratch is float32
+// [row_blocks * nkv * nsplit * (hd + 2) * 128] and counters int32 [row_blocks * nkv], zero at the first launch
+// (the kernel leaves them zero).
 extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, long q_stride, int num_tokens,
                                   const void* k_cache, const void* v_cache, const int* block_table, int bt_stride,
                                   const int* cu_q, const int* ctx_len, const int* req_slot, int n_entries,
                                   int row_blocks, int nh, int nkv, int hd, int page_size, int num_pages, int window,
-                                  float scale, int* status, cudaStream_t stream) {
+                                  float scale, int nsplit, float* scratch, int* counters, int* status,
+                                  cudaStream_t stream) {
   if (row_blocks <= 0 || n_entries <= 0) return 0;
   if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0 || nkv > 65535 || nh / nkv > 128)
     return (int)cudaErrorInvalidValue;
   if (!(page_size == 8 || page_size == 16 || page_size == 32 || (page_size > 0 && page_size % 64 == 0)))
     return (int)cudaErrorInvalidValue;
   if ((q_stride % 8) != 0 || (out_stride % 8) != 0 || ((uintptr_t)q % 16) != 0 || ((uintptr_t)out % 16) != 0)
+    return (int)cudaErrorInvalidValue;
+  if (nsplit < 1 || nsplit > 8 || (nsplit > 1 && (scratch == nullptr || counters == nullptr || ((uintptr_t)scratch % 16) != 0)))
     return (int)cudaErrorInvalidValue;
   at_encode_fn enc = at_encoder();
   if (enc == nullptr) return (int)cudaErrorNotSupported;
@@ -491,6 +568,9 @@ extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, lon
   p.window = window;
   p.box_rows = page_size < 64 ? page_size : 64;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.nsplit = nsplit;
+  p.scratch = scratch;
+  p.counters = counters;
   p.status = status;
 
   CUtensorMap qmap, kmap, vmap;
@@ -514,7 +594,7 @@ extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, lon
       return (int)cudaErrorInvalidValue;
   }
   const size_t smem = (size_t)128 * hd * 2 + (size_t)AT_KS * 2 * AT_KB * hd * 2 + 128 * AT_KB * 2 + 256;
-  dim3 grid(row_blocks, nkv);
+  dim3 grid(row_blocks * nsplit, nkv);
   if (hd == 64) {
     cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ll_launch(attn_prefill_tc_kernel<64>, grid, dim3(AT_THREADS), smem, stream, p, qmap, kmap, vmap);

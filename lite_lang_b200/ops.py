@@ -329,12 +329,29 @@ def attn_prefill_tc_blocks(q_lens, group: int) -> int:
     return sum((int(n) + tpb - 1) // tpb for n in q_lens)
 
 
+_attn_tc_scratch = {}
+
+
+def attn_prefill_tc_splits(row_blocks: int, num_kv_heads: int, device) -> int:
+    """CTAs a row block's keys may be split over: as many as keep the SMs (two CTAs each) busy when the step
+    has few row blocks (a short portion behind a long context), none when there are plenty."""
+    ctas = row_blocks * num_kv_heads
+    slots = 2 * sm_count(device)
+    for n in (8, 4):
+        if ctas * n <= slots:
+            return n
+    return 2 if ctas <= slots else 1      # (measured: one prompt of 2,048 tokens, 196 CTAs, 49 -> 37 us with 2)
+
+
 def attn_prefill_tc(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
                     num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                    page_size: int, window: Optional[int], scale: float, status: Optional[torch.Tensor]) -> None:
-    """Paged attention for portions of prompts on the tcgen05 tensor cores (TMA loads, S and PV in tensor
-    memory).  ``row_blocks`` from ``attn_prefill_tc_blocks``.  Otherwise as ``attn_prefill``."""
+                    page_size: int, window: Optional[int], scale: float, status: Optional[torch.Tensor],
+                    nsplit: Optional[int] = None) -> None:
+    """Paged attention for portions of prompts on the tcgen05 tensor cores (TMA loads, S and O in tensor
+    memory).  ``row_blocks`` from ``attn_prefill_tc_blocks``.  Otherwise as ``attn_prefill``.
+    ``nsplit`` (1, 2, 4, 8; default: by the size of the step): the keys of a row block are split over that
+    many CTAs, which merge through scratch memory kept by this module (grown when needed, never shrunk)."""
     _need_cuda(out, q, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot)
     for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot")):
         _i32(t, nm)
@@ -350,11 +367,24 @@ def attn_prefill_tc(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: 
     _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache plane shape")
     _need(cu_q.numel() >= num_entries + 1 and ctx_len.numel() >= num_entries and req_slot.numel() >= num_entries,
           "attn_prefill_tc: entry arrays too short")
+    if nsplit is None:
+        nsplit = attn_prefill_tc_splits(row_blocks, num_kv_heads, q.device)
+    _need(nsplit in (1, 2, 4, 8), "attn_prefill_tc: nsplit is 1, 2, 4 or 8")
+    scratch = counters = None
+    if nsplit > 1:
+        floats = row_blocks * num_kv_heads * nsplit * 128 * (head_dim + 2)
+        have = _attn_tc_scratch.get(q.device)
+        if have is None or have[0].numel() < floats or have[1].numel() < row_blocks * num_kv_heads:
+            have = (torch.empty(max(floats, have[0].numel() if have else 0), dtype=torch.float32, device=q.device),
+                    torch.zeros(max(row_blocks * num_kv_heads, 1024), dtype=torch.int32, device=q.device))
+            _attn_tc_scratch[q.device] = have
+        scratch, counters = have
     load_library("attn_tc").call(
         "ll_attn_prefill_tc", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), c_int(q.shape[0]),
         _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.stride(0)), _ptr(cu_q), _ptr(ctx_len),
         _ptr(req_slot), c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
-        c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(status), _stream())
+        c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), c_int(nsplit), _ptr(scratch),
+        _ptr(counters), _ptr(status), _stream())
 
 
 _sample_scratch = {}

@@ -401,7 +401,7 @@ def test_attn_prefill_finds_one_far_key(where):
     assert (float(c["ref"][-1].mean()) > 4.5) == (where != "window_out")
 
 
-def _run_prefill_tc(c, nh, nkv, hd, ps, lens, q_lens, window, status=None):
+def _run_prefill_tc(c, nh, nkv, hd, ps, lens, q_lens, window, status=None, nsplit=None):
     from lite_lang_b200 import ops
     d = dev()
     cu = [0]
@@ -411,7 +411,8 @@ def _run_prefill_tc(c, nh, nkv, hd, ps, lens, q_lens, window, status=None):
     ctx = torch.tensor([l - ql for l, ql in zip(lens, q_lens)], dtype=torch.int32, device=d)
     out = torch.full_like(c["q"], 3.0)
     ops.attn_prefill_tc(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], cu_q, ctx, c["req_slot"], len(lens),
-                        ops.attn_prefill_tc_blocks(q_lens, nh // nkv), nh, nkv, hd, ps, window, hd ** -0.5, status)
+                        ops.attn_prefill_tc_blocks(q_lens, nh // nkv), nh, nkv, hd, ps, window, hd ** -0.5, status,
+                        nsplit)
     return out
 
 
@@ -422,9 +423,10 @@ def _run_prefill_tc(c, nh, nkv, hd, ps, lens, q_lens, window, status=None):
 def test_attn_prefill_tc(nh, nkv, hd, ps, lens, q_lens, window):
     c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, lens, q_lens, window, seed=18)
     status = torch.zeros(1, dtype=torch.int32, device=dev())
-    out = _run_prefill_tc(c, nh, nkv, hd, ps, lens, q_lens, window, status)
-    assert status.item() == 0
-    assert_close(out, c["ref"], torch.bfloat16, "attn_prefill_tc")
+    for nsplit in (1, None, 4, 8):      # unsplit, as the engine would, and with the keys split over 4 and 8 CTAs
+        out = _run_prefill_tc(c, nh, nkv, hd, ps, lens, q_lens, window, status, nsplit)
+        assert status.item() == 0
+        assert_close(out, c["ref"], torch.bfloat16, f"attn_prefill_tc nsplit {nsplit}")
 
 
 @pytest.mark.parametrize("where", ["first", "block_edge", "last_of_block", "window_in", "window_out"])
@@ -440,8 +442,9 @@ def test_attn_prefill_tc_finds_one_far_key(where):
         window = 300
         peak = (lambda l: l - 300) if where == "window_in" else (lambda l: l - 301)
     c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, [L], [40], window, seed=19, peak=peak)
-    out = _run_prefill_tc(c, nh, nkv, hd, ps, [L], [40], window)
-    assert_close(out, c["ref"], torch.bfloat16, where)
+    for nsplit in (1, 8):
+        out = _run_prefill_tc(c, nh, nkv, hd, ps, [L], [40], window, nsplit=nsplit)
+        assert_close(out, c["ref"], torch.bfloat16, where)
     assert (float(c["ref"][-1].mean()) > 4.5) == (where != "window_out")
 
 
