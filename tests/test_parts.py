@@ -94,15 +94,15 @@ def _attention_spec(prefix, hidden, nh, nkv, hd, window=None):
     }, prefix + "self_attn.")
 
 
-def _spec(order, mixers=None, hidden=48, layers=2):
+def _spec(order, mixers=None, hidden=48, layers=2, ffns=None):
     from lite_lang_b200.config import LayerSpec, ModelSpec, PartSpec
     norm = {"hidden_size": hidden, "eps": 1e-6}
     ls = []
     for i in range(layers):
         p = f"model.layers.{i}."
         mixer = mixers[i](p) if mixers else _attention_spec(p, hidden, 4, 2, 16)
-        ls.append(LayerSpec("pre_norm", mixer,
-                            PartSpec("gated_mlp", {"hidden_size": hidden, "intermediate_size": 80}, p + "mlp."),
+        ffn = ffns[i](p) if ffns else PartSpec("gated_mlp", {"hidden_size": hidden, "intermediate_size": 80}, p + "mlp.")
+        ls.append(LayerSpec("pre_norm", mixer, ffn,
                             PartSpec("rms_norm", norm, p + "input_layernorm."),
                             PartSpec("rms_norm", norm, p + "post_attention_layernorm.")))
     return ModelSpec("Test", hidden, 97, 256,
@@ -305,3 +305,123 @@ def test_toy_mixer_with_state_needs_no_change_to_the_framework():
     assert runner.reserve(a, 10) and runner.reserve(b, T)
     out = runner.step([StepEntry(a, toks[:10], (9,)), StepEntry(b, toks, (T - 1,))]).float().cpu().numpy()
     assert rel_err(out, ref[[9, T - 1]]) <= 1e-4
+
+
+# ---------------------------------------------------------------------------
+# a toy feed-forward with routing and a toy position encoding, defined here
+# ---------------------------------------------------------------------------
+
+def test_toy_routed_feed_forward_and_another_position_encoding_need_no_change_to_the_framework():
+    """Layer 0 keeps the stock parts; layer 1 gets a feed-forward that routes every token to two of four
+    small experts and an attention whose position encoding rotates neighbouring pairs (2i, 2i+1) of only the
+    first half of each head.  Both parts live in this file; the framework builds, loads and steps them."""
+    from lite_lang_b200.config import PartSpec, RunStep
+    from lite_lang_b200.parts import FeedForward, PositionEncoding, TensorDecl, register_part
+
+    E, TOPK, INNER, H, HD, ROT = 4, 2, 24, 48, 16, 8
+
+    class ToyRoutedFFN(FeedForward):
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.h, self.e, self.inner, self.k = (int(spec.params[n]) for n in ("hidden_size", "experts", "inner", "top_k"))
+
+        def tensors(self):
+            return {"router.weight": TensorDecl((self.e, self.h)),
+                    "experts.w_in": TensorDecl((self.e, self.inner, self.h)),       # stacked along the expert axis
+                    "experts.w_out": TensorDecl((self.e, self.h, self.inner))}
+
+        def load(self, fetch, dtype, device):
+            self.router = fetch("router.weight").float().to(device)                  # router in float32
+            self.w_in = fetch("experts.w_in").to(dtype).to(device)
+            self.w_out = fetch("experts.w_out").to(dtype).to(device)
+
+        def forward(self, x, step):
+            logits = x.float() @ self.router.t()                                     # [T, E] float32
+            top, idx = torch.topk(logits, self.k, dim=-1)
+            gate = torch.softmax(top, dim=-1)                                        # renormalised over the chosen
+            out = torch.zeros_like(x, dtype=torch.float32)
+            for e in range(self.e):                                                  # tokens of expert e, gathered
+                rows, slot = (idx == e).nonzero(as_tuple=True)
+                if rows.numel() == 0:
+                    continue
+                hcur = torch.relu(x[rows].float() @ self.w_in[e].float().t())
+                out.index_add_(0, rows, (hcur @ self.w_out[e].float().t()) * gate[rows, slot].unsqueeze(1))
+            return out.to(x.dtype)
+
+    class PairRotary(PositionEncoding):
+        """Rotates the pairs (2i, 2i+1) of the first `rot` dimensions of every q and k head."""
+        fuses_with_store = False
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.rot, self.theta = int(spec.params["rot"]), float(spec.params["theta"])
+
+        def apply(self, qkv, positions, num_heads, num_kv_heads, head_dim, num_tokens):
+            half = self.rot // 2
+            inv = self.theta ** (-torch.arange(half, device=qkv.device, dtype=torch.float32) * 2 / self.rot)
+            ang = positions[:num_tokens].float().unsqueeze(1) * inv                  # [T, half]
+            cos, sin = torch.cos(ang).unsqueeze(1), torch.sin(ang).unsqueeze(1)
+            heads = qkv[:num_tokens, :(num_heads + num_kv_heads) * head_dim].view(num_tokens, -1, head_dim)
+            part = heads[..., :self.rot].float().reshape(num_tokens, -1, half, 2)
+            a, b = part[..., 0], part[..., 1]
+            rotated = torch.stack((a * cos - b * sin, a * sin + b * cos), dim=-1).reshape(num_tokens, -1, self.rot)
+            heads[..., :self.rot] = rotated.to(qkv.dtype)
+
+    register_part("feed_forward", "toy_routed", ToyRoutedFFN)
+    register_part("position", "toy_pair_rotary", PairRotary)
+
+    def toy_attention(p):
+        return PartSpec("gqa_attention", {
+            "hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": HD, "qkv_bias": True,
+            "scale": HD ** -0.5, "window": None,
+            "position": PartSpec("toy_pair_rotary", {"rot": ROT, "theta": 100.0})}, p + "self_attn.")
+
+    mixers = [lambda p: _attention_spec(p, H, 4, 2, HD), toy_attention]
+    ffns = [lambda p: PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": 80}, p + "mlp."),
+            lambda p: PartSpec("toy_routed", {"hidden_size": H, "experts": E, "inner": INNER, "top_k": TOPK}, p + "moe.")]
+    model, mgr, runner, w = _build_runner(_spec([RunStep(0), RunStep(1)], mixers, H, ffns=ffns), torch.float32)
+    assert "model.layers.1.moe.experts.w_in" in model.declared_tensors()
+
+    toks = [int(t) for t in np.random.default_rng(4).integers(0, 97, 23)]
+    T = len(toks)
+    h = P.embedding(w["model.embed_tokens.weight"], torch.tensor(toks))
+    h = _plain_layer(h, w, 0)
+    # layer 1 by hand: attention with the pair rotation, then the routed feed-forward
+    p1 = "model.layers.1."
+    x = P.rms_norm(h, w[p1 + "input_layernorm.weight"], 1e-6)
+    pos = torch.arange(T)
+
+    def proj(name, heads):
+        y = P.linear(x, w[p1 + f"self_attn.{name}_proj.weight"], w[p1 + f"self_attn.{name}_proj.bias"])
+        return y.view(T, heads, HD)
+
+    def pair_rotate(t):
+        half = ROT // 2
+        inv = 100.0 ** (-torch.arange(half, dtype=torch.float64) * 2 / ROT)
+        ang = pos.double().unsqueeze(1) * inv
+        cos, sin = torch.cos(ang).unsqueeze(1), torch.sin(ang).unsqueeze(1)
+        t = t.double().clone()
+        a, b = t[..., 0:ROT:2].clone(), t[..., 1:ROT:2].clone()
+        t[..., 0:ROT:2] = a * cos - b * sin
+        t[..., 1:ROT:2] = a * sin + b * cos
+        return t.float()
+
+    q, k, v = pair_rotate(proj("q", 4)), pair_rotate(proj("k", 2)), proj("v", 2)
+    attn = P.attention(q, k, v, None).reshape(T, 4 * HD)
+    h = h + P.linear(attn, w[p1 + "self_attn.o_proj.weight"])
+    x = P.rms_norm(h, w[p1 + "post_attention_layernorm.weight"], 1e-6)
+    logits = x.double() @ w[p1 + "moe.router.weight"].double().t()
+    top, idx = torch.topk(logits, TOPK, dim=-1)
+    gate = torch.softmax(top, dim=-1)
+    y = torch.zeros(T, H, dtype=torch.float64)
+    for t in range(T):
+        for j in range(TOPK):
+            e = int(idx[t, j])
+            hid = torch.relu(w[p1 + "moe.experts.w_in"][e].double() @ x[t].double())
+            y[t] += gate[t, j] * (w[p1 + "moe.experts.w_out"][e].double() @ hid)
+    h = h + y.float()
+    ref = P.linear(P.rms_norm(h, w["model.norm.weight"], 1e-6), w["lm_head.weight"]).numpy()
+
+    whole, cut = _run_whole_and_cut(runner, mgr, toks)
+    assert rel_err(whole, ref) <= 1e-4 and rel_err(cut, ref) <= 1e-4
+    assert len({int(e) for e in idx.flatten()}) >= 3          # the routing really spreads the tokens
