@@ -586,13 +586,18 @@ def tc_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def tc_preferred(x: torch.Tensor, weight: torch.Tensor, gated: bool = False) -> bool:
-    """Where the tcgen05 kernel was measured ahead of the library product on a B200: more tokens than
-    ``gemm_stream`` takes and few enough that the step is still bound by reading the weights.  The gated
-    feed-forward up to 64 tokens; a product with a long k (split over k, partial sums to the norm) up to 128."""
-    if not (TC_ENABLED and tc_supported(x, weight) and x.shape[0] > STREAM_M):
+TC_MIN_M = 17       # from this many tokens on the tcgen05 kernel was measured ahead of gemm_stream's mma.sync tiles
+
+
+def tc_preferred(x: torch.Tensor, weight: torch.Tensor, gated: bool = False, wide: bool = False) -> bool:
+    """Where the tcgen05 kernel was measured ahead on a B200: more tokens than ``gemm_stream`` takes well
+    (its mma.sync tiles get slower from 16 tokens up) and few enough that the step is still bound by reading
+    the weights.  The gated feed-forward and a wide product (the logits) up to 64 tokens; a product with a
+    long k (split over k, partial sums to the norm) up to 128.  Other products of such steps go to
+    ``gemm_stream`` (up to 32 tokens) or the library."""
+    if not (TC_ENABLED and tc_supported(x, weight) and x.shape[0] >= TC_MIN_M):
         return False
-    if gated:
+    if gated or wide:
         return x.shape[0] <= 64
     return x.shape[1] >= 4096 and tc_ksplit(weight.shape[0], x.shape[1], x.device) > 1
 
@@ -639,10 +644,10 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x @ Wg.T) * (x @ Wu.T) with W = [Wg; Wu]: fused for few tokens, else product + kernel."""
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
-    if stream_mode(x, w_gate_up, gated=True) is not None:
-        return gemm_stream(x, w_gate_up, act, 1)
     if tc_preferred(x, w_gate_up, gated=True):
         return gemm_tc(x, w_gate_up, act, gated=True)
+    if stream_mode(x, w_gate_up, gated=True) is not None:
+        return gemm_stream(x, w_gate_up, act, 1)
     if smallm_preferred(x, w_gate_up, gated=True):
         return gemm_smallm(x, w_gate_up, act, gated=True)
     gu = linear(x, w_gate_up)
@@ -663,6 +668,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
     kernel) accepts float32 partial sums [parts, n, out] of a product split over k.
     """
     _need_cuda(x, weight)
+    if out is None and partial_ok and out_dtype in (None, x.dtype) and tc_preferred(x, weight):
+        parts = tc_ksplit(weight.shape[0], x.shape[1], x.device)
+        out = torch.empty((parts, x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+        return gemm_tc(x, weight, out)
+    if out is None and weight.shape[0] >= 8192 and tc_preferred(x, weight, wide=True):
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+        return gemm_tc(x, weight, out)
     mode = stream_mode(x, weight) if (out is None or out.stride(1) == 1) else None
     if mode is not None:
         dt = out_dtype or x.dtype
@@ -674,10 +686,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
             out = torch.empty((x.shape[0], weight.shape[0]), dtype=dt, device=x.device)
         if out.dtype == dt:
             return gemm_stream(x, weight, out, mode)
-    if out is None and partial_ok and out_dtype in (None, x.dtype) and tc_preferred(x, weight):
-        parts = tc_ksplit(weight.shape[0], x.shape[1], x.device)
-        out = torch.empty((parts, x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
-        return gemm_tc(x, weight, out)
     if smallm_preferred(x, weight) and (out is None or out.stride(1) == 1):
         dt = out_dtype or x.dtype
         if out is None:

@@ -83,9 +83,9 @@ class GQAttention(Mixer):
     def kernel_libraries(self):
         libs = ["core"]
         if self.w_qkv is not None and self.w_qkv.dtype == torch.bfloat16:
-            libs.extend(["gemm_smallm", "gemm_stream"])
+            libs.extend(["gemm_smallm", "gemm_stream", "gemm_tc"])
             if self.head_dim in (64, 128):
-                libs.append("attn_mma")
+                libs.extend(["attn_mma", "attn_tc"])
         return libs
 
     def prepare(self, device, dtype) -> None:
