@@ -165,6 +165,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
   const unsigned stage0 = gt_smem(smem);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == GT_CONSUMERS * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");  // the producer's map
   if (tid == 0) {
     for (int s = 0; s < S::STAGES; ++s) {
       gt_mbar_init(full0 + 8 * s, 1);
