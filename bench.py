@@ -110,12 +110,12 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def build_engine(layers, max_batch, dtype="bfloat16"):
+def build_engine(layers, max_batch, dtype="bfloat16", model=None):
     import torch
     from lite_lang_b200 import Engine, EngineConfig
     from lite_lang_b200.config import config_from_dict
 
-    cfg = config_from_dict(dict(QWEN2_1P5B, num_hidden_layers=layers))
+    cfg = config_from_dict(dict(model or QWEN2_1P5B, num_hidden_layers=layers))
     pages_per_req = (CONTEXT + 15) // 16
     ecfg = EngineConfig(dtype=dtype, page_size=16, num_pages=max_batch * pages_per_req + 8,
                         max_batch_size=max_batch, max_input_length=PROMPT_LEN, max_output_length=CONTEXT - PROMPT_LEN,
@@ -292,10 +292,11 @@ def run_ours(args):
     from lite_lang_b200.csrc import build as kbuild
 
     pk = peaks()
-    layers_full = QWEN2_1P5B["num_hidden_layers"]
+    shape = WORKLOADS[args.shape]["model"] if args.shape else QWEN2_1P5B   # (--only runs may use another shape)
+    layers_full = shape["num_hidden_layers"]
     layers = args.layers or layers_full
     batch = args.batch
-    engine = build_engine(layers, batch if args.only else max(64, batch))
+    engine = build_engine(layers, batch if args.only else max(64, batch), model=shape)
     cfg = engine.model_config
     weight_bytes = engine.model.weight_bytes_per_step()
     kvb = kv_bytes_per_token(engine)
@@ -376,6 +377,65 @@ def run_reference(args):
     return 0
 
 
+WORKLOADS = {
+    # the two serving workloads named beside the headline configuration: layer sizes, requests, lengths
+    "3b_batch40": dict(
+        model=dict(architectures=["Qwen2ForCausalLM"], hidden_size=2048, num_hidden_layers=36, num_attention_heads=16,
+                   num_key_value_heads=2, head_dim=128, intermediate_size=11008, vocab_size=151936, rope_theta=1e6,
+                   rms_norm_eps=1e-6, max_position_embeddings=4096, tie_word_embeddings=True),
+        requests=40, prompt=(600, 600), new_tokens=600, max_batch=40),
+    "7b_mixed64": dict(
+        model=dict(architectures=["Qwen2ForCausalLM"], hidden_size=3584, num_hidden_layers=28, num_attention_heads=28,
+                   num_key_value_heads=4, head_dim=128, intermediate_size=18944, vocab_size=152064, rope_theta=1e6,
+                   rms_norm_eps=1e-6, max_position_embeddings=8192, tie_word_embeddings=False),
+        requests=64, prompt=(128, 4096), new_tokens=256, max_batch=64),
+}
+
+
+def run_workload(args):
+    """A whole serving workload through Engine.step(): admission, prompts cut into portions of at most 2,048
+    tokens a step beside the decode tokens of the others, sampling, finishing.  Wall clock around all of it."""
+    import numpy as np
+    import torch
+    from lite_lang_b200 import Engine, EngineConfig, SamplingParams
+    from lite_lang_b200.config import config_from_dict
+
+    w = WORKLOADS[args.workload]
+    layers_full = w["model"]["num_hidden_layers"]
+    layers = args.layers or layers_full
+    cfg = config_from_dict(dict(w["model"], num_hidden_layers=layers))
+    lo, hi = w["prompt"]
+    rng = np.random.default_rng(11)
+    lengths = [int(rng.integers(lo, hi + 1)) for _ in range(w["requests"])]
+    longest = max(lengths) + w["new_tokens"] + 1
+    pages = sum((n + w["new_tokens"] + 16) // 16 + 1 for n in lengths) + 8
+    ecfg = EngineConfig(dtype="bfloat16", page_size=16, num_pages=pages, max_batch_size=w["max_batch"],
+                        max_input_length=max(lengths), max_output_length=w["new_tokens"], max_model_len=longest,
+                        max_tokens_per_step=2048, cuda_graphs=True, seed=0)
+    engine = Engine(config=cfg, engine_config=ecfg, random_seed=1234)
+    engine.runner.capture_all()
+    sp = SamplingParams(temperature=0.0, max_new_tokens=w["new_tokens"], ignore_eos=True)
+    prompts = [[int(t) for t in rng.integers(0, cfg.vocab_size, size=n)] for n in lengths]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    reqs = [engine.add_request(p, sp) for p in prompts]
+    steps = 0
+    while engine.scheduler.has_work():
+        engine.step()
+        steps += 1
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    new = sum(len(r.output) for r in reqs)
+    st = engine.stats()
+    print(json.dumps({"workload": args.workload, "impl": "ours", "layers": layers, "layers_full": layers_full,
+                      "requests": len(reqs), "prompt_tokens": sum(lengths), "new_tokens": new,
+                      "seconds": round(dt, 3), "steps": steps, "new_tokens_per_s": round(new / dt, 1),
+                      "all_tokens_per_s": round((new + sum(lengths)) / dt, 1),
+                      "preemptions": st.get("preemptions", 0), "graph_replays": st.get("graph_replays", 0),
+                      "dtype": "bf16", "data": "synthetic"}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -387,7 +447,15 @@ def main():
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "kernels"],
                     help="a small case for profilers: only the decode steps or only the prefill (prints a short "
                          "line), or 'kernels': the decode step's kernels timed inside its graph by torch.profiler")
+    ap.add_argument("--workload", default="", choices=[""] + sorted(WORKLOADS),
+                    help="instead of the headline measurement: a whole serving workload through the scheduler "
+                         "(Qwen2.5-3B sizes, 40 requests of 600 + 600 tokens; Qwen2-7B sizes, 64 requests with prompts "
+                         "of 128..4096 tokens cut into portions of 2,048 a step, 256 new tokens each)")
+    ap.add_argument("--shape", default="", choices=[""] + sorted(WORKLOADS),
+                    help="with --only: the layer sizes of that workload's model instead of Qwen2-1.5B's")
     args = ap.parse_args()
+    if args.shape and not args.only:
+        ap.error("--shape goes with --only (the headline measurement is of the Qwen2-1.5B sizes)")
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not built (this engine has no multi-GPU path)")
         return 2
@@ -395,6 +463,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload:
+        return run_workload(args)
     return run_ours(args)
 
 
