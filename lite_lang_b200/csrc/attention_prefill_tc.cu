@@ -134,6 +134,18 @@ __device__ __forceinline__ void at_st32(unsigned taddr, const float (&v)[32]) {
       "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31])), "r"(taddr)
       : "memory");
 }
+// one MUFU instruction (exp2f without this carries range handling around it); -inf gives 0
+__device__ __forceinline__ float at_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// maximum of three in one instruction (sm_100)
+__device__ __forceinline__ float at_max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 #define AT_FENCE_BEFORE() asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory")
 #define AT_FENCE_AFTER() asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory")
 
@@ -370,26 +382,35 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
         for (int i = 0; i < AT_KB; ++i)
           if (k0 + i > prow || k0 + i < lo_row) sv[i] = -INFINITY;
       }
+      // (the softmax warps are bound by instruction issue: packed float32 pairs for the scaling and the sums,
+      // three-input maxima, one MUFU instruction per exponential)
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < AT_KB; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
+      for (int i = 0; i < AT_KB; i += 8) {
+        mx4[0] = at_max3(mx4[0], sv[i], sv[i + 1]);
+        mx4[1] = at_max3(mx4[1], sv[i + 2], sv[i + 3]);
+        mx4[2] = at_max3(mx4[2], sv[i + 4], sv[i + 5]);
+        mx4[3] = at_max3(mx4[3], sv[i + 6], sv[i + 7]);
+      }
       const float mxs = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       const bool grow = mxs > m_ref + 8.0f;          // also the first keys a row sees (m_ref = -inf)
-      const float factor = grow ? exp2f(m_ref - mxs) : 1.0f;   // m_ref = -inf: 0 (O and the sum are 0 then)
+      const float factor = grow ? at_ex2(m_ref - mxs) : 1.0f;   // m_ref = -inf: 0 (O and the sum are 0 then)
       if (grow) m_ref = mxs;
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
       // the row of P in registers: 64 bfloat16 = 8 pieces of 16 bytes
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_use, -m_use);
       unsigned pw[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float e0 = exp2f(fmaf(sv[2 * i], p.scale_log2, -m_use));
-        const float e1 = exp2f(fmaf(sv[2 * i + 1], p.scale_log2, -m_use));
-        sum4[i & 3] += e0 + e1;
-        const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+        const float2 a = __ffma2_rn(make_float2(sv[2 * i], sv[2 * i + 1]), sc2, nm2);
+        const float2 e = make_float2(at_ex2(a.x), at_ex2(a.y));
+        sum2[i & 1] = __fadd2_rn(sum2[i & 1], e);
+        const __nv_bfloat162 h = __floats2bfloat162_rn(e.x, e.y);
         pw[i] = *reinterpret_cast<const unsigned*>(&h);
       }
-      l_run = l_run * factor + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      const float2 st = __fadd2_rn(sum2[0], sum2[1]);
+      l_run = l_run * factor + (st.x + st.y);
       // the block before must be in O, and P read, before either is touched
       if (j > 0) {
         at_mbar_wait(pv_done, (unsigned)((j - 1) & 1), p.status, dead);

@@ -47,6 +47,7 @@ class StepBatch(StepView):
     token_req: torch.Tensor            # int32 [num_tokens] entry index of each token
     feed: torch.Tensor                 # int32 [num_tokens] place in the last step's sampled tokens, or -1
     has_feed: bool                     # some token of the step is taken from the last step's results
+    entry_ctx: list                    # host copy of ctx_len for the real entries
     cu_q: torch.Tensor                 # int32 [num_entries + 1] first token of each entry
     ctx_len: torch.Tensor              # int32 [num_entries] tokens cached before this step
     req_slot: torch.Tensor             # int32 [num_entries] request slot (-1: padding)
@@ -237,6 +238,7 @@ class BatchBuilder:
         b.entries = arranged
         b.scratch = {}
         b.has_feed = bool((feed[:t_all] >= 0).any())
+        b.entry_ctx = [int(c) for c in ctx_len[:n_real]]       # host copy: tokens cached before the step, per entry
         if not views:
             return b
         d = self.dev

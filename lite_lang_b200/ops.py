@@ -332,15 +332,34 @@ def attn_prefill_tc_blocks(q_lens, group: int) -> int:
 _attn_tc_scratch = {}
 
 
-def attn_prefill_tc_splits(row_blocks: int, num_kv_heads: int, device) -> int:
-    """CTAs a row block's keys may be split over: as many as keep the SMs (two CTAs each) busy when the step
-    has few row blocks (a short portion behind a long context), none when there are plenty."""
+def attn_prefill_tc_plan(entries, group: int, window: Optional[int]):
+    """(row blocks, longest, mean) of a step for ``attn_prefill_tc``.  ``entries``: (cached tokens, new tokens)
+    per entry; a row block takes floor(128 / group) tokens; longest / mean: key blocks of 64 a row block walks."""
+    tpb = 128 // group
+    blocks, longest, total = 0, 0, 0
+    for ctx, q in entries:
+        for first in range(0, q, tpb):
+            hi = ctx + min(first + tpb, q) - 1
+            lo = max(0, ctx + first - window + 1) if window else 0
+            n = hi // 64 - lo // 64 + 1
+            blocks += 1
+            total += n
+            longest = max(longest, n)
+    return blocks, longest, (total / blocks if blocks else 0.0)
+
+
+def attn_prefill_tc_splits(row_blocks: int, num_kv_heads: int, device, longest: float = 0.0, mean: float = 0.0) -> int:
+    """CTAs a row block's keys may be split over.  As many as still fit the SMs (two CTAs each) in one wave when
+    the step has few row blocks (a short portion behind a long context).  When the unsplit CTAs already fill
+    more than half of them, two only if the row blocks are of very different length (a whole causal prompt:
+    the longest walks twice the mean; measured 49 -> 37 us for 2,048 tokens), since equal ones just get a
+    second wave (four portions of 512 behind 1,536 tokens: 49 -> 60 us)."""
     ctas = row_blocks * num_kv_heads
     slots = 2 * sm_count(device)
-    for n in (8, 4):
+    for n in (8, 4, 2):
         if ctas * n <= slots:
             return n
-    return 2 if ctas <= slots else 1      # (measured: one prompt of 2,048 tokens, 196 CTAs, 49 -> 37 us with 2)
+    return 2 if (ctas <= slots and longest >= 1.5 * mean and longest >= 16) else 1
 
 
 def attn_prefill_tc(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,

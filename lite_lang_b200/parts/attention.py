@@ -174,13 +174,22 @@ class GQAttention(Mixer):
                 if ops.TC_ENABLED and ops.attn_prefill_tc_supported(qkv.dtype, self.head_dim, cache.page_size,
                                                                     qkv.stride(0), group):
                     # tcgen05: S and O in tensor memory, K and V page by page through TMA
-                    key = ("attn_prefill_tc", group)
-                    blocks = step.scratch.get(key)
-                    if blocks is None:
-                        blocks = step.scratch[key] = ops.attn_prefill_tc_blocks(
-                            (len(e.tokens) for e in step.entries[n_single:]), group)
-                    ops.attn_prefill_tc(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, *rest, blocks,
-                                        *args, step.status)
+                    key = ("attn_prefill_tc", group, self.window)
+                    plan = step.scratch.get(key)
+                    if plan is None:
+                        ctxs = getattr(step, "entry_ctx", None)
+                        rest_entries = step.entries[n_single:]
+                        if ctxs is not None:
+                            blocks, longest, mean = ops.attn_prefill_tc_plan(
+                                [(ctxs[n_single + i], len(e.tokens)) for i, e in enumerate(rest_entries)], group,
+                                self.window)
+                        else:
+                            blocks, longest, mean = ops.attn_prefill_tc_blocks(
+                                (len(e.tokens) for e in rest_entries), group), 0.0, 0.0
+                        nsplit = ops.attn_prefill_tc_splits(blocks, self.num_kv_heads, qkv.device, longest, mean)
+                        plan = step.scratch[key] = (blocks, nsplit)
+                    ops.attn_prefill_tc(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, *rest, plan[0],
+                                        *args, step.status, nsplit=plan[1])
                 else:
                     key = ("attn_prefill", group)
                     blocks = step.scratch.get(key)
