@@ -19,7 +19,7 @@
 // beside the other's MMAs.
 // Roles: warp 0 loads (one thread: Q once through a 3-d tensor map [token, head, head size]; K and V
 // of a block page by page through 2-d maps over the cache plane, into a ring of two stages), warp 1
-// issues the MMAs (one thread; S of the next block before P V of this one, so that the tensor cores work
+// issues the MMAs (one thread; S a whole block ahead of the softmax, so that the tensor cores work
 // while the softmax threads do), warps 2..5 are the softmax rows.  All hand-offs are mbarriers: TMA
 // completes the "full" ones, tcgen05.commit the ones the tensor cores free, the softmax warps arrive
 // on the rest.  Every wait is bounded; one that runs out records LL_ERR_WAIT_TIMEOUT, stops waiting in
@@ -103,7 +103,33 @@ __device__ __forceinline__ void at_mma(unsigned tmem_d, unsigned long long da, u
 __device__ __forceinline__ void at_commit(unsigned bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// 32 consecutive float32 columns of this thread's tensor-memory lane
+// 32 consecutive float32 columns of this thread's tensor-memory lane: the load is asynchronous, the values may
+// be used after at_ld_wait() (so that several loads can be on their way at once)
+__device__ __forceinline__ void at_ld32_issue(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// (the registers are tied to the wait so that no use of them can be scheduled before it)
+__device__ __forceinline__ void at_ld_wait(unsigned (&a)[32], unsigned (&b)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(a[8]),
+                 "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]), "+r"(a[16]),
+                 "+r"(a[17]), "+r"(a[18]), "+r"(a[19]), "+r"(a[20]), "+r"(a[21]), "+r"(a[22]), "+r"(a[23]), "+r"(a[24]),
+                 "+r"(a[25]), "+r"(a[26]), "+r"(a[27]), "+r"(a[28]), "+r"(a[29]), "+r"(a[30]), "+r"(a[31]), "+r"(b[0]),
+                 "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]), "+r"(b[8]), "+r"(b[9]),
+                 "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15]), "+r"(b[16]), "+r"(b[17]),
+                 "+r"(b[18]), "+r"(b[19]), "+r"(b[20]), "+r"(b[21]), "+r"(b[22]), "+r"(b[23]), "+r"(b[24]), "+r"(b[25]),
+                 "+r"(b[26]), "+r"(b[27]), "+r"(b[28]), "+r"(b[29]), "+r"(b[30]), "+r"(b[31])
+               :
+               : "memory");
+}
 __device__ __forceinline__ void at_ld32(unsigned taddr, float (&v)[32]) {
   unsigned r[32];
   asm volatile(
@@ -289,7 +315,7 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
       if (page < 0 || page >= p.num_pages) page = 0;   // given back or beyond the context: masked below
       return (page * p.nkv + kvh) * p.page_size + kp % p.page_size;
     };
-    // order of the copies: K(0), then K(j + 1) before V(j), the order in which the MMAs want them
+    // order of the copies: K(0), K(1), then V(j) before K(j + 2), the order in which the MMAs want them
     auto load = [&](int j, int row, bool is_v) {
       const int s = j % AT_KS;
       const unsigned full = (is_v ? v_full0 : k_full0) + 8 * s;
@@ -303,13 +329,15 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
         for (int h = 0; h < HB; ++h) at_tma_2d(dst + h * (KV_BYTES / HB), is_v ? &vmap : &kmap, h * 64, row, full);
       }
     };
-    int row_cur = page_of(0);
-    load(0, row_cur, false);
+    int row0 = page_of(0), row1 = page_of(1);   // cache rows of blocks j and j + 1
+    load(0, row0, false);
+    if (nblk > 1) load(1, row1, false);
     for (int j = 0; j < nblk; ++j) {
-      const int row_next = page_of(j + 1);
-      if (j + 1 < nblk) load(j + 1, row_next, false);
-      load(j, row_cur, true);
-      row_cur = row_next;
+      const int row2 = page_of(j + 2);
+      load(j, row0, true);
+      if (j + 2 < nblk) load(j + 2, row2, false);
+      row0 = row1;
+      row1 = row2;
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issue ------------------------------
@@ -330,9 +358,12 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
         at_commit(k_empty0 + 8 * s);   // the K stage is free once these MMAs have read it
       };
       at_mbar_wait(q_full, 0, p.status, dead);
+      // S runs a whole block ahead of the softmax: S(j + 2) is issued as soon as P(j) has gone into O, into
+      // the buffer whose S(j) the softmax warps read long ago, so S(j + 1) is complete when they want it
+      // however far apart the four warps have drifted
       mma_s(0);
+      if (nblk > 1) mma_s(1);
       for (int j = 0; j < nblk; ++j) {
-        if (j + 1 < nblk) mma_s(j + 1);
         const int s = j % AT_KS;
         at_mbar_wait(v_full0 + 8 * s, (unsigned)((j / AT_KS) & 1), p.status, dead);
         at_mbar_wait(p_full, (unsigned)(j & 1), p.status, dead);
@@ -345,6 +376,7 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
                  (j > 0 || k16 > 0) ? 1u : 0u);
         at_commit(pv_done);            // P may be written again; O holds the blocks up to j
         at_commit(v_empty0 + 8 * s);
+        if (j + 2 < nblk) mma_s(j + 2);
       }
     }
   } else {
@@ -365,13 +397,15 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
       AT_FENCE_AFTER();
       float sv[AT_KB];
       {
-        float v[32];
-        at_ld32(tmem_s + lane_addr + b * AT_KB, v);
+        unsigned ra[32], rb[32];      // both halves of the row are on their way before the one wait
+        at_ld32_issue(tmem_s + lane_addr + b * AT_KB, ra);
+        at_ld32_issue(tmem_s + lane_addr + b * AT_KB + 32, rb);
+        at_ld_wait(ra, rb);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sv[i] = v[i];
-        at_ld32(tmem_s + lane_addr + b * AT_KB + 32, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) sv[32 + i] = v[i];
+        for (int i = 0; i < 32; ++i) {
+          sv[i] = __uint_as_float(ra[i]);
+          sv[32 + i] = __uint_as_float(rb[i]);
+        }
       }
       AT_FENCE_BEFORE();
       __syncwarp();
