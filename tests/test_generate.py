@@ -181,6 +181,62 @@ def test_steps_launched_ahead_give_the_same_tokens_and_end_requests_on_time():
     assert st_a["graph_replays"] > 0
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_random_serving_runs_equal_the_plain_continuation(seed):
+    """Random prompts, limits, an eos id taken from the plain continuations, requests arriving while others run,
+    tight page pools (requests leave and are recomputed), steps launched ahead or not: every request's tokens
+    equal the plain greedy continuation, and every page comes back."""
+    import random
+    from lite_lang_b200 import Engine, EngineConfig, SamplingParams
+    rng = random.Random(1000 + seed)
+    name = "ABC"[seed % 3]
+    folder = make_model_folder(name, scales={"matrix": 0.08})
+    cfg, w = P.read_model_folder(folder)
+    n_req = rng.randint(3, 8)
+    prompts = [random_tokens(rng.randint(1, 60), cfg["vocab_size"], seed * 100 + i) for i in range(n_req)]
+    max_new = [rng.randint(1, 14) for _ in range(n_req)]
+    plain = [P.greedy_generate(cfg, w, p, m) for p, m in zip(prompts, max_new)]
+    eos = None
+    if rng.random() < 0.6:
+        cand = plain[rng.randrange(n_req)]
+        eos = cand[rng.randrange(len(cand))]
+        with open(os.path.join(folder, "config.json"), "w") as fh:
+            json.dump(dict(cfg, eos_token_id=eos), fh)
+    ps = TINY[name]["page_size"]
+    need = max((len(p) + m + ps) // ps + 1 for p, m in zip(prompts, max_new))
+    pages = rng.randint(need, need + 3) if rng.random() < 0.7 else rng.randint(need, need * 3)
+    eng = Engine(folder, EngineConfig(dtype="float32", page_size=ps, num_pages=pages, max_batch_size=rng.choice([2, 4]),
+                                      max_input_length=100, max_output_length=16,
+                                      max_tokens_per_step=rng.choice([8, 16, 64])))
+    eng._pipeline = rng.random() < 0.8
+    order = list(range(n_req))
+    rng.shuffle(order)
+    first = order[:rng.randint(1, n_req)]
+    later = order[len(first):]
+    reqs = {i: eng.add_request(prompts[i], SamplingParams(temperature=0.0, max_new_tokens=max_new[i])) for i in first}
+    steps = 0
+    while eng.scheduler.has_work() or later:
+        if later and (steps % 3 == 2 or not eng.scheduler.has_work()):
+            i = later.pop()
+            reqs[i] = eng.add_request(prompts[i], SamplingParams(temperature=0.0, max_new_tokens=max_new[i]))
+        eng.step()
+        steps += 1
+        assert steps < 5000
+    eng.manager.check_invariants()
+    assert eng.manager.num_free_pages() == eng.manager.total_pages()
+    for i in range(n_req):
+        want = plain[i]
+        if eos is not None and eos in want:
+            want = want[:want.index(eos) + 1]
+        got = list(reqs[i].output)
+        if reqs[i].finish_reason == "cache_full" or got == want:
+            continue
+        k = next((j for j, (a, b) in enumerate(zip(got, want)) if a != b), min(len(got), len(want)))
+        logits = P.forward_logits(cfg, w, prompts[i] + want[:k])[-1]
+        top2 = torch.topk(logits, 2).values          # only a near-tie in the plain logits excuses a difference
+        assert float(top2[0] - top2[1]) <= 1e-4 * float(logits.abs().max()), (i, got, want)
+
+
 def test_command_line():
     folder = make_model_folder("A", scales={"matrix": 0.08})
     cfg, w = P.read_model_folder(folder)
