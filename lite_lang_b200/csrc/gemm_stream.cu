@@ -16,7 +16,9 @@
 // The weights take the M side of the MMA (16 rows a tile), the tokens the N side.  As in
 // gemm_smallm.cu the contraction index of an MMA step is mapped to 8 contiguous elements
 // per thread, so a thread's A fragment is one 16-byte read from a stage row and its B
-// fragment one 16-byte read of a token row (global memory, L1 resident).
+// fragment one 16-byte read of a token row.  The token rows of a stage's k range travel with
+// its weights: a second tensor map (of x, boxes of 8..32 rows x 64 k) puts them behind the
+// weight boxes of the stage, after griddepcontrol.wait (the weights start before it).
 //
 // Three shapes of work unit:
 //   WIDE    64 output features x all of K; a stage is 64 rows x 128 k (two boxes); warp w
@@ -148,26 +150,44 @@ struct GtParams {
   int* status;
 };
 
+// What a stage holds and how many there are.  The token rows of the stage's k range travel with the weights
+// (boxes of 8 MT rows x 64 k through a tensor map of x), so the consumers read both operands from shared
+// memory.  (They used to read x from global memory chunk by chunk; with a handful of tokens that was a
+// chain of L2 latencies inside every product: 12 % of a decode step at batch 8, 10 % at batch 32.)
+template <int MODE, int MT> struct GtStage {
+  using S = GtShape<MODE>;
+  static constexpr int KBOXES = S::KC / 64;                 // boxes along k in a stage
+  static constexpr int W_BYTES = S::ROWS * S::KC * 2;
+  static constexpr int XBOX_BYTES = 8 * MT * 128;           // 8 MT token rows x 64 k
+  static constexpr int STAGE_BYTES = W_BYTES + KBOXES * XBOX_BYTES;
+  static constexpr int FIT = (96 * 1024) / STAGE_BYTES;     // the ring stays within 96 KB (two CTAs an SM)
+  static constexpr int STAGES = FIT < S::STAGES ? FIT : S::STAGES;
+};
+
 template <int MODE, int MT, typename OutT>
 __global__ void __launch_bounds__(GT_THREADS)
-gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
+gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap) {
   using S = GtShape<MODE>;
-  constexpr int KBOXES = S::KC / 64;                 // boxes along k in a stage
+  using G = GtStage<MODE, MT>;
+  constexpr int KBOXES = G::KBOXES;
   constexpr int BOX_BYTES = S::BOX_ROWS * 128;       // one box: BOX_ROWS rows of 128 bytes, swizzled
   constexpr int RBOXES = S::ROWS / S::BOX_ROWS;      // boxes along the rows (GATED: gate box, up box)
-  constexpr int STAGE_BYTES = S::ROWS * S::KC * 2;
+  constexpr int W_BYTES = G::W_BYTES, XBOX_BYTES = G::XBOX_BYTES, STAGE_BYTES = G::STAGE_BYTES, STAGES = G::STAGES;
   extern __shared__ unsigned char smem_raw[];
   // the swizzle pattern repeats every 1024 bytes: stages start on a 1024-byte boundary
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + S::STAGES * STAGE_BYTES);
-  float* red = reinterpret_cast<float*>(smem + S::STAGES * STAGE_BYTES + 2 * S::STAGES * 8);
-  const unsigned full0 = gt_smem(bars), empty0 = gt_smem(bars + S::STAGES);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
+  float* red = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 2 * STAGES * 8);
+  const unsigned full0 = gt_smem(bars), empty0 = gt_smem(bars + STAGES);
   const unsigned stage0 = gt_smem(smem);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == GT_CONSUMERS * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");  // the producer's map
+  if (tid == GT_CONSUMERS * 32) {   // the producer's maps
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&xmap) : "memory");
+  }
   if (tid == 0) {
-    for (int s = 0; s < S::STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       gt_mbar_init(full0 + 8 * s, 1);
       gt_mbar_init(empty0 + 8 * s, GT_CONSUMERS);
     }
@@ -180,12 +200,13 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
 
   if (warp == GT_CONSUMERS) {
     // ------------------------------ producer ------------------------------
-    // The weights do not depend on the kernel before this one, so streaming starts at once.
+    // The weights do not depend on the kernel before this one, so streaming starts at once.  The token
+    // rows do: their boxes follow after griddepcontrol.wait, first for the stages already under way.
     if (lane == 0) {
-      long it = 0;
-      for (int uu = blockIdx.x; uu < p.units; uu += gridDim.x) {
+      int uu = blockIdx.x, kc = 0, kc_end = 0, y[RBOXES];
+      auto open_unit = [&]() {   // rows and k range of work unit uu
+        if (uu >= p.units) return;
         const int u = uu / p.ksplit, kp = uu - u * p.ksplit;
-        int y[RBOXES];
         if (MODE == GT_MODE_WIDE) {
           y[0] = u * 64;
         } else if (MODE == GT_MODE_GATED) {
@@ -199,19 +220,47 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
         } else {
           y[0] = u * 16;
         }
-        const int kc_end = min(kchunks, (kp + 1) * p.cpp);
-        for (int kc = kp * p.cpp; kc < kc_end; ++kc, ++it) {
-          const int s = (int)(it % S::STAGES);
-          const unsigned ph = (unsigned)((it / S::STAGES) & 1);
-          gt_mbar_wait(empty0 + 8 * s, ph ^ 1, p.status);
-          gt_mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-#pragma unroll
-          for (int kb = 0; kb < KBOXES; ++kb)
-#pragma unroll
-            for (int rb = 0; rb < RBOXES; ++rb)
-              gt_tma_load(stage0 + s * STAGE_BYTES + (kb * RBOXES + rb) * BOX_BYTES, &wmap, kc * S::KC + kb * 64, y[rb],
-                          full0 + 8 * s);
+        kc = kp * p.cpp;
+        kc_end = min(kchunks, (kp + 1) * p.cpp);
+      };
+      auto advance = [&]() {
+        if (++kc >= kc_end) {
+          uu += gridDim.x;
+          open_unit();
         }
+      };
+      auto issue_w = [&](int s) {
+#pragma unroll
+        for (int kb = 0; kb < KBOXES; ++kb)
+#pragma unroll
+          for (int rb = 0; rb < RBOXES; ++rb)
+            gt_tma_load(stage0 + s * STAGE_BYTES + (kb * RBOXES + rb) * BOX_BYTES, &wmap, kc * S::KC + kb * 64, y[rb],
+                        full0 + 8 * s);
+      };
+      auto issue_x = [&](int s, int k) {
+#pragma unroll
+        for (int kb = 0; kb < KBOXES; ++kb)
+          gt_tma_load(stage0 + s * STAGE_BYTES + W_BYTES + kb * XBOX_BYTES, &xmap, k * S::KC + kb * 64, 0, full0 + 8 * s);
+      };
+      open_unit();
+      int early_kc[STAGES];
+      int early = 0;
+      for (; early < STAGES && uu < p.units; ++early) {   // the ring's first round: weights now
+        gt_mbar_expect_tx(full0 + 8 * early, STAGE_BYTES);
+        issue_w(early);
+        early_kc[early] = kc;
+        advance();
+      }
+      LL_PDL_WAIT();
+      for (int s = 0; s < early; ++s) issue_x(s, early_kc[s]);   // their token rows once those exist
+      for (long it = early; uu < p.units; ++it) {
+        const int s = (int)(it % STAGES);
+        const unsigned ph = (unsigned)((it / STAGES) & 1);
+        gt_mbar_wait(empty0 + 8 * s, ph ^ 1, p.status);
+        gt_mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+        issue_w(s);
+        issue_x(s, kc);
+        advance();
       }
     }
     return;
@@ -219,9 +268,6 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
 
   // ------------------------------ consumers ------------------------------
   const int g = lane >> 2, c = lane & 3;
-  const bf16* xp[MT];
-#pragma unroll
-  for (int j = 0; j < MT; ++j) xp[j] = p.x + (size_t)min(8 * j + g, p.M - 1) * p.x_stride + 8 * c;
   // the token rows are written by the kernel before this one; the producer warp does not wait (it
   // only reads weights), the consumers do, so no CTA exits before the kernel before has finished
   LL_PDL_WAIT();
@@ -252,17 +298,19 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap) {
     for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     const int kc_end = min(kchunks, (kp + 1) * p.cpp);
     for (int kc = kp * p.cpp; kc < kc_end; ++kc, ++it) {
-      const int s = (int)(it % S::STAGES);
-      const unsigned ph = (unsigned)((it / S::STAGES) & 1);
+      const int s = (int)(it % STAGES);
+      const unsigned ph = (unsigned)((it / STAGES) & 1);
       uint4 xv[MYBOXES][2][MT];
+      gt_mbar_wait(full0 + 8 * s, ph, p.status);
+      // token row 8 j + g of the stage's x box: its 16-byte chunk 4 i + c sits at chunk (4 i + c) ^ g
 #pragma unroll
       for (int b = 0; b < MYBOXES; ++b)
 #pragma unroll
         for (int i = 0; i < 2; ++i)
 #pragma unroll
           for (int j = 0; j < MT; ++j)
-            xv[b][i][j] = *reinterpret_cast<const uint4*>(xp[j] + (size_t)kc * S::KC + (kb0 + b) * 64 + 32 * i);
-      gt_mbar_wait(full0 + 8 * s, ph, p.status);
+            xv[b][i][j] = gt_lds16(stage0 + s * STAGE_BYTES + W_BYTES + (kb0 + b) * XBOX_BYTES + (8 * j + g) * 128 +
+                                   (((unsigned)(4 * i + c) ^ sw) * 16));
 #pragma unroll
       for (int b = 0; b < MYBOXES; ++b) {
         const unsigned box = stage0 + s * STAGE_BYTES + (kb0 + b) * RBOXES * BOX_BYTES;
@@ -413,12 +461,13 @@ static gt_encode_fn gt_encoder() {
   return fn;
 }
 
-// Tensor map of W [rows, K] (bfloat16, row-major) with boxes of box_rows rows x 64 k, 128-byte swizzle.
-static int gt_make_map(CUtensorMap* map, const void* w, long rows, long K, int box_rows) {
+// Tensor map of a bfloat16 matrix [rows, K] (rows row_stride elements apart; 0: K) with boxes of box_rows rows
+// x 64 k, 128-byte swizzle.  Rows beyond the matrix read as zeros.
+static int gt_make_map(CUtensorMap* map, const void* w, long rows, long K, int box_rows, long row_stride = 0) {
   gt_encode_fn enc = gt_encoder();
   if (enc == nullptr) return (int)cudaErrorNotSupported;
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint64_t strides[1] = {(cuuint64_t)(row_stride > 0 ? row_stride : K) * 2};
   const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w), dims, strides, box, estr,
@@ -430,16 +479,19 @@ static int gt_make_map(CUtensorMap* map, const void* w, long rows, long K, int b
 template <int MODE, int MT, typename OutT>
 static int gt_launch(const GtParams& p, const void* w, int sm_count, cudaStream_t stream) {
   using S = GtShape<MODE>;
-  CUtensorMap map;
+  using G = GtStage<MODE, MT>;
+  CUtensorMap map, xmap;
   const long w_rows = (MODE == GT_MODE_GATED) ? 2l * p.N : p.N;
-  const int rc = gt_make_map(&map, w, w_rows, p.K, S::BOX_ROWS);
+  int rc = gt_make_map(&map, w, w_rows, p.K, S::BOX_ROWS);
   if (rc != 0) return rc;
-  const size_t smem = 1024 + (size_t)S::STAGES * S::ROWS * S::KC * 2 + 2 * S::STAGES * 8 +
+  rc = gt_make_map(&xmap, p.x, p.M, p.K, 8 * MT, p.x_stride);   // token rows: boxes of 8 MT rows, zeros beyond M
+  if (rc != 0) return rc;
+  const size_t smem = 1024 + (size_t)G::STAGES * G::STAGE_BYTES + 2 * G::STAGES * 8 +
                       ((MODE == GT_MODE_NARROW || MODE == GT_MODE_QKV_ROPE) ? sizeof(float) * GT_CONSUMERS * 16 * 8 * MT : 0);
   cudaFuncSetAttribute(gemm_stream_kernel<MODE, MT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   // two CTAs an SM (one an SM, so that the next product's CTAs could move in early, was measured slower)
   const int grid = p.units < 2 * sm_count ? p.units : 2 * sm_count;
-  ll_launch(gemm_stream_kernel<MODE, MT, OutT>, dim3(grid), dim3(GT_THREADS), smem, stream, p, map);
+  ll_launch(gemm_stream_kernel<MODE, MT, OutT>, dim3(grid), dim3(GT_THREADS), smem, stream, p, map, xmap);
   return LL_LAUNCH_RESULT();
 }
 
