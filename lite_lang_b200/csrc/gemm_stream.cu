@@ -296,6 +296,41 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
     float acc[MT][4];
 #pragma unroll
     for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    // QKV_ROPE: what the unit's epilogue reads from global memory (bias, the token's position and cache slot,
+    // its cos and sin) is asked for now, so that it has arrived when the MMAs are done
+    constexpr int EP_ITEMS = (MODE == GT_MODE_QKV_ROPE) ? (8 * 8 * MT + GT_CONSUMERS * 32 - 1) / (GT_CONSUMERS * 32) : 1;
+    float ep_b0[EP_ITEMS], ep_b1[EP_ITEMS], ep_cs[EP_ITEMS], ep_sn[EP_ITEMS];
+    long ep_slot[EP_ITEMS];
+    if (MODE == GT_MODE_QKV_ROPE) {
+      const int upr = p.hd / 16, half = p.hd / 2;
+      const int head = u / upr, i0 = (u - head * upr) * 8;
+#pragma unroll
+      for (int e = 0; e < EP_ITEMS; ++e) {
+        const int idx = tid + e * GT_CONSUMERS * 32;
+        const int t = idx >> 3, j = idx & 7;
+        ep_b0[e] = ep_b1[e] = 0.f;
+        ep_cs[e] = 1.f;
+        ep_sn[e] = 0.f;
+        ep_slot[e] = -1;
+        if (idx < 8 * 8 * MT && t < p.M) {
+          const int f0 = head * p.hd + i0 + j;
+          if (p.bias) {
+            ep_b0[e] = p.bias[f0];
+            ep_b1[e] = p.bias[f0 + half];
+          }
+          if (head < p.nh + p.nkv) {
+            int pos = p.positions[t];
+            if (pos < 0 || pos >= p.max_pos) {
+              set_status(p.status, LL_ERR_POSITION_RANGE);
+              pos = 0;
+            }
+            ep_cs[e] = p.cos_sin[(size_t)pos * p.hd + i0 + j];
+            ep_sn[e] = p.cos_sin[(size_t)pos * p.hd + half + i0 + j];
+          }
+          if (head >= p.nh && p.slot_map) ep_slot[e] = (long)p.slot_map[t];
+        }
+      }
+    }
     const int kc_end = min(kchunks, (kp + 1) * p.cpp);
     for (int kc = kp * p.cpp; kc < kc_end; ++kc, ++it) {
       const int s = (int)(it % STAGES);
@@ -377,9 +412,11 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
         // rows 0..7: features i0 + j of the head, rows 8..15: their partners i0 + j + hd/2
         const int upr = p.hd / 16, half = p.hd / 2;
         const int head = u / upr, i0 = (u - head * upr) * 8;
-        for (int idx = tid; idx < 8 * TOK; idx += GT_CONSUMERS * 32) {
+#pragma unroll
+        for (int e = 0; e < EP_ITEMS; ++e) {
+          const int idx = tid + e * GT_CONSUMERS * 32;
           const int t = idx >> 3, j = idx & 7;
-          if (t >= p.M) continue;
+          if (idx >= 8 * TOK || t >= p.M) continue;
           float x0 = 0.f, x1 = 0.f;
 #pragma unroll
           for (int wi = 0; wi < GT_CONSUMERS; ++wi) {
@@ -387,22 +424,11 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
             x1 += red[((size_t)wi * 16 + j + 8) * TOK + t];
           }
           // the unfused path rounds the projection to bfloat16 before bias and rotation: the same here
-          x0 = __bfloat162float(__float2bfloat16_rn(x0));
-          x1 = __bfloat162float(__float2bfloat16_rn(x1));
+          x0 = __bfloat162float(__float2bfloat16_rn(x0)) + ep_b0[e];
+          x1 = __bfloat162float(__float2bfloat16_rn(x1)) + ep_b1[e];
           const int f0 = head * p.hd + i0 + j;
-          if (p.bias) {
-            x0 += p.bias[f0];
-            x1 += p.bias[f0 + half];
-          }
           if (head < p.nh + p.nkv) {
-            int pos = p.positions[t];
-            if (pos < 0 || pos >= p.max_pos) {
-              set_status(p.status, LL_ERR_POSITION_RANGE);
-              pos = 0;
-            }
-            const float cs = p.cos_sin[(size_t)pos * p.hd + i0 + j];
-            const float sn = p.cos_sin[(size_t)pos * p.hd + half + i0 + j];
-            const float r0v = x0 * cs - x1 * sn, r1v = x0 * sn + x1 * cs;
+            const float r0v = x0 * ep_cs[e] - x1 * ep_sn[e], r1v = x0 * ep_sn[e] + x1 * ep_cs[e];
             x0 = r0v;
             x1 = r1v;
           }
@@ -412,7 +438,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
             q[0] = o0;
             q[half] = o1;
           } else {
-            long slot = p.slot_map ? (long)p.slot_map[t] : -1;
+            long slot = ep_slot[e];
             if (slot >= p.num_slots) {
               set_status(p.status, LL_ERR_SLOT_RANGE);
               slot = -1;

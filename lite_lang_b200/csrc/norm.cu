@@ -78,12 +78,18 @@ add_rmsnorm_bf16x8_kernel(bf16* __restrict__ out, bf16* __restrict__ residual, c
                           const float* __restrict__ w, float eps, int hidden, const int* __restrict__ rows,
                           int write_residual) {
   __shared__ float scratch[32];
+  const int i0 = threadIdx.x * 8;
+  const bool active = i0 < hidden;
+  // the norm weights do not depend on the kernel before: they are on their way before the wait for it
+  float4 wa = make_float4(0.f, 0.f, 0.f, 0.f), wb = wa;
+  if (active) {
+    wa = *reinterpret_cast<const float4*>(w + i0);
+    wb = *reinterpret_cast<const float4*>(w + i0 + 4);
+  }
   LL_PDL_WAIT();
   LL_PDL_TRIGGER();
   const int i_out = blockIdx.x;
   const int r = rows ? rows[i_out] : i_out;
-  const int i0 = threadIdx.x * 8;
-  const bool active = i0 < hidden;
   float v[8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) v[k] = 0.f;
@@ -137,8 +143,6 @@ add_rmsnorm_bf16x8_kernel(bf16* __restrict__ out, bf16* __restrict__ residual, c
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
   if (active) {
-    const float4 wa = *reinterpret_cast<const float4*>(w + i0);
-    const float4 wb = *reinterpret_cast<const float4*>(w + i0 + 4);
     const float ww[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
     uint4 ov;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
