@@ -12,7 +12,7 @@
 // so that a thread's eight values of a key row serve four tiles (P V; two keys are paired by a byte
 // permute).
 //
-// One CTA (4 warps) works on one (entry, kv head, split of the keys); its warps take the split's 16-key
+// One CTA (4 or 8 warps) works on one (entry, kv head, split of the keys); its warps take the split's 16-key
 // tiles in turn and are merged through shared memory.  The splits of an (entry, kv head) are the CTAs of
 // one thread-block cluster (1, 2, 4 or 8) and merge through distributed shared memory: every CTA
 // finishes a slice of the head dimensions.  No scratch memory, no counters, nothing spins (the cluster
@@ -21,8 +21,6 @@
 // Head sizes 64 and 128, groups of at most 8 query heads, pages of a multiple of 16 tokens.
 #include "common.cuh"
 
-#define AD_WARPS 4
-#define AD_THREADS 128
 #define AD_TILE 16
 #define AD_HEADS 8
 #define AD_BT_CACHE 256
@@ -92,23 +90,39 @@ __device__ __forceinline__ float ad_ld_peer(const float* local, unsigned rank) {
   return v;
 }
 
-template <int HD>
-__global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const AttnDecodeParams p) {
+template <int HD, int NW>
+__global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodeParams p) {
   constexpr int KS = HD / 32;   // 16-byte loads per key row and thread for Q K^T
   constexpr int VS = HD / 64;   // 16-byte loads per value row and thread
   constexpr int MT = HD / 16;   // MMA row tiles of O^T
-  __shared__ float sm_o[AD_WARPS][AD_HEADS][HD + 4];
-  __shared__ float sm_m[AD_WARPS][AD_HEADS];
-  __shared__ float sm_l[AD_WARPS][AD_HEADS];
+  __shared__ float sm_o[NW][AD_HEADS][HD + 4];
+  __shared__ float sm_m[NW][AD_HEADS];
+  __shared__ float sm_l[NW][AD_HEADS];
   __shared__ int sm_bt[AD_BT_CACHE];
-  LL_PDL_WAIT();
-  LL_PDL_TRIGGER();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int e = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   if (e >= p.n_entries) return;
+  // What the step's index arrays say (slot, context length, block table) was uploaded before the step's
+  // first kernel and is read before the wait for the kernel before this one; q and the new token's key
+  // and value are that kernel's output and are read after it.
   const int slot = p.req_slot[e];
   const int ctx = p.ctx_len[e];
+  const int pos = ctx;  // position of the new token; it looks at keys lo..pos
+  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int t_first = lo / AD_TILE, t_last = pos / AD_TILE;
+  const int ntiles = t_last - t_first + 1;
+  const int tps = (ntiles + p.nsplit - 1) / p.nsplit;
+  const int t_begin = t_first + split * tps;
+  const int t_end = min(t_last + 1, t_begin + tps);
+  const int* bt = p.block_table + (size_t)max(slot, 0) * p.bt_stride;
+  const int nt_split = t_end - t_begin;
+  const bool bt_cached = nt_split <= AD_BT_CACHE;
+  if (bt_cached && slot >= 0)
+    for (int i = tid; i < nt_split; i += (NW * 32)) sm_bt[i] = bt[((t_begin + i) * AD_TILE) / p.page_size];
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
+  __syncthreads();
   // ---- Q^T fragments: thread (g, c) holds head g, dims 32 s + 8 c .. + 7 ----
   uint4 qf[KS];
   {
@@ -119,24 +133,9 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const AttnDecod
   }
   if (slot < 0) {  // padding entry of a captured step: zeros, no reads (the same for the whole cluster)
     if (split == 0)
-      for (int i = tid; i < p.group * HD; i += AD_THREADS)
+      for (int i = tid; i < p.group * HD; i += (NW * 32))
         p.out[(size_t)e * p.out_stride + (size_t)kvh * p.group * HD + i] = __float2bfloat16_rn(0.f);
     return;
-  }
-  const int pos = ctx;  // position of the new token; it looks at keys lo..pos
-  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-  const int t_first = lo / AD_TILE, t_last = pos / AD_TILE;
-  const int ntiles = t_last - t_first + 1;
-  const int tps = (ntiles + p.nsplit - 1) / p.nsplit;
-  const int t_begin = t_first + split * tps;
-  const int t_end = min(t_last + 1, t_begin + tps);
-
-  const int* bt = p.block_table + (size_t)slot * p.bt_stride;
-  const int nt_split = t_end - t_begin;
-  const bool bt_cached = nt_split <= AD_BT_CACHE;
-  if (bt_cached) {
-    for (int i = tid; i < nt_split; i += AD_THREADS) sm_bt[i] = bt[((t_begin + i) * AD_TILE) / p.page_size];
-    __syncthreads();
   }
   auto tile_base = [&](int t) -> long {
     const int key0 = t * AD_TILE;
@@ -176,8 +175,8 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const AttnDecod
     load_k(tb);
     load_v(tb);
   }
-  for (; t < t_end; t += AD_WARPS) {
-    const int t_next = t + AD_WARPS;
+  for (; t < t_end; t += NW) {
+    const int t_next = t + NW;
     const long tb_next = (t_next < t_end) ? tile_base(t_next) : -1;
     if (tb < 0) {
       tb = tb_next;
@@ -285,16 +284,16 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const AttnDecod
     sm_o[warp][2 * c + 1][d1] = o_acc[T][3];
   }
   __syncthreads();
-  constexpr int CPR = AD_THREADS / AD_HEADS;  // 16 threads per head
+  constexpr int CPR = (NW * 32) / AD_HEADS;  // 16 threads per head
   constexpr int DPT = HD / CPR;               // 8 or 4 dims per thread
   const int row = tid / CPR, dbase = (tid % CPR) * DPT;
   float M = -INFINITY;
 #pragma unroll
-  for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, sm_m[w][row]);
+  for (int w = 0; w < NW; ++w) M = fmaxf(M, sm_m[w][row]);
   const float Ms = (M == -INFINITY) ? 0.f : M;
-  float L = 0.f, wgt[AD_WARPS];
+  float L = 0.f, wgt[NW];
 #pragma unroll
-  for (int w = 0; w < AD_WARPS; ++w) {
+  for (int w = 0; w < NW; ++w) {
     wgt[w] = ad_exp2(sm_m[w][row] - Ms);
     L += sm_l[w][row] * wgt[w];
   }
@@ -303,7 +302,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const AttnDecod
   for (int d = 0; d < DPT; ++d) {
     float a = 0.f;
 #pragma unroll
-    for (int w = 0; w < AD_WARPS; ++w) a += sm_o[w][row][dbase + d] * wgt[w];
+    for (int w = 0; w < NW; ++w) a += sm_o[w][row][dbase + d] * wgt[w];
     acc[d] = a;
   }
   if (p.nsplit == 1) {
@@ -329,7 +328,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const AttnDecod
   const unsigned rank = ad_cluster_rank();
   const int slice = HD / cs;                     // dims this CTA finishes: 8 .. 64
   const int outputs = AD_HEADS * slice;          // 64 .. 512
-  const int per = max(1, outputs / AD_THREADS);  // 1 .. 4 consecutive dims of one head per thread
+  const int per = max(1, outputs / (NW * 32));  // 1 .. 4 consecutive dims of one head per thread
   const bool worker = tid * per < outputs;
   const int o0 = worker ? tid * per : 0;
   const int row2 = o0 / slice, d0 = (int)rank * slice + (o0 - row2 * slice);
@@ -364,15 +363,17 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const AttnDecod
 
 // One new token per entry: q row e (head h at q + e*q_stride + h*hd) attends to the cached keys of
 // the request in req_slot[e] up to position ctx_len[e] (its own key is already in the cache).
-// nsplit in {1, 2, 4, 8}: CTAs per (entry, kv head), launched as one cluster.
+// nsplit in {1, 2, 4, 8}: CTAs per (entry, kv head), launched as one cluster; warps in {4, 8}: warps a CTA
+// (they take the split's 16-key tiles in turn).
 extern "C" int ll_attn_decode(void* out, long out_stride, const void* q, long q_stride, const void* k_cache,
                               const void* v_cache, const int* block_table, int bt_stride, const int* ctx_len,
                               const int* req_slot, int n_entries, int nh, int nkv, int hd, int page_size,
-                              int num_pages, int window, float scale, int nsplit, int* status, cudaStream_t stream) {
+                              int num_pages, int window, float scale, int nsplit, int warps, int* status,
+                              cudaStream_t stream) {
   if (n_entries <= 0) return 0;
   if ((hd != 64 && hd != 128) || page_size % AD_TILE != 0 || nkv <= 0 || nh % nkv != 0 || nkv > 65535)
     return (int)cudaErrorInvalidValue;
-  if (nh / nkv > AD_HEADS || !(nsplit == 1 || nsplit == 2 || nsplit == 4 || nsplit == 8))
+  if (nh / nkv > AD_HEADS || !(nsplit == 1 || nsplit == 2 || nsplit == 4 || nsplit == 8) || !(warps == 4 || warps == 8))
     return (int)cudaErrorInvalidValue;
   if ((q_stride % 8) != 0 || (out_stride % 2) != 0) return (int)cudaErrorInvalidValue;
   AttnDecodeParams p;
@@ -397,9 +398,13 @@ extern "C" int ll_attn_decode(void* out, long out_stride, const void* q, long q_
   p.nsplit = nsplit;
   p.status = status;
   dim3 grid(n_entries, nkv, nsplit);
-  if (hd == 64)
-    ll_launch_cluster(attn_decode_kernel<64>, grid, dim3(AD_THREADS), 0, stream, nsplit, p);
+  if (hd == 64 && warps == 4)
+    ll_launch_cluster(attn_decode_kernel<64, 4>, grid, dim3(128), 0, stream, nsplit, p);
+  else if (hd == 64)
+    ll_launch_cluster(attn_decode_kernel<64, 8>, grid, dim3(256), 0, stream, nsplit, p);
+  else if (warps == 4)
+    ll_launch_cluster(attn_decode_kernel<128, 4>, grid, dim3(128), 0, stream, nsplit, p);
   else
-    ll_launch_cluster(attn_decode_kernel<128>, grid, dim3(AD_THREADS), 0, stream, nsplit, p);
+    ll_launch_cluster(attn_decode_kernel<128, 8>, grid, dim3(256), 0, stream, nsplit, p);
   return LL_LAUNCH_RESULT();
 }

@@ -128,19 +128,32 @@ class GQAttention(Mixer):
     def _plan_mma(self, step, entries, max_kv_len):
         """Row blocks, splits and warps of the decode kernel for ``entries`` single-token entries."""
         group = self.num_heads // self.num_kv_heads
+        max_tiles = (max_kv_len + 15) // 16
+        if group <= 8:
+            # attn_decode: one CTA per (entry, kv head, split).  Measured on a B200 (1.5B sizes, context 2k,
+            # batch 1..64): about 128 CTAs are best, as splits of 8, 4, 2 or none, with at least 8 tiles
+            # (128 keys) a split; 8 warps a CTA, except that many clusters of 8 such CTAs do not find room
+            # side by side (batch 8: 4 warps 1.24 ms a step, 8 warps 1.44 ms).
+            base = entries * self.num_kv_heads
+            nsplit = 1
+            for n in (8, 4, 2):
+                if base * n <= 128 and n <= max(1, max_tiles // 8):
+                    nsplit = n
+                    break
+            warps = 4 if (nsplit == 8 and base * nsplit > 64) else 8
+            return entries, nsplit, True, warps
         blocks = entries * ((group + 15) // 16)
         ctas = blocks * self.num_kv_heads
-        max_tiles = (max_kv_len + 15) // 16
-        # one wave of CTAs at most, and at least 8 tiles (128 keys) a split: with less, merging the
+        # attn_mma: one wave of CTAs at most, and at least 8 tiles (128 keys) a split: with less, merging the
         # splits costs more than the split saves.  The splits of a row block form a thread-block cluster
-        # (2, 4, 8 or 16 CTAs) and merge through distributed shared memory: no scratch memory, no counters.
+        # and merge through distributed shared memory: no scratch memory, no counters.
         want = max(1, min((2 * self.SM_COUNT) // ctas, max(1, max_tiles // 8)))
         # (clusters of 16, the non-portable size, were measured slower than 8: placement costs more
         # than the shorter key ranges save)
         nsplit = 8 if want >= 8 else 4 if want >= 4 else 2 if want >= 2 else 1
         # 8 warps a CTA when the step has very few row blocks: more warps to hide instruction latency
         # behind.  Not beyond half the SMs: 8-warp CTAs fit one an SM, and clusters of 8 of them then
-        # no longer find room in one wave (measured: batch 8 got slower, batch 1 faster)
+        # no longer find room in one wave
         warps = 8 if ctas * nsplit <= self.SM_COUNT // 2 and max_tiles >= 16 * nsplit else 4
         return blocks, nsplit, group <= 16, warps
 
@@ -163,7 +176,7 @@ class GQAttention(Mixer):
                 if self.num_heads // self.num_kv_heads <= 8:
                     # keys on the M side, the group's heads on the N side of the MMA: half the work a tile
                     ops.attn_decode(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.ctx_len,
-                                    step.req_slot, n_single, *args, nsplit, step.status)
+                                    step.req_slot, n_single, *args, nsplit, step.status, warps=warps)
                 else:
                     ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q,
                                  step.ctx_len, step.req_slot, n_single, blocks, *args, nsplit, None, None,
