@@ -86,7 +86,7 @@ __device__ __forceinline__ float ad_ld_peer(const float* local, unsigned rank) {
   unsigned la = (unsigned)__cvta_generic_to_shared(local), ra;
   float v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra));
   return v;
 }
 
@@ -332,14 +332,21 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   const bool worker = tid * per < outputs;
   const int o0 = worker ? tid * per : 0;
   const int row2 = o0 / slice, d0 = (int)rank * slice + (o0 - row2 * slice);
-  float ms[8], ls[8], Mg = -INFINITY;
+  // every value wanted from the peers is asked for before the first one is used: the loads through the
+  // cluster's shared memory overlap instead of queueing behind each other's use
+  float ms[8], ls[8], ov[8][4], Mg = -INFINITY;
 #pragma unroll
   for (int sI = 0; sI < 8; ++sI)
     if (sI < cs) {
       ms[sI] = ad_ld_peer(&sm_m[0][row2], sI);
       ls[sI] = ad_ld_peer(&sm_l[0][row2], sI);
-      Mg = fmaxf(Mg, ms[sI]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (k < per) ov[sI][k] = ad_ld_peer(&sm_o[0][row2][d0 + k], sI);
     }
+#pragma unroll
+  for (int sI = 0; sI < 8; ++sI)
+    if (sI < cs) Mg = fmaxf(Mg, ms[sI]);
   const float Mgs = (Mg == -INFINITY) ? 0.f : Mg;
   float Lg = 0.f, fin[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -349,7 +356,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
       Lg += ls[sI] * ws;
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        if (k < per) fin[k] += ad_ld_peer(&sm_o[0][row2][d0 + k], sI) * ws;
+        if (k < per) fin[k] += ov[sI][k] * ws;
     }
   if (worker && row2 < p.group) {
     bf16* o2 = p.out + (size_t)e * p.out_stride + (size_t)(kvh * p.group + row2) * HD + d0;
