@@ -6,11 +6,13 @@
 //     S^T[16 keys x 8 heads] = K[16 x hd] Q^T[hd x 8],      O^T[hd x 8 heads] += V^T[hd x 16 keys] P^T[16 x 8],
 // which halves the MMAs, the accumulator registers and the softmax work per tile (8 columns instead of
 // 16 rows) and leaves room for three CTAs an SM.  P^T moves from the accumulator layout to the B-operand
-// layout with two movmatrix transposes.  Keys and values go straight from global memory into the MMA
-// registers with 16-byte loads, by the same freedom as in attention_mma.cu: the contraction index is
-// mapped to 8 contiguous head dimensions per thread (Q K^T), and the output rows of an MMA tile are mapped
-// so that a thread's eight values of a key row serve four tiles (P V; two keys are paired by a byte
-// permute).
+// layout with two movmatrix transposes.  Keys and values come through a ring of two tiles a warp in
+// shared memory, filled with cp.async one tile ahead (loads straight into registers kept too few bytes
+// in flight: the compiler holds them back behind the softmax of the tile before), and are read from it
+// with 16-byte loads by the same freedom as in attention_mma.cu: the contraction index is mapped to 8
+// contiguous head dimensions per thread (Q K^T), and the output rows of an MMA tile are mapped so that a
+// thread's eight values of a key row serve four tiles (P V; two keys are paired by a byte permute).  The
+// 16-byte chunks of a row are XOR-swizzled by the row so that both read patterns are conflict-free.
 //
 // One CTA (4 or 8 warps) works on one (entry, kv head, split of the keys); its warps take the split's 16-key
 // tiles in turn and are merged through shared memory.  The splits of an (entry, kv head) are the CTAs of
@@ -146,22 +148,40 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
     }
     return (((long)page * p.nkv + kvh) * p.page_size + (key0 % p.page_size)) * HD;
   };
-  uint4 ka[KS], kb[KS], vv[VS][4];
-  auto load_k = [&](long tb) {
+  // ---- the warp's ring of tiles in shared memory ----
+  // A warp's tiles (16 keys: 16 rows of K and of V, HD * 2 bytes each) are copied into its own ring of
+  // DEPTH stages with cp.async, 16 bytes a lane and instruction, DEPTH - 1 tiles ahead of the one being
+  // worked on: with a few hundred keys a split the loop is a chain of memory latencies, and the ring
+  // shortens it by that factor; with many requests it keeps enough bytes in flight for the bandwidth.
+  // The 16-byte piece j of row r sits at piece j ^ swizzle(r), chosen so that the fragment reads below
+  // (K: rows g, g + 8, pieces 4 s + c; V: rows 2 c (+1, +8, +9), pieces 8 h + g) hit all banks once.
+  constexpr int DEPTH = 2;   // (deeper rings were measured: no faster, and their shared memory keeps the next
+                             //  product's CTAs, which stream their weights ahead, from moving in beside this kernel)
+  constexpr int ROW_BYTES = HD * 2, CH = HD / 8;           // pieces a row
+  constexpr int TILE_BYTES = AD_TILE * ROW_BYTES;           // K (or V) of a tile
+  extern __shared__ __align__(16) unsigned char ad_ring[];
+  unsigned char* my_ring = ad_ring + (size_t)warp * DEPTH * 2 * TILE_BYTES;
+  const unsigned ring_addr = (unsigned)__cvta_generic_to_shared(my_ring);
+  auto issue_tile = [&](int stage, long tb) {   // the whole warp; tb < 0: nothing to copy (still a group)
+    if (tb >= 0) {
+      const unsigned kdst = ring_addr + stage * 2 * TILE_BYTES, vdst = kdst + TILE_BYTES;
 #pragma unroll
-    for (int s = 0; s < KS; ++s) {
-      ka[s] = ad_ldg16(p.k_cache + tb + (long)g * HD + 32 * s + 8 * c);        // key g
-      kb[s] = ad_ldg16(p.k_cache + tb + (long)(g + 8) * HD + 32 * s + 8 * c);  // key g + 8
+      for (int i = 0; i < AD_TILE * CH / 32; ++i) {
+        const int idx = lane + 32 * i, r = idx / CH, j = idx % CH;
+        const bf16* ksrc = p.k_cache + tb + (long)r * HD + 8 * j;
+        const bf16* vsrc = p.v_cache + tb + (long)r * HD + 8 * j;
+        const unsigned kd = kdst + r * ROW_BYTES + ((j ^ (4 * (r & 1))) << 4);
+        const unsigned vd = vdst + r * ROW_BYTES + ((j ^ (2 * ((r >> 1) & 3))) << 4);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kd), "l"(ksrc) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vd), "l"(vsrc) : "memory");
+      }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  auto load_v = [&](long tb) {
-#pragma unroll
-    for (int h = 0; h < VS; ++h) {
-      vv[h][0] = ad_ldg16(p.v_cache + tb + (long)(2 * c) * HD + 64 * h + 8 * g);
-      vv[h][1] = ad_ldg16(p.v_cache + tb + (long)(2 * c + 1) * HD + 64 * h + 8 * g);
-      vv[h][2] = ad_ldg16(p.v_cache + tb + (long)(2 * c + 8) * HD + 64 * h + 8 * g);
-      vv[h][3] = ad_ldg16(p.v_cache + tb + (long)(2 * c + 9) * HD + 64 * h + 8 * g);
-    }
+  auto lds16 = [&](unsigned addr) -> uint4 {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
   };
 
   float o_acc[MT][4];  // O^T tile (h, jj): rows = dims 64 h + 8 g + jj and + 4, columns = heads 2c, 2c + 1
@@ -169,22 +189,38 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   for (int t = 0; t < MT; ++t) o_acc[t][0] = o_acc[t][1] = o_acc[t][2] = o_acc[t][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // heads 2c and 2c + 1
 
-  int t = t_begin + warp;
-  long tb = (t < t_end) ? tile_base(t) : -1;
-  if (t < t_end && tb >= 0) {
-    load_k(tb);
-    load_v(tb);
+  // tiles t_begin + warp, + NW, ...: the first DEPTH - 1 are asked for now, one more in every iteration
+  long tbase[DEPTH];   // cache offset of the tile in each stage (< 0: an invalid page, skipped)
+#pragma unroll
+  for (int d = 0; d < DEPTH - 1; ++d) {
+    const int td = t_begin + warp + d * NW;
+    tbase[d] = (td < t_end) ? tile_base(td) : -1;
+    issue_tile(d, tbase[d]);
   }
-  for (; t < t_end; t += NW) {
-    const int t_next = t + NW;
-    const long tb_next = (t_next < t_end) ? tile_base(t_next) : -1;
-    if (tb < 0) {
-      tb = tb_next;
-      if (tb >= 0) {
-        load_k(tb);
-        load_v(tb);
-      }
-      continue;
+  int it = 0;
+  for (int t = t_begin + warp; t < t_end; t += NW, ++it) {
+    const int stage = it % DEPTH;
+    asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 2) : "memory");   // this lane's copies of tile `it` are in
+    __syncwarp();                                                           // and so are the other lanes'
+    {   // the stage freed in the iteration before takes the tile DEPTH - 1 ahead
+      const int ta = t + (DEPTH - 1) * NW, sa = (it + DEPTH - 1) % DEPTH;
+      const long tba = (ta < t_end) ? tile_base(ta) : -1;
+#pragma unroll
+      for (int d = 0; d < DEPTH; ++d)
+        if (d == sa) tbase[d] = tba;
+      issue_tile(sa, tba);
+    }
+    long tb = -1;
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d)
+      if (d == stage) tb = tbase[d];
+    if (tb < 0) continue;
+    const unsigned kst = ring_addr + stage * 2 * TILE_BYTES, vst = kst + TILE_BYTES;
+    uint4 ka[KS], kb[KS], vv[VS][4];
+#pragma unroll
+    for (int s = 0; s < KS; ++s) {
+      ka[s] = lds16(kst + g * ROW_BYTES + (((4 * s + c) ^ (4 * (g & 1))) << 4));          // key g
+      kb[s] = lds16(kst + (g + 8) * ROW_BYTES + (((4 * s + c) ^ (4 * (g & 1))) << 4));    // key g + 8
     }
     // ---- S^T = K Q^T: rows = keys g and g + 8, columns = heads 2c, 2c + 1 ----
     float s_acc[4] = {0.f, 0.f, 0.f, 0.f}, s_odd[4] = {0.f, 0.f, 0.f, 0.f};
@@ -193,7 +229,6 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
       ad_mma(s_acc, ka[s].x, kb[s].x, ka[s].y, kb[s].y, qf[s].x, qf[s].y);
       ad_mma(s_odd, ka[s].z, kb[s].z, ka[s].w, kb[s].w, qf[s].z, qf[s].w);
     }
-    if (tb_next >= 0) load_k(tb_next);
     // ---- scale, mask, online softmax per head (column) ----
     const int key0 = t * AD_TILE;
     const bool boundary = (key0 + AD_TILE - 1 > pos) || (key0 < lo);
@@ -231,6 +266,15 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
     // P^T as the B operand: (keys 2c, 2c+1 | 2c+8, 2c+9; head g) from (key g | g+8; heads 2c, 2c+1)
     const unsigned b0 = ad_movmatrix(ad_pack(s_acc[0], s_acc[1]));
     const unsigned b1 = ad_movmatrix(ad_pack(s_acc[2], s_acc[3]));
+#pragma unroll
+    for (int h = 0; h < VS; ++h) {
+      const unsigned sw = (unsigned)(2 * (c & 3));   // rows 2 c, 2 c + 1, 2 c + 8, 2 c + 9 share the swizzle
+      const unsigned piece = ((unsigned)(8 * h + g) ^ sw) << 4;
+      vv[h][0] = lds16(vst + (2 * c) * ROW_BYTES + piece);
+      vv[h][1] = lds16(vst + (2 * c + 1) * ROW_BYTES + piece);
+      vv[h][2] = lds16(vst + (2 * c + 8) * ROW_BYTES + piece);
+      vv[h][3] = lds16(vst + (2 * c + 9) * ROW_BYTES + piece);
+    }
     // ---- O^T = O^T * alpha + V^T P^T ----
     const bool rescale = (alpha[0] != 1.f) || (alpha[1] != 1.f);
 #pragma unroll
@@ -257,9 +301,8 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
         ad_mma(o_acc[T], a0, a1, a2, a3, b0, b1);
       }
     }
-    if (tb_next >= 0) load_v(tb_next);
-    tb = tb_next;
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 
   // ---- merge the four warps (rows of the merge = heads) ----
 #pragma unroll
@@ -405,13 +448,20 @@ extern "C" int ll_attn_decode(void* out, long out_stride, const void* q, long q_
   p.nsplit = nsplit;
   p.status = status;
   dim3 grid(n_entries, nkv, nsplit);
-  if (hd == 64 && warps == 4)
-    ll_launch_cluster(attn_decode_kernel<64, 4>, grid, dim3(128), 0, stream, nsplit, p);
-  else if (hd == 64)
-    ll_launch_cluster(attn_decode_kernel<64, 8>, grid, dim3(256), 0, stream, nsplit, p);
-  else if (warps == 4)
-    ll_launch_cluster(attn_decode_kernel<128, 4>, grid, dim3(128), 0, stream, nsplit, p);
-  else
-    ll_launch_cluster(attn_decode_kernel<128, 8>, grid, dim3(256), 0, stream, nsplit, p);
+  // the warps' rings: two stages of a K and a V tile each
+  const size_t ring = (size_t)warps * 2 * 2 * AD_TILE * hd * 2;
+  if (hd == 64 && warps == 4) {
+    cudaFuncSetAttribute(attn_decode_kernel<64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+    ll_launch_cluster(attn_decode_kernel<64, 4>, grid, dim3(128), ring, stream, nsplit, p);
+  } else if (hd == 64) {
+    cudaFuncSetAttribute(attn_decode_kernel<64, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+    ll_launch_cluster(attn_decode_kernel<64, 8>, grid, dim3(256), ring, stream, nsplit, p);
+  } else if (warps == 4) {
+    cudaFuncSetAttribute(attn_decode_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+    ll_launch_cluster(attn_decode_kernel<128, 4>, grid, dim3(128), ring, stream, nsplit, p);
+  } else {
+    cudaFuncSetAttribute(attn_decode_kernel<128, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+    ll_launch_cluster(attn_decode_kernel<128, 8>, grid, dim3(256), ring, stream, nsplit, p);
+  }
   return LL_LAUNCH_RESULT();
 }
