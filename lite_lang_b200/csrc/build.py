@@ -39,6 +39,7 @@ LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "gemm_smallm": (("gemm_smallm.cu",), ()),
     "gemm_stream": (("gemm_stream.cu",), ()),
     "gemm_tc": (("gemm_tc.cu",), ()),
+    "gemm_pair": (("gemm_pair.cu",), ()),
     "attn_tc": (("attention_prefill_tc.cu",), ()),
     "attn_mma_static": (("attention_mma_static.cu",), ()),
 }

@@ -34,6 +34,7 @@ _STATUS_TEXT = {
     4: "a position outside the position table",
     5: "a bounded wait inside a kernel (TMA or tensor-core pipeline) that ran out",
     6: "a shared-memory window that is not aligned as the kernel needs",
+    7: "tensor memory of a pair of CTAs that is not at the same columns in both",
 }
 
 

@@ -661,6 +661,35 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: boo
     return out
 
 
+PAIR_MIN_M = 65     # from this many tokens on (measured from 129 to 4,096) the two-SM tcgen05 kernel with the
+                    # activation in its epilogue is ahead of a library product followed by ``silu_mul``
+
+
+def pair_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether ``gemm_pair`` takes this product: bfloat16, K % 8 == 0, 16-byte aligned rows."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] > 0
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.shape[1] % 8 == 0
+            and weight.is_contiguous() and weight.shape[1] == x.shape[1]
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False,
+              status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = x @ weight.T for many bfloat16 tokens on the tcgen05 tensor cores, a pair of SMs a tile of
+    256 tokens x 256 columns.  ``gated``: weight is [2 I, K] and out = silu(gate) * up, the activation done
+    on the accumulator, so gate and up never go to memory."""
+    _need_cuda(x, weight, out, status)
+    _need(pair_supported(x, weight), "gemm_pair: bfloat16, K % 8 == 0, 16-byte aligned rows")
+    m, k = x.shape
+    n = weight.shape[0] // 2 if gated else weight.shape[0]
+    _need(out.dtype == torch.bfloat16 and out.dim() == 2 and out.shape[0] == m and out.shape[1] == n
+          and out.stride(1) == 1, "gemm_pair: out is bfloat16 [M, N] with unit column stride")
+    load_library("gemm_pair").call(
+        "ll_gemm_pair", _ptr(out), c_long(out.stride(0)), _ptr(x), c_long(x.stride(0)), _ptr(weight), c_int(m),
+        c_int(n), c_int(k), c_int(1 if gated else 0), c_int(sm_count(x.device)), _ptr(status), _stream())
+    return out
+
+
 def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x @ Wg.T) * (x @ Wu.T) with W = [Wg; Wu]: fused for few tokens, else product + kernel."""
     inter = w_gate_up.shape[0] // 2
@@ -671,6 +700,8 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         return gemm_stream(x, w_gate_up, act, 1)
     if smallm_preferred(x, w_gate_up, gated=True):
         return gemm_smallm(x, w_gate_up, act, gated=True)
+    if TC_ENABLED and x.shape[0] >= PAIR_MIN_M and pair_supported(x, w_gate_up):
+        return gemm_pair(x, w_gate_up, act, gated=True)
     gu = linear(x, w_gate_up)
     silu_mul(act, gu)
     return act

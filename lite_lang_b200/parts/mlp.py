@@ -45,7 +45,7 @@ class GatedMLP(FeedForward):
 
     def kernel_libraries(self):
         bf16 = self.w_down is not None and self.w_down.dtype == torch.bfloat16
-        return ["core", "gemm_smallm", "gemm_stream", "gemm_tc"] if bf16 else ["core"]
+        return ["core", "gemm_smallm", "gemm_stream", "gemm_tc", "gemm_pair"] if bf16 else ["core"]
 
     def weight_bytes(self) -> int:
         return self.w_gate_up.numel() * self.w_gate_up.element_size() + self.w_down.numel() * self.w_down.element_size()

@@ -721,6 +721,60 @@ def test_gemm_tc_refuses_what_it_cannot_do():
         ops.gemm_tc(x[:8, :32], w[:, :32].contiguous(), torch.empty(8, 128, dtype=torch.bfloat16, device=dev()))
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 512, 448), (300, 331, 200), (1, 40, 8), (700, 1100, 1096)])
+def test_gemm_pair_is_exact_on_small_integers(m, n, k):
+    """The two-SM tcgen05 product on integer operands whose sums are exact in float32 and in bfloat16
+    (|sum| <= 256): a wrong half of the pair, descriptor, swizzle or tensor-memory lane is a wrong integer."""
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(44)
+    x = torch.randint(-1, 2, (m, k), generator=g).to(torch.bfloat16)
+    w = torch.randint(-1, 2, (n, k), generator=g).to(torch.bfloat16)
+    w[:, k // 4:] *= (torch.rand(n, k - k // 4, generator=g) < 128.0 / k).to(torch.bfloat16)   # keep |sum| small
+    ref = x.double() @ w.double().t()
+    assert float(ref.abs().max()) <= 256
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    out = torch.full((m + 1, n + 8), 7.0, dtype=torch.bfloat16, device=dev())
+    for _ in range(2):
+        ops.gemm_pair(x.to(dev()), w.to(dev()), out[:m, :n], status=status)
+    assert status.item() == 0
+    assert torch.equal(out[:m, :n].double().cpu(), ref)
+    assert bool((out[m:] == 7).all()) and bool((out[:, n:] == 7).all())     # nothing written outside
+
+
+@pytest.mark.parametrize("m,inter,k", [(2048, 8960, 1536), (512, 203, 384), (777, 1000, 264), (256, 128, 64)])
+def test_gemm_pair_gated(m, inter, k):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(45)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(dev())
+    w = (2 * torch.randn(2 * inter, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(dev())
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    fused = torch.full((m, inter), 7.0, dtype=torch.bfloat16, device=dev())
+    for _ in range(2):
+        ops.gemm_pair(x, w, fused, gated=True, status=status)
+    assert status.item() == 0
+    rows = torch.arange(0, m, max(1, m // 97))          # a sample of rows keeps the float64 reference quick
+    xs = x[rows].double().cpu()
+    gate = (xs @ w[:inter].double().cpu().t()).to(torch.bfloat16).double()
+    up = (xs @ w[inter:].double().cpu().t()).to(torch.bfloat16).double()
+    ref = gate / (1 + torch.exp(-gate)) * up
+    err = float((fused[rows].double().cpu() - ref).abs().max()) / float(ref.abs().max())
+    assert err <= 1.5e-2, err
+    # and against the unfused path it replaces, everywhere
+    unfused = torch.empty(m, inter, dtype=torch.bfloat16, device=dev())
+    ops.silu_mul(unfused, torch.mm(x, w.t()))
+    assert float((fused.float() - unfused.float()).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
+def test_gemm_pair_refuses_what_it_cannot_do():
+    from lite_lang_b200 import ops
+    x = torch.zeros(256, 68, dtype=torch.bfloat16, device=dev())
+    w = torch.zeros(128, 68, dtype=torch.bfloat16, device=dev())
+    with pytest.raises((RuntimeError, ValueError)):
+        ops.gemm_pair(x, w, torch.empty(256, 128, dtype=torch.bfloat16, device=dev()))      # K % 8
+    with pytest.raises((RuntimeError, ValueError)):
+        ops.gemm_pair(x[:, :64], w[:, :64].contiguous(), torch.empty(256, 128, dtype=torch.float32, device=dev()))
+
+
 @pytest.mark.parametrize("m,hidden,nh,nkv,hd,ps", [(8, 1536, 12, 2, 128, 16), (1, 256, 3, 1, 64, 32), (19, 512, 4, 4, 32, 16),
                                                    (32, 768, 6, 2, 128, 64)])
 def test_gemm_stream_qkv_rope_equals_the_three_kernels_it_replaces(m, hidden, nh, nkv, hd, ps):
