@@ -14,14 +14,20 @@
 // issues the MMAs (256 x 256 x 16), which read both CTAs' shared memory and write both tensor memories.
 // In gated mode the even CTA's weight rows are 128 gate features and the odd CTA's the up rows of the same
 // features: columns 0..127 of the accumulator are gate, 128..255 up.
+// In q|k|v mode a tile's 256 columns are whole heads (head size 64, 128 or 256), and the epilogue does what
+// follows the projection: bias, the half-split rotation of q and k by the token's position (both halves of a
+// head are columns of the same lane), q to its output, k and v into the token's slot of the paged cache.  The
+// q|k|v row never goes to memory and one kernel stands for two.
 //
-// Roles in a CTA (192 threads):
+// Roles in a CTA (320 threads):
 //   warp 0    producer: one thread keeps a ring of six 32 KB stages filled; both CTAs' copies complete on
 //             the even CTA's `full` barrier of the stage;
 //   warp 1    MMA: in the even CTA one thread issues the MMAs of a stage when it is full, and a
 //             tcgen05.commit hands the stage back to both producers; the accumulator is double-buffered
 //             (2 x 256 columns), so the MMAs of the next tile run while this one's epilogue reads;
-//   warps 2-5 epilogue: tensor memory -> registers -> activation -> 16-byte stores of the thread's own row.
+//   warps 2-9 epilogue: tensor memory -> registers -> activation -> 16-byte stores of the thread's own row;
+//             a warp reads the 32 lanes that its number modulo 4 gives, so two warps share a token row and each
+//             takes half of the tile's columns (a pair with one tile has nothing to hide its epilogue behind).
 // Tiles go to the pairs round-robin, tokens fastest, so the pairs that run together share weight rows in L2.
 //
 // Every mbarrier wait is bounded (about two seconds of clock): a wait that runs out records
@@ -36,12 +42,13 @@
 
 #define LL_ERR_WAIT_TIMEOUT 5
 #define LL_ERR_TMEM_PAIR 7
-#define GP_THREADS 192
+#define GP_THREADS 320
 #define GP_STAGES 6
 #define GP_A_BYTES (128 * 128)
 #define GP_STAGE_BYTES (2 * GP_A_BYTES)
 #define GP_MODE_PLAIN 0
 #define GP_MODE_GATED 1
+#define GP_MODE_QKV 2
 #define GP_SMEM (1024 + GP_STAGES * GP_STAGE_BYTES + (2 * GP_STAGES + 4) * 8 + 16)
 
 __device__ __forceinline__ unsigned gp_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -165,6 +172,16 @@ struct GpParams {
   int tiles;        // m_tiles x column tiles (plain: 256 features a tile, gated: 128)
   int vec_ok;       // the output takes 16-byte pieces (aligned base and stride, N a multiple of 8)
   int* status;
+  // q|k|v mode only: what follows the projection (N = (nh + 2 nkv) hd; out is q [M, nh hd])
+  const float* bias;      // float32 [N] or null
+  const int* positions;   // int32 [M]
+  const float* cos_sin;   // float32 [max_pos, hd]: cos of the hd/2 angles, then sin
+  int max_pos, nh, nkv, hd;
+  const int* slot_map;    // int32 [M] or null (no cache write); slot = page * page_size + offset, -1 skips
+  bf16* k_cache;          // [num_pages, nkv, page_size, hd]
+  bf16* v_cache;
+  int page_size;
+  long num_slots;
 };
 
 // 32 accumulator columns -> 32 bfloat16 features of the thread's row, from column f0 on
@@ -188,18 +205,181 @@ __device__ __forceinline__ void gp_store32(const GpParams& p, bf16* row, int f0,
   }
 }
 
+// 32 values -> 32 bfloat16 at dst (16-byte aligned)
+__device__ __forceinline__ void gp_put32(bf16* dst, const float (&v)[32]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint4 pk;
+    unsigned* w = reinterpret_cast<unsigned*>(&pk);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * q + 2 * j], v[8 * q + 2 * j + 1]);
+      w[j] = *reinterpret_cast<const unsigned*>(&h);
+    }
+    *reinterpret_cast<uint4*>(dst + 8 * q) = pk;
+  }
+}
+// The q|k|v epilogue works in two steps, because a thread that owns a token row (a lane of tensor memory) would
+// read its own row of the cos/sin table and write its own rows of q and of the cache: 32 different lines an
+// instruction.  Step 1: the accumulator tile goes to shared memory, rounded to bfloat16 (as the unfused path
+// sees the product), [128 rows][256 columns], the 16-byte pieces of every 128 bytes XOR-swizzled by the row.
+// Step 2: consecutive threads take consecutive pieces of a row, as the stand-alone rotation kernel does.
+#define GP_STG_BYTES (128 * 512)
+__device__ __forceinline__ unsigned gp_stg_offset(int row, int piece) {   // piece: 8 columns
+  return (unsigned)(row * 512 + (((piece & ~7) | ((piece ^ row) & 7)) << 4));
+}
+// step 1 for 32 columns of the thread's row
+__device__ __forceinline__ void gp_stage32(unsigned char* stg, int row, int col0, const unsigned (&a)[32]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint4 pk;
+    unsigned* w = reinterpret_cast<unsigned*>(&pk);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(a[8 * q + 2 * j]), __uint_as_float(a[8 * q + 2 * j + 1]));
+      w[j] = *reinterpret_cast<const unsigned*>(&h);
+    }
+    *reinterpret_cast<uint4*>(stg + gp_stg_offset(row, (col0 >> 3) + q)) = pk;
+  }
+}
+__device__ __forceinline__ void gp_unpack8(const uint4& a, float (&x)[8]) {
+  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(a2[k]);
+    x[2 * k] = f.x;
+    x[2 * k + 1] = f.y;
+  }
+}
+__device__ __forceinline__ uint4 gp_pack8(const float (&x)[8]) {
+  uint4 o;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) o2[k] = __floats2bfloat162_rn(x[2 * k], x[2 * k + 1]);
+  return o;
+}
+// step 2 for the CTA's 128 rows.  A work item is 8 columns of the first half of a head and their 8 partners in
+// the second half; a row has 16 of them, and epilogue thread e (of 256) takes item e % 16 of the rows
+// e / 16 + 16 k, k = 0..7: the same head and columns in eight rows.  What it needs from global memory for
+// that (bias, the rows' positions and cache slots) does not depend on the product and is read while the MMAs
+// of the tile still run (gp_qkv_prepare); the rows' cos and sin are asked for one row ahead.
+struct GpQkvPrep {
+  int pos[8];
+  int slot[8];
+  float b0[8], b1[8];
+};
+__device__ __forceinline__ void gp_qkv_prepare(const GpParams& p, int e, int row0, int head0, GpQkvPrep& w) {
+  const int hd = p.hd, half = hd >> 1, per_head = half >> 3;
+  const int pi = e & 15, hl = pi / per_head, i0 = (pi - hl * per_head) << 3, h = head0 + hl;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int row = row0 + (e >> 4) + 16 * k;
+    w.pos[k] = row < p.M ? p.positions[row] : 0;
+    w.slot[k] = (row < p.M && p.slot_map != nullptr) ? p.slot_map[row] : -1;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) w.b0[j] = w.b1[j] = 0.f;
+  if (p.bias != nullptr && h < p.nh + 2 * p.nkv) {
+    const float* bb = p.bias + (size_t)h * hd + i0;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const float4 x = __ldg(reinterpret_cast<const float4*>(bb) + q);
+      const float4 y = __ldg(reinterpret_cast<const float4*>(bb + half) + q);
+      w.b0[4 * q] = x.x; w.b0[4 * q + 1] = x.y; w.b0[4 * q + 2] = x.z; w.b0[4 * q + 3] = x.w;
+      w.b1[4 * q] = y.x; w.b1[4 * q + 1] = y.y; w.b1[4 * q + 2] = y.z; w.b1[4 * q + 3] = y.w;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if (w.pos[k] < 0 || w.pos[k] >= p.max_pos) {
+      set_status(p.status, LL_ERR_POSITION_RANGE);
+      w.pos[k] = 0;
+    }
+    if ((long)w.slot[k] >= p.num_slots) {
+      set_status(p.status, LL_ERR_SLOT_RANGE);
+      w.slot[k] = -1;
+    }
+  }
+}
+__device__ __forceinline__ void gp_qkv_finish(const GpParams& p, const unsigned char* stg, int e, int row0, int head0,
+                                              const GpQkvPrep& w) {
+  const int hd = p.hd, half = hd >> 1, per_head = half >> 3;
+  const int pi = e & 15, hl = pi / per_head, i0 = (pi - hl * per_head) << 3, h = head0 + hl;
+  if (h >= p.nh + 2 * p.nkv) return;
+  const bool rotate = h < p.nh + p.nkv;   // q or k head; v heads: bias and store
+  const int piece = (hl * hd + i0) >> 3;
+  float4 cs[4];                           // cos (2) and sin (2) of the row in hand
+  auto ask = [&](int k, float4 (&t)[4]) {
+    const float* src = p.cos_sin + (size_t)w.pos[k] * hd + i0;
+    t[0] = __ldg(reinterpret_cast<const float4*>(src));
+    t[1] = __ldg(reinterpret_cast<const float4*>(src) + 1);
+    t[2] = __ldg(reinterpret_cast<const float4*>(src + half));
+    t[3] = __ldg(reinterpret_cast<const float4*>(src + half) + 1);
+  };
+  if (rotate) ask(0, cs);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int r = (e >> 4) + 16 * k, row = row0 + r;
+    float4 nxt[4];
+    if (rotate && k + 1 < 8) ask(k + 1, nxt);
+    bf16* dst = nullptr;
+    if (row < p.M) {
+      if (h < p.nh) {
+        dst = p.out + (size_t)row * p.out_stride + (size_t)h * hd;
+      } else if (w.slot[k] >= 0) {
+        const int page = w.slot[k] / p.page_size;
+        const int off = w.slot[k] - page * p.page_size;
+        dst = rotate ? p.k_cache + (((size_t)page * p.nkv + (h - p.nh)) * p.page_size + off) * hd
+                     : p.v_cache + (((size_t)page * p.nkv + (h - p.nh - p.nkv)) * p.page_size + off) * hd;
+      }
+    }
+    if (dst != nullptr) {
+      float x0[8], x1[8];
+      gp_unpack8(*reinterpret_cast<const uint4*>(stg + gp_stg_offset(r, piece)), x0);
+      gp_unpack8(*reinterpret_cast<const uint4*>(stg + gp_stg_offset(r, piece + (half >> 3))), x1);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        x0[j] += w.b0[j];
+        x1[j] += w.b1[j];
+      }
+      if (rotate) {
+        const float c[8] = {cs[0].x, cs[0].y, cs[0].z, cs[0].w, cs[1].x, cs[1].y, cs[1].z, cs[1].w};
+        const float sn[8] = {cs[2].x, cs[2].y, cs[2].z, cs[2].w, cs[3].x, cs[3].y, cs[3].z, cs[3].w};
+        float o0[8], o1[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o0[j] = x0[j] * c[j] - x1[j] * sn[j];
+          o1[j] = x0[j] * sn[j] + x1[j] * c[j];
+        }
+        *reinterpret_cast<uint4*>(dst + i0) = gp_pack8(o0);
+        *reinterpret_cast<uint4*>(dst + i0 + half) = gp_pack8(o1);
+      } else {
+        *reinterpret_cast<uint4*>(dst + i0) = gp_pack8(x0);
+        *reinterpret_cast<uint4*>(dst + i0 + half) = gp_pack8(x1);
+      }
+    }
+    if (rotate && k + 1 < 8) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) cs[j] = nxt[j];
+    }
+  }
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(GP_THREADS)
 gemm_pair_kernel(const GpParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap) {
-  constexpr int STAGES = GP_STAGES, STAGE_BYTES = GP_STAGE_BYTES, A_BYTES = GP_A_BYTES;
+  // (q|k|v mode gives two of the six stages' room to its epilogue's staging tile)
+  constexpr int STAGES = (MODE == GP_MODE_QKV) ? GP_STAGES - GP_STG_BYTES / GP_STAGE_BYTES : GP_STAGES;
+  constexpr int STAGE_BYTES = GP_STAGE_BYTES, A_BYTES = GP_A_BYTES;
   constexpr int COLS = (MODE == GP_MODE_GATED) ? 128 : 256;   // output features a tile
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 4);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + GP_STAGES * STAGE_BYTES);
+  unsigned char* stg = smem + STAGES * STAGE_BYTES;   // q|k|v mode only
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * GP_STAGES + 4);
   const unsigned stage0 = gp_smem(smem);
-  const unsigned full0 = gp_smem(bars), empty0 = gp_smem(bars + STAGES);
-  const unsigned acc_full0 = gp_smem(bars + 2 * STAGES), acc_empty0 = gp_smem(bars + 2 * STAGES + 2);
+  const unsigned full0 = gp_smem(bars), empty0 = gp_smem(bars + GP_STAGES);
+  const unsigned acc_full0 = gp_smem(bars + 2 * GP_STAGES), acc_empty0 = gp_smem(bars + 2 * GP_STAGES + 2);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned rank = gp_cluster_rank();   // 0: issues the MMAs and owns the `full` and `acc_empty` barriers
@@ -215,7 +395,7 @@ gemm_pair_kernel(const GpParams p, const __grid_constant__ CUtensorMap wmap, con
     }
     for (int b = 0; b < 2; ++b) {
       gp_mbar_init(acc_full0 + 8 * b, 1);    // one commit
-      gp_mbar_init(acc_empty0 + 8 * b, 8);   // the four epilogue warps of both CTAs
+      gp_mbar_init(acc_empty0 + 8 * b, 16);  // the eight epilogue warps of both CTAs
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -284,20 +464,33 @@ gemm_pair_kernel(const GpParams p, const __grid_constant__ CUtensorMap wmap, con
         }
       }
     } else {
-      // ------------------------------ epilogue (warps 2..5) ------------------------------
-      const int ew = warp & 3;   // the 32 tensor-memory lanes this warp may read: 32 ew .. 32 ew + 31
+      // ------------------------------ epilogue (warps 2..9) ------------------------------
+      const int ew = warp & 3;          // the 32 tensor-memory lanes this warp may read: 32 ew .. 32 ew + 31
+      const int eh = (warp - 2) >> 2;   // which half of the tile's columns it takes
       const unsigned acc_empty_lead = gp_mapa(acc_empty0, 0);
       int tl = 0;
       for (int t = pair; t < p.tiles; t += pairs, ++tl) {
         const int mt = t % p.m_tiles, nt = t / p.m_tiles;
         const int b = tl & 1;
         const int row = mt * 256 + (int)rank * 128 + 32 * ew + lane;
+        GpQkvPrep prep;
+        if (MODE == GP_MODE_QKV) gp_qkv_prepare(p, tid - 64, mt * 256 + (int)rank * 128, nt * (256 / p.hd), prep);
         gp_mbar_wait(acc_full0 + 8 * b, (unsigned)((tl >> 1) & 1), p.status, dead);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned taddr = tmem + ((unsigned)(32 * ew) << 16) + (unsigned)(b * 256);
+        if (MODE == GP_MODE_QKV) {
+          const int r = 32 * ew + lane;
+#pragma unroll 1
+          for (int c = eh * 4; c < eh * 4 + 4; ++c) {
+            unsigned a[32];
+            gp_ld32_issue(taddr + 32 * c, a);
+            gp_ld_wait(a);
+            gp_stage32(stg, r, 32 * c, a);
+          }
+        } else {
         bf16* out_row = p.out + (size_t)(row < p.M ? row : 0) * p.out_stride;
 #pragma unroll 1
-        for (int c = 0; c < COLS / 32; ++c) {
+        for (int c = eh * (COLS / 64); c < (eh + 1) * (COLS / 64); ++c) {
           float v[32];
           if (MODE == GP_MODE_GATED) {
             unsigned g[32], u[32];
@@ -322,9 +515,15 @@ gemm_pair_kernel(const GpParams p, const __grid_constant__ CUtensorMap wmap, con
           }
           if (row < p.M) gp_store32(p, out_row, nt * COLS + 32 * c, v);
         }
+        }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) gp_mbar_arrive_cluster(acc_empty_lead + 8 * b);
+        if (MODE == GP_MODE_QKV) {
+          asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps: the staged tile is complete
+          gp_qkv_finish(p, stg, tid - 64, mt * 256 + (int)rank * 128, nt * (256 / p.hd), prep);
+          asm volatile("bar.sync 1, 256;" ::: "memory");   // it may be overwritten by the next tile
+        }
       }
     }
   }
@@ -440,6 +639,51 @@ extern "C" int ll_gemm_pair(void* out, long out_stride, const void* x, long x_st
   p.K = K;
   p.status = status;
   p.vec_ok = ((uintptr_t)out % 16 == 0 && out_stride % 8 == 0 && N % 8 == 0) ? 1 : 0;
+  p.bias = nullptr;
+  p.positions = nullptr;
+  p.cos_sin = nullptr;
+  p.slot_map = nullptr;
+  p.k_cache = p.v_cache = nullptr;
+  p.max_pos = p.nh = p.nkv = p.hd = p.page_size = 0;
+  p.num_slots = 0;
   return gated ? gp_launch<GP_MODE_GATED>(p, w, x, x_stride, sm_count, stream)
                : gp_launch<GP_MODE_PLAIN>(p, w, x, x_stride, sm_count, stream);
+}
+
+// The q|k|v projection of an attention layer with what follows it: qkv = x W^T (+ bias), q and k rotated by
+// the token's position (half-split pairs, whole head), q -> q_out [M, nh hd] (bfloat16, row stride q_stride),
+// k and v -> the cache plane at slot_map[token] (null: no cache write).  w: [(nh + 2 nkv) hd, K]; head size 64,
+// 128 or 256; cos_sin: float32 [max_pos, hd]; bias: float32 or null.
+extern "C" int ll_gemm_pair_qkv_rope(void* q_out, long q_stride, const void* x, long x_stride, const void* w, int M, int K,
+                                     const float* bias, const int* positions, const float* cos_sin, int max_pos, int nh,
+                                     int nkv, int hd, const int* slot_map, void* k_cache, void* v_cache, int page_size,
+                                     long num_slots, int sm_count, int* status, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (K <= 0 || (K % 8) != 0 || (x_stride % 8) != 0 || sm_count < 2 || (hd != 64 && hd != 128 && hd != 256) || nh <= 0 ||
+      nkv <= 0 || positions == nullptr || cos_sin == nullptr || (q_stride % 8) != 0 || (uintptr_t)q_out % 16 != 0 ||
+      (bias != nullptr && (uintptr_t)bias % 16 != 0) || (uintptr_t)cos_sin % 16 != 0 ||
+      (slot_map != nullptr && (k_cache == nullptr || v_cache == nullptr || page_size <= 0 || (uintptr_t)k_cache % 16 != 0 ||
+                               (uintptr_t)v_cache % 16 != 0)))
+    return (int)cudaErrorInvalidValue;
+  GpParams p;
+  p.out = reinterpret_cast<bf16*>(q_out);
+  p.out_stride = q_stride;
+  p.M = M;
+  p.N = (nh + 2 * nkv) * hd;
+  p.K = K;
+  p.status = status;
+  p.vec_ok = 1;
+  p.bias = bias;
+  p.positions = positions;
+  p.cos_sin = cos_sin;
+  p.max_pos = max_pos;
+  p.nh = nh;
+  p.nkv = nkv;
+  p.hd = hd;
+  p.slot_map = slot_map;
+  p.k_cache = reinterpret_cast<bf16*>(k_cache);
+  p.v_cache = reinterpret_cast<bf16*>(v_cache);
+  p.page_size = page_size;
+  p.num_slots = num_slots;
+  return gp_launch<GP_MODE_QKV>(p, w, x, x_stride, sm_count, stream);
 }

@@ -690,6 +690,52 @@ def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: b
     return out
 
 
+def pair_qkv_supported(x: torch.Tensor, w_qkv: torch.Tensor, head_dim: int, rot_dim: int) -> bool:
+    """Whether the two-SM tcgen05 projection with bias, rotation and cache write in its epilogue takes
+    this step: whole heads in a tile of 256 columns, rotation of the whole head."""
+    return TC_ENABLED and pair_supported(x, w_qkv) and head_dim in (64, 128, 256) and rot_dim == head_dim
+
+
+def pair_qkv_preferred(x: torch.Tensor, w_qkv: torch.Tensor) -> bool:
+    """Where it was measured ahead of a library product followed by ``bias_rope_store``: when the
+    tiles of 256 tokens x 256 columns are enough for a good part of the SM pairs."""
+    tiles = ((x.shape[0] + 255) // 256) * ((w_qkv.shape[0] + 255) // 256)
+    return tiles * 4 >= sm_count(x.device)
+
+
+def gemm_pair_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor],
+                       positions: torch.Tensor, cos_sin: torch.Tensor, num_heads: int, num_kv_heads: int,
+                       head_dim: int, slot_map: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                       v_cache: Optional[torch.Tensor], page_size: int, status: Optional[torch.Tensor]) -> None:
+    """q|k|v projection of many tokens with what follows it, in one kernel: bias, half-split rotation of q
+    and k, q into ``q_out`` [tokens, num_heads * head_dim], k and v into the cache plane."""
+    _need_cuda(q_out, x, w_qkv, bias, positions, cos_sin, slot_map, k_cache, v_cache, status)
+    _f32(bias, "bias")
+    _f32(cos_sin, "cos_sin")
+    _i32(positions, "positions")
+    _i32(slot_map, "slot_map")
+    m, k = x.shape
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    _need(pair_qkv_supported(x, w_qkv, head_dim, cos_sin.shape[1]), "gemm_pair_qkv_rope: shapes")
+    _need(tuple(w_qkv.shape) == (width, k), "gemm_pair_qkv_rope: weight shape")
+    _need(q_out.dtype == torch.bfloat16 and q_out.shape[0] == m and q_out.shape[1] >= num_heads * head_dim
+          and q_out.stride(1) == 1 and q_out.stride(0) % 8 == 0, "gemm_pair_qkv_rope: q_out")
+    _need(cos_sin.is_contiguous() and positions.numel() >= m, "gemm_pair_qkv_rope: table and positions")
+    if bias is not None:
+        _need(bias.numel() == width and bias.is_contiguous(), "bias size")
+    num_slots = 0
+    if slot_map is not None:
+        _need(k_cache is not None and v_cache is not None and k_cache.dtype == torch.bfloat16
+              and k_cache.is_contiguous() and v_cache.is_contiguous() and slot_map.numel() >= m
+              and tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache plane")
+        num_slots = k_cache.shape[0] * page_size
+    load_library("gemm_pair").call(
+        "ll_gemm_pair_qkv_rope", _ptr(q_out), c_long(q_out.stride(0)), _ptr(x), c_long(x.stride(0)), _ptr(w_qkv),
+        c_int(m), c_int(k), _ptr(bias), _ptr(positions), _ptr(cos_sin), c_int(cos_sin.shape[0]), c_int(num_heads),
+        c_int(num_kv_heads), c_int(head_dim), _ptr(slot_map), _ptr(k_cache), _ptr(v_cache), c_int(page_size),
+        c_long(num_slots), c_int(sm_count(x.device)), _ptr(status), _stream())
+
+
 def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x @ Wg.T) * (x @ Wu.T) with W = [Wg; Wu]: fused for few tokens, else product + kernel."""
     inter = w_gate_up.shape[0] // 2

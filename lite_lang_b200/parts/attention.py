@@ -83,7 +83,7 @@ class GQAttention(Mixer):
     def kernel_libraries(self):
         libs = ["core"]
         if self.w_qkv is not None and self.w_qkv.dtype == torch.bfloat16:
-            libs.extend(["gemm_smallm", "gemm_stream", "gemm_tc"])
+            libs.extend(["gemm_smallm", "gemm_stream", "gemm_tc", "gemm_pair"])
             if self.head_dim in (64, 128):
                 libs.extend(["attn_mma", "attn_tc"])
         return libs
@@ -103,6 +103,17 @@ class GQAttention(Mixer):
             ops.gemm_stream_qkv_rope(q, x, self.w_qkv, self.b_qkv, step.positions, self.position.fused_table(),
                                      self.num_heads, self.num_kv_heads, self.head_dim, slot_map, cache.k, cache.v,
                                      cache.page_size, step.status)
+            attn = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
+            self.attend(attn, q, step, cache)
+            return ops.linear(attn, self.w_o, partial_ok=True)
+        if (self.position is not None and self.position.fuses_with_store
+                and ops.pair_qkv_supported(x, self.w_qkv, self.head_dim, self.position.fused_table().shape[1])
+                and ops.pair_qkv_preferred(x, self.w_qkv)):
+            # portions of prompts: the same fusion on the two-SM tcgen05 kernel
+            q = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
+            ops.gemm_pair_qkv_rope(q, x, self.w_qkv, self.b_qkv, step.positions, self.position.fused_table(),
+                                   self.num_heads, self.num_kv_heads, self.head_dim, slot_map, cache.k, cache.v,
+                                   cache.page_size, step.status)
             attn = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
             self.attend(attn, q, step, cache)
             return ops.linear(attn, self.w_o, partial_ok=True)

@@ -811,6 +811,55 @@ def test_gemm_stream_qkv_rope_equals_the_three_kernels_it_replaces(m, hidden, nh
     assert float((kc.float().abs().sum(dim=(1, 3)) > 0).sum()) == float((kc_ref.float().abs().sum(dim=(1, 3)) > 0).sum())
 
 
+@pytest.mark.parametrize("m,hidden,nh,nkv,hd,ps", [(2048, 1536, 12, 2, 128, 16), (300, 264, 3, 1, 64, 32),
+                                                   (257, 512, 5, 5, 64, 16), (520, 328, 2, 1, 256, 64), (1, 64, 1, 1, 128, 16)])
+def test_gemm_pair_qkv_rope_equals_the_two_kernels_it_replaces(m, hidden, nh, nkv, hd, ps):
+    from lite_lang_b200 import ops
+    from lite_lang_b200.parts.rope import rope_table
+    g = torch.Generator().manual_seed(31)
+    d = dev()
+    width = (nh + 2 * nkv) * hd
+    x = torch.randn(m, hidden, generator=g).to(torch.bfloat16).to(d)
+    w = (torch.randn(width, hidden, generator=g) / hidden ** 0.5).to(torch.bfloat16).to(d)
+    bias = (0.5 * torch.randn(width, generator=g)).to(d)
+    max_pos = 3000
+    num_pages = (m + ps - 1) // ps + 3
+    pos = torch.randint(0, max_pos, (m,), generator=g, dtype=torch.int32).to(d)
+    slots = torch.randperm(num_pages * ps, generator=g)[:m].to(torch.int32)
+    if m > 2:
+        slots[2] = -1
+    slots = slots.to(d)
+    table = rope_table(hd, 10000.0, max_pos).to(d)
+    status = torch.zeros(1, dtype=torch.int32, device=d)
+    ref_qkv = torch.mm(x, w.t())
+    kc_ref = torch.zeros(num_pages, nkv, ps, hd, dtype=torch.bfloat16, device=d)
+    vc_ref = torch.zeros_like(kc_ref)
+    ops.bias_rope_store(ref_qkv, bias, pos, table, nh, nkv, hd, slots, kc_ref, vc_ref, ps, status)
+    q = torch.full((m + 1, nh * hd + 8), 7.0, dtype=torch.bfloat16, device=d)
+    kc, vc = torch.zeros_like(kc_ref), torch.zeros_like(kc_ref)
+    for _ in range(2):
+        ops.gemm_pair_qkv_rope(q[:m, :nh * hd], x, w, bias, pos, table, nh, nkv, hd, slots, kc, vc, ps, status)
+    assert status.item() == 0
+    scale = float(ref_qkv.float().abs().max())
+    for got, want, what in ((q[:m, :nh * hd], ref_qkv[:, :nh * hd], "q"), (kc, kc_ref, "k cache"), (vc, vc_ref, "v cache")):
+        err = float((got.float() - want.float()).abs().max()) / scale
+        assert err <= 1.6e-2, (what, err)       # same roundings; only the order of the float32 sums differs
+    assert bool((q[m:] == 7).all()) and bool((q[:, nh * hd:] == 7).all())
+    written = lambda c: c.float().abs().sum(dim=(1, 3)) > 0
+    assert bool((written(kc) == written(kc_ref)).all()) and bool((written(vc) == written(vc_ref)).all())
+    # no bias, no cache write: q only
+    q2 = torch.empty(m, nh * hd, dtype=torch.bfloat16, device=d)
+    ops.gemm_pair_qkv_rope(q2, x, w, None, pos, table, nh, nkv, hd, None, None, None, ps, status)
+    ref2 = torch.mm(x, w.t())
+    ops.bias_rope_store(ref2, None, pos, table, nh, nkv, hd, None, None, None, ps, status)
+    assert float((q2.float() - ref2[:, :nh * hd].float()).abs().max()) / scale <= 1.6e-2
+    # a position outside the table is reported
+    bad = pos.clone()
+    bad[0] = max_pos
+    ops.gemm_pair_qkv_rope(q2, x, w, None, bad, table, nh, nkv, hd, None, None, None, ps, status)
+    assert status.item() == 4
+
+
 def test_linear_picks_the_library_for_other_shapes():
     from lite_lang_b200 import ops
     ops.configure_matmul_precision()
