@@ -17,7 +17,8 @@
 // One CTA (4 or 8 warps) works on one (entry, kv head, split of the keys); its warps take the split's 16-key
 // tiles in turn and are merged through shared memory.  The splits of an (entry, kv head) are the CTAs of
 // one thread-block cluster (1, 2, 4 or 8) and merge through distributed shared memory: every CTA
-// finishes a slice of the head dimensions.  No scratch memory, no counters, nothing spins (the cluster
+// finishes a slice of the head dimensions, which the others send to it with stores into its shared memory
+// before the cluster's one barrier.  No scratch memory, no counters, nothing spins (the cluster
 // barrier is the hardware's; every CTA of a cluster reaches it, early exits are the same for all of them).
 //
 // Head sizes 64 and 128, groups of at most 8 query heads, pages of a multiple of 16 tokens.
@@ -84,12 +85,20 @@ __device__ __forceinline__ unsigned ad_cluster_rank() {
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
 }
-__device__ __forceinline__ float ad_ld_peer(const float* local, unsigned rank) {
+// the address, in CTA `rank` of the cluster, of what is at `local` in this CTA's shared memory
+__device__ __forceinline__ unsigned ad_peer_addr(const void* local, unsigned rank) {
   unsigned la = (unsigned)__cvta_generic_to_shared(local), ra;
-  float v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra));
-  return v;
+  return ra;
+}
+__device__ __forceinline__ void ad_st_peer(unsigned addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void ad_st_peer2(unsigned addr, float a, float b) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void ad_st_peer4(unsigned addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 template <int HD, int NW>
@@ -101,6 +110,11 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   __shared__ float sm_m[NW][AD_HEADS];
   __shared__ float sm_l[NW][AD_HEADS];
   __shared__ int sm_bt[AD_BT_CACHE];
+  // what the other CTAs of the cluster send for the slice of dims that this CTA finishes: [sender][head][dim of
+  // the slice] (8 HD values whatever the cluster's size), and every sender's maximum and sum per head
+  __shared__ __align__(16) float rx_o[AD_HEADS * HD];
+  __shared__ float rx_m[8][AD_HEADS];
+  __shared__ float rx_l[8][AD_HEADS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int e = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -139,6 +153,9 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
         p.out[(size_t)e * p.out_stride + (size_t)kvh * p.group * HD + i] = __float2bfloat16_rn(0.f);
     return;
   }
+  // The cluster's merge below writes into the other CTAs' shared memory, which needs them to have started:
+  // every CTA says so here and checks it only when it gets there (by then it costs nothing).
+  if (p.nsplit > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
   auto tile_base = [&](int t) -> long {
     const int key0 = t * AD_TILE;
     const int page = bt_cached ? sm_bt[t - t_begin] : bt[key0 / p.page_size];
@@ -359,56 +376,60 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
     return;
   }
   // ---- the splits are the CTAs of one cluster: each finishes a slice of the dims of all heads ----
-  __syncthreads();
-#pragma unroll
-  for (int d = 0; d < DPT; ++d) sm_o[0][row][dbase + d] = acc[d];
-  if ((tid % CPR) == 0) {
-    sm_m[0][row] = M;
-    sm_l[0][row] = L;
-  }
-  ad_cluster_sync();
+  // Every CTA sends each of its partial sums to the CTA that finishes that dim (stores into the peer's shared
+  // memory, which nobody waits for one by one), then one cluster barrier, then everybody reads only its own
+  // shared memory: nothing of a CTA is read by another one after the barrier, so it may leave at once.
   const int cs = p.nsplit;
   const unsigned rank = ad_cluster_rank();
-  const int slice = HD / cs;                     // dims this CTA finishes: 8 .. 64
+  const int slice = HD / cs;                     // dims a CTA finishes: 8 .. 64 (a multiple of DPT)
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");   // (the arrive is above the tile loop)
+  {
+    const unsigned owner = (unsigned)(dbase / slice);
+    const int ds = dbase - (int)owner * slice;
+    const unsigned dst = ad_peer_addr(&rx_o[((int)rank * AD_HEADS + row) * slice + ds], owner);
+    if (DPT == 8) {
+      ad_st_peer4(dst, acc[0], acc[1], acc[2], acc[3]);
+      ad_st_peer4(dst + 16, acc[DPT - 4], acc[DPT - 3], acc[DPT - 2], acc[DPT - 1]);
+    } else if (DPT == 4) {
+      ad_st_peer4(dst, acc[0], acc[1], acc[2], acc[3]);
+    } else {
+      ad_st_peer2(dst, acc[0], acc[1]);
+    }
+    // a head's maximum and sum go to every CTA: the head's CPR threads share the cs receivers among them
+    const int j = tid % CPR;
+    if (j < cs) {
+      ad_st_peer(ad_peer_addr(&rx_m[rank][row], (unsigned)j), M);
+      ad_st_peer(ad_peer_addr(&rx_l[rank][row], (unsigned)j), L);
+    }
+  }
+  ad_cluster_sync();
   const int outputs = AD_HEADS * slice;          // 64 .. 512
   const int per = max(1, outputs / (NW * 32));  // 1 .. 4 consecutive dims of one head per thread
   const bool worker = tid * per < outputs;
   const int o0 = worker ? tid * per : 0;
-  const int row2 = o0 / slice, d0 = (int)rank * slice + (o0 - row2 * slice);
-  // every value wanted from the peers is asked for before the first one is used: the loads through the
-  // cluster's shared memory overlap instead of queueing behind each other's use
-  float ms[8], ls[8], ov[8][4], Mg = -INFINITY;
+  const int row2 = o0 / slice, dl = o0 - row2 * slice;
+  float Mg = -INFINITY;
 #pragma unroll
   for (int sI = 0; sI < 8; ++sI)
-    if (sI < cs) {
-      ms[sI] = ad_ld_peer(&sm_m[0][row2], sI);
-      ls[sI] = ad_ld_peer(&sm_l[0][row2], sI);
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        if (k < per) ov[sI][k] = ad_ld_peer(&sm_o[0][row2][d0 + k], sI);
-    }
-#pragma unroll
-  for (int sI = 0; sI < 8; ++sI)
-    if (sI < cs) Mg = fmaxf(Mg, ms[sI]);
+    if (sI < cs) Mg = fmaxf(Mg, rx_m[sI][row2]);
   const float Mgs = (Mg == -INFINITY) ? 0.f : Mg;
   float Lg = 0.f, fin[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int sI = 0; sI < 8; ++sI)
     if (sI < cs) {
-      const float ws = ad_exp2(ms[sI] - Mgs);
-      Lg += ls[sI] * ws;
+      const float ws = ad_exp2(rx_m[sI][row2] - Mgs);
+      Lg += rx_l[sI][row2] * ws;
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        if (k < per) fin[k] += ov[sI][k] * ws;
+        if (k < per) fin[k] += rx_o[(sI * AD_HEADS + row2) * slice + dl + k] * ws;
     }
   if (worker && row2 < p.group) {
-    bf16* o2 = p.out + (size_t)e * p.out_stride + (size_t)(kvh * p.group + row2) * HD + d0;
+    bf16* o2 = p.out + (size_t)e * p.out_stride + (size_t)(kvh * p.group + row2) * HD + (int)rank * slice + dl;
     const float inv = Lg > 0.f ? 1.0f / Lg : 0.f;
 #pragma unroll
     for (int k = 0; k < 4; ++k)
       if (k < per) o2[k] = __float2bfloat16_rn(fin[k] * inv);
   }
-  ad_cluster_sync();  // nobody leaves while its shared memory may still be read
 }
 
 // One new token per entry: q row e (head h at q + e*q_stride + h*hd) attends to the cached keys of
