@@ -101,12 +101,12 @@ __device__ __forceinline__ void ad_st_peer4(unsigned addr, float a, float b, flo
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-template <int HD, int NW>
+template <int HD, int NW, int DEPTH>
 __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodeParams p) {
   constexpr int KS = HD / 32;   // 16-byte loads per key row and thread for Q K^T
   constexpr int VS = HD / 64;   // 16-byte loads per value row and thread
   constexpr int MT = HD / 16;   // MMA row tiles of O^T
-  __shared__ float sm_o[NW][AD_HEADS][HD + 4];
+  // (the warps' partial outputs, [NW][AD_HEADS][HD + 4] floats, are laid over the ring of tiles when the loop is over)
   __shared__ float sm_m[NW][AD_HEADS];
   __shared__ float sm_l[NW][AD_HEADS];
   __shared__ int sm_bt[AD_BT_CACHE];
@@ -172,8 +172,9 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   // shortens it by that factor; with many requests it keeps enough bytes in flight for the bandwidth.
   // The 16-byte piece j of row r sits at piece j ^ swizzle(r), chosen so that the fragment reads below
   // (K: rows g, g + 8, pieces 4 s + c; V: rows 2 c (+1, +8, +9), pieces 8 h + g) hit all banks once.
-  constexpr int DEPTH = 2;   // (deeper rings were measured: no faster, and their shared memory keeps the next
-                             //  product's CTAs, which stream their weights ahead, from moving in beside this kernel)
+  // (DEPTH 2; 3 for long streams without splits, where more bytes in flight are worth the shared memory.  With
+  //  few keys a CTA deeper rings were measured no faster, and their shared memory keeps the next product's
+  //  CTAs, which stream their weights ahead, from moving in beside this kernel.)
   constexpr int ROW_BYTES = HD * 2, CH = HD / 8;           // pieces a row
   constexpr int TILE_BYTES = AD_TILE * ROW_BYTES;           // K (or V) of a tile
   extern __shared__ __align__(16) unsigned char ad_ring[];
@@ -328,6 +329,10 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 8);
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 16);
   }
+  // every warp is done with its ring (its last copies were waited for in the loop): the partial outputs go there
+  static_assert(sizeof(float) * NW * AD_HEADS * (HD + 4) <= (size_t)NW * DEPTH * 2 * TILE_BYTES, "sm_o fits the ring");
+  float (*sm_o)[AD_HEADS][HD + 4] = reinterpret_cast<float (*)[AD_HEADS][HD + 4]>(ad_ring);
+  __syncthreads();
   if (g == 0) {
     sm_m[warp][2 * c] = m_run[0];
     sm_m[warp][2 * c + 1] = m_run[1];
@@ -469,20 +474,20 @@ extern "C" int ll_attn_decode(void* out, long out_stride, const void* q, long q_
   p.nsplit = nsplit;
   p.status = status;
   dim3 grid(n_entries, nkv, nsplit);
-  // the warps' rings: two stages of a K and a V tile each
-  const size_t ring = (size_t)warps * 2 * 2 * AD_TILE * hd * 2;
-  if (hd == 64 && warps == 4) {
-    cudaFuncSetAttribute(attn_decode_kernel<64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
-    ll_launch_cluster(attn_decode_kernel<64, 4>, grid, dim3(128), ring, stream, nsplit, p);
-  } else if (hd == 64) {
-    cudaFuncSetAttribute(attn_decode_kernel<64, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
-    ll_launch_cluster(attn_decode_kernel<64, 8>, grid, dim3(256), ring, stream, nsplit, p);
-  } else if (warps == 4) {
-    cudaFuncSetAttribute(attn_decode_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
-    ll_launch_cluster(attn_decode_kernel<128, 4>, grid, dim3(128), ring, stream, nsplit, p);
-  } else {
-    cudaFuncSetAttribute(attn_decode_kernel<128, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
-    ll_launch_cluster(attn_decode_kernel<128, 8>, grid, dim3(256), ring, stream, nsplit, p);
-  }
+  // the warps' rings: two stages of a K and a V tile each; three for 8 warps that run through all keys
+  const int depth = (warps == 8 && nsplit == 1) ? 3 : 2;
+  const size_t ring = (size_t)warps * depth * 2 * AD_TILE * hd * 2;
+#define AD_LAUNCH(HD_, NW_, DEPTH_)                                                                                  \
+  do {                                                                                                               \
+    cudaFuncSetAttribute(attn_decode_kernel<HD_, NW_, DEPTH_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring); \
+    ll_launch_cluster(attn_decode_kernel<HD_, NW_, DEPTH_>, grid, dim3(NW_ * 32), ring, stream, nsplit, p);          \
+  } while (0)
+  if (hd == 64 && warps == 4) AD_LAUNCH(64, 4, 2);
+  else if (hd == 64 && depth == 2) AD_LAUNCH(64, 8, 2);
+  else if (hd == 64) AD_LAUNCH(64, 8, 3);
+  else if (warps == 4) AD_LAUNCH(128, 4, 2);
+  else if (depth == 2) AD_LAUNCH(128, 8, 2);
+  else AD_LAUNCH(128, 8, 3);
+#undef AD_LAUNCH
   return LL_LAUNCH_RESULT();
 }
