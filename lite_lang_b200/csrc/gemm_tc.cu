@@ -287,7 +287,8 @@ gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const
           // gate and up rounded to bfloat16 first, as the unfused path does between product and activation
           const float gt = __bfloat162float(__float2bfloat16_rn(a));
           const float uv = __bfloat162float(__float2bfloat16_rn(stg[(64 + fl) * (NT + 1) + t]));
-          return gt / (1.0f + __expf(-gt)) * uv;
+          // (x * rcp(y), not the IEEE division: that is a chain of dependent instructions with a branch an element)
+          return __fdividef(gt, 1.0f + __expf(-gt)) * uv;
         }
         return a;
       };
