@@ -65,3 +65,51 @@ def test_whole_then_token_by_token(model, dtype):
         assert err <= TOL[dtype], (i, err)
     runner.check_status()
     assert runner.graph_replays == 16
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_long_portion_through_the_two_sm_kernels(model, dtype):
+    """A prompt portion of 1,300 tokens in one step: at these sizes the q|k|v projection (with bias, rotation
+    and cache write in its epilogue) and the gated feed-forward go to the two-SM tcgen05 kernel in bfloat16.
+    Logits at the edges of its 256-token tiles, then three decoded tokens, which read the cache it wrote."""
+    from lite_lang_b200 import ops
+    from lite_lang_b200.cache import CacheManager
+    from lite_lang_b200.config import load_config
+    from lite_lang_b200.engine.batch import StepEntry
+    from lite_lang_b200.engine.model import CausalLM
+    from lite_lang_b200.engine.runner import ModelRunner
+    from lite_lang_b200.weights import load_weights
+
+    folder, _, _ = model
+    dev = torch.device("cuda:0")
+    n_prompt, n_dec = 1300, 3
+    cfg, w = P.read_model_folder(folder, device="cuda:0")          # the plain formulas, float32, on the device
+    toks = random_tokens(n_prompt + n_dec, cfg["vocab_size"], 78)
+    places = [0, 127, 128, 255, 256, 1023, 1024, 1279, 1280, n_prompt - 1] + list(range(n_prompt, n_prompt + n_dec))
+    ops.configure_matmul_precision()
+    tok = torch.as_tensor(toks, dtype=torch.long, device=dev)
+    h = P.embedding(w["model.embed_tokens.weight"], tok)
+    for layer in range(cfg["num_hidden_layers"]):
+        h = P.decoder_layer(h, torch.arange(len(toks), device=dev), w, layer, cfg)
+    y = P.rms_norm(h[places], w["model.norm.weight"], float(cfg["rms_norm_eps"]))
+    ref = P.linear(y, w["model.embed_tokens.weight"]).cpu().numpy()
+
+    m = CausalLM(load_config(folder).model_spec())
+    load_weights(m, folder, torch.bfloat16 if dtype == "bfloat16" else torch.float32, dev)
+    if dtype == "bfloat16":
+        x = torch.empty(n_prompt, cfg["hidden_size"], dtype=torch.bfloat16, device=dev)
+        mixer = m.blocks[0].mixer
+        assert ops.pair_qkv_supported(x, mixer.w_qkv, mixer.head_dim, mixer.head_dim) and ops.pair_qkv_preferred(x, mixer.w_qkv)
+    mgr = CacheManager(m.cache_groups, [96], 16, 2, 1536)
+    runner = ModelRunner(m, mgr, dev, 1536, cuda_graphs=False)
+    a = mgr.open()
+    assert runner.reserve(a, n_prompt)
+    want = tuple(p for p in places if p < n_prompt)
+    lg = runner.step([StepEntry(a, toks[:n_prompt], want)]).float().cpu().numpy()
+    assert rel_err(lg, ref[:len(want)]) <= TOL[dtype]
+    for i in range(n_dec):
+        assert runner.reserve(a, 1)
+        lg = runner.step([StepEntry(a, [toks[n_prompt + i]], (0,))]).float().cpu().numpy()
+        err = rel_err(lg, ref[len(want) + i:len(want) + i + 1])
+        assert err <= TOL[dtype], (i, err)
+    runner.check_status()
