@@ -736,6 +736,26 @@ def gemm_pair_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w_qkv: torch.Tensor
         c_long(num_slots), c_int(sm_count(x.device)), _ptr(status), _stream())
 
 
+ACCUMULATE_MIN_M = 129   # more tokens than any of the hand-written plain products takes: library territory
+
+
+def accumulate_preferred(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether ``linear_accumulate`` should stand for ``linear`` + a later residual sum: when the product
+    is a library one anyway (portions of prompts), its epilogue adds the residual for the price of reading it."""
+    return x.shape[0] >= ACCUMULATE_MIN_M and x.dtype == weight.dtype
+
+
+def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, acc: torch.Tensor) -> None:
+    """acc += x @ weight.T in place (library product with beta = 1: float32 accumulation, the sum with ``acc``
+    in float32, one rounding), so that the norm after it reads the residual stream only."""
+    _need_cuda(x, weight, acc)
+    _need(acc.dtype == x.dtype and acc.shape[0] == x.shape[0] and acc.shape[1] == weight.shape[0]
+          and acc.stride(1) == 1, "linear_accumulate: acc is [tokens, out] of the operands' dtype")
+    if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise RuntimeError("TF32 is on; call ops.configure_matmul_precision() before a float32 product")
+    torch.addmm(acc, x, weight.t(), out=acc)
+
+
 def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x @ Wg.T) * (x @ Wu.T) with W = [Wg; Wu]: fused for few tokens, else product + kernel."""
     inter = w_gate_up.shape[0] // 2

@@ -93,7 +93,15 @@ class GQAttention(Mixer):
             self.position.prepare(device)
 
     # ------------------------------------------------------------------
-    def forward(self, x, step, cache):
+    accumulates = True
+
+    def _project_out(self, attn, residual):
+        if residual is not None and ops.accumulate_preferred(attn, self.w_o):
+            ops.linear_accumulate(attn, self.w_o, residual)
+            return None
+        return ops.linear(attn, self.w_o, partial_ok=True)
+
+    def forward(self, x, step, cache, residual=None):
         n = x.shape[0]
         slot_map = cache.slot_map if cache.writable else None
         if (self.position is not None and self.position.fuses_with_store
@@ -105,7 +113,7 @@ class GQAttention(Mixer):
                                      cache.page_size, step.status)
             attn = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
             self.attend(attn, q, step, cache)
-            return ops.linear(attn, self.w_o, partial_ok=True)
+            return self._project_out(attn, residual)
         if (self.position is not None and self.position.fuses_with_store
                 and ops.pair_qkv_supported(x, self.w_qkv, self.head_dim, self.position.fused_table().shape[1])
                 and ops.pair_qkv_preferred(x, self.w_qkv)):
@@ -116,7 +124,7 @@ class GQAttention(Mixer):
                                    cache.page_size, step.status)
             attn = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
             self.attend(attn, q, step, cache)
-            return ops.linear(attn, self.w_o, partial_ok=True)
+            return self._project_out(attn, residual)
         qkv = ops.linear(x, self.w_qkv)
         if self.position is None or self.position.fuses_with_store:
             table = self.position.fused_table() if self.position is not None else None
@@ -132,7 +140,7 @@ class GQAttention(Mixer):
                                     slot_map, cache.k, cache.v, cache.page_size, step.status, n)
         attn = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
         self.attend(attn, qkv, step, cache)
-        return ops.linear(attn, self.w_o, partial_ok=True)
+        return self._project_out(attn, residual)
 
     SM_COUNT = 148
 

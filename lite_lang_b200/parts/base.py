@@ -136,6 +136,10 @@ class Mixer(Part):
     def prepare(self, device: torch.device, dtype: torch.dtype) -> None:
         pass
 
+    # True: ``forward`` takes ``residual=h`` and may add its output to the residual stream itself (in its
+    # last product's epilogue), returning None instead of the output
+    accumulates = False
+
     def forward(self, x: torch.Tensor, step: "StepView", cache: Any) -> torch.Tensor:
         """x [tokens, hidden] -> [tokens, hidden].  ``cache`` is the view of this run-step's plane."""
         raise NotImplementedError
@@ -143,6 +147,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     kind_family = "feed_forward"
+    accumulates = False   # as for a mixer
 
     def forward(self, x: torch.Tensor, step: "StepView") -> torch.Tensor:
         raise NotImplementedError

@@ -13,9 +13,12 @@ from .base import Block, register_part
 class PreNormBlock(Block):
     def forward(self, h, delta, step, cache):
         x = self.mixer_norm.add_forward(h, delta)
-        a = self.mixer.forward(x, step, cache)
+        # a part that can add its output to h in its last product (portions of prompts) returns None
+        a = (self.mixer.forward(x, step, cache, residual=h) if self.mixer.accumulates
+             else self.mixer.forward(x, step, cache))
         x = self.feed_forward_norm.add_forward(h, a)
-        f = self.feed_forward.forward(x, step)
+        f = (self.feed_forward.forward(x, step, residual=h) if self.feed_forward.accumulates
+             else self.feed_forward.forward(x, step))
         return h, f
 
 

@@ -50,8 +50,13 @@ class GatedMLP(FeedForward):
     def weight_bytes(self) -> int:
         return self.w_gate_up.numel() * self.w_gate_up.element_size() + self.w_down.numel() * self.w_down.element_size()
 
-    def forward(self, x, step):
+    accumulates = True
+
+    def forward(self, x, step, residual=None):
         act = ops.gated_linear(x, self.w_gate_up)
+        if residual is not None and ops.accumulate_preferred(act, self.w_down):
+            ops.linear_accumulate(act, self.w_down, residual)
+            return None
         return ops.linear(act, self.w_down, partial_ok=True)
 
 
