@@ -117,25 +117,53 @@ sample_stage2_kernel(const float* __restrict__ logits, long row_stride, const fl
   const int r = blockIdx.x;
   const float* pr = part + (size_t)r * nchunks * 3;
   const float temp = temperature ? temperature[r] : 0.f;
+  // the chunks' partial results: thread c reads chunk c's (all in flight at once; one thread going through
+  // them one after the other was a chain of memory latencies), then the block reduces
+  __shared__ float s_val[SM_T1 / 32];
+  __shared__ int s_idx[SM_T1 / 32];
+  float best = -INFINITY, my_max = -INFINITY, my_sum = 0.f;
+  int best_i = 0x7fffffff;
+  for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {   // (nchunks <= blockDim.x for every vocabulary up to 500 k)
+    my_max = pr[c * 3];
+    my_sum = pr[c * 3 + 2];
+    argmax_combine(best, best_i, my_max, __float_as_int(pr[c * 3 + 1]));
+  }
+  const bool one_each = nchunks <= (int)blockDim.x;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    argmax_combine(best, best_i, ov, oi);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s_val[threadIdx.x >> 5] = best;
+    s_idx[threadIdx.x >> 5] = best_i;
+  }
+  if (one_each) s_part[threadIdx.x] = 0.f;
+  __syncthreads();
   if (threadIdx.x == 0) {
-    float M = -INFINITY;
-    int arg = 0;
-    for (int c = 0; c < nchunks; ++c)
-      if (pr[c * 3] > M) {
-        M = pr[c * 3];
-        arg = __float_as_int(pr[c * 3 + 1]);
-      }
+    float M = s_val[0];
+    int arg = s_idx[0];
+    for (int w = 1; w < SM_T1 / 32; ++w) argmax_combine(M, arg, s_val[w], s_idx[w]);
     s_M = M;
     s_arg = arg;
     s_chunk = -1;
-    if (temp > 0.f) {
-      const float inv_t = 1.0f / temp;
+  }
+  __syncthreads();
+  if (temp > 0.f) {
+    const float inv_t = 1.0f / temp, M = s_M;
+    if (one_each) {   // every chunk's share of the total, in chunk order, by its own thread
+      if ((int)threadIdx.x < nchunks) s_part[threadIdx.x] = my_sum * expf((my_max - M) * inv_t);
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) {
       float total = 0.f;
-      for (int c = 0; c < nchunks; ++c) total += pr[c * 3 + 2] * expf((pr[c * 3] - M) * inv_t);
+      for (int c = 0; c < nchunks; ++c)
+        total += one_each ? s_part[c] : pr[c * 3 + 2] * expf((pr[c * 3] - M) * inv_t);
       const float target = uniform[r] * total;
       float run = 0.f;
       for (int c = 0; c < nchunks; ++c) {
-        const float share = pr[c * 3 + 2] * expf((pr[c * 3] - M) * inv_t);
+        const float share = one_each ? s_part[c] : pr[c * 3 + 2] * expf((pr[c * 3] - M) * inv_t);
         if (share > 0.f && run + share >= target) {
           s_chunk = c;
           break;
