@@ -20,14 +20,16 @@
 // q|k|v row never goes to memory and one kernel stands for two.
 //
 // Roles in a CTA (320 threads):
-//   warp 0    producer: one thread keeps a ring of six 32 KB stages filled; both CTAs' copies complete on
-//             the even CTA's `full` barrier of the stage;
+//   warp 0    producer: one thread keeps a ring of six 32 KB stages filled (four in q|k|v mode, whose epilogue
+//             takes the room of two for its staging tile); both CTAs' copies complete on the even CTA's
+//             `full` barrier of the stage;
 //   warp 1    MMA: in the even CTA one thread issues the MMAs of a stage when it is full, and a
 //             tcgen05.commit hands the stage back to both producers; the accumulator is double-buffered
 //             (2 x 256 columns), so the MMAs of the next tile run while this one's epilogue reads;
-//   warps 2-9 epilogue: tensor memory -> registers -> activation -> 16-byte stores of the thread's own row;
-//             a warp reads the 32 lanes that its number modulo 4 gives, so two warps share a token row and each
-//             takes half of the tile's columns (a pair with one tile has nothing to hide its epilogue behind).
+//   warps 2-9 epilogue: tensor memory -> registers -> activation -> 16-byte stores of the thread's own row
+//             (q|k|v mode: -> shared memory, then rows finished by consecutive threads); a warp reads the 32
+//             lanes that its number modulo 4 gives, so two warps share a token row and each takes half of the
+//             tile's columns (a pair with one tile has nothing to hide its epilogue behind).
 // Tiles go to the pairs round-robin, tokens fastest, so the pairs that run together share weight rows in L2.
 //
 // Every mbarrier wait is bounded (about two seconds of clock): a wait that runs out records
