@@ -172,6 +172,12 @@ __device__ __forceinline__ float at_max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
   return y;
 }
+// untiled bulk copy, global -> this CTA's shared memory; both addresses 16-byte aligned, bytes a multiple of 16
+__device__ __forceinline__ void at_bulk_load(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
 #define AT_FENCE_BEFORE() asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory")
 #define AT_FENCE_AFTER() asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory")
 
@@ -190,7 +196,7 @@ struct AttnTcParams {
   // the key blocks of a row block may be split over up to nsplit CTAs (long contexts, few row blocks):
   // partial results (unnormalised O, reference maximum, sum) meet in scratch memory, the last CTA to
   // arrive (a counter per row block and kv head, left at zero again) merges them
-  int nsplit;
+  int nsplit, row_blocks, split_len;
   float* scratch;      // [row blocks * nkv * nsplit][HD + 2][128]
   int* counters;       // [row blocks * nkv], zero between launches
   int* status;
@@ -227,12 +233,15 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
   unsigned* merge_flag = tmem_slot + 1;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int kvh = blockIdx.y;
-
-  // ---- which rows: row block rb of the step (heavier, later blocks of an entry first) ----
-  const int item = gridDim.x - 1 - blockIdx.x;
-  const int split = item % p.nsplit;
-  const int rb_step = item / p.nsplit;       // row block within the step (names its scratch and counter)
+  // ---- which rows: row block rb of the step.  Order of the CTAs (the hardware starts them in the order of
+  // their number, and one that has to wait holds back all after it): first split 0 of every row block, the
+  // heavier, later blocks of an entry first, the kv heads side by side; then split 1 of every row block, and
+  // so on.  The CTAs without work (splits that a short row block does not have) are the last of each round,
+  // and nearly all of them the last of the grid. ----
+  const int kvh = blockIdx.x % p.nkv;
+  const int l2 = blockIdx.x / p.nkv;
+  const int split = l2 / p.row_blocks;
+  const int rb_step = p.row_blocks - 1 - l2 % p.row_blocks;   // row block within the step (names its scratch and counter)
   int rb = rb_step;
   int entry = -1, qlen = 0;
   for (int e = 0; e < p.n_entries; ++e) {
@@ -258,8 +267,9 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
   const int hi = pos0 + ntok - 1;
   const int lo_min = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
   const int nblk_all = hi / AT_KB - lo_min / AT_KB + 1;      // key blocks the rows may see
-  // splits that have work: at least eight blocks (512 keys) each, none empty; the same for every CTA of the row block
-  int eff = min(p.nsplit, max(1, nblk_all / 8));
+  // splits that have work: about split_len blocks each (the host chooses that length so that the step's CTAs
+  // just fit the SMs at once), none empty; the same for every CTA of the row block
+  int eff = min(p.nsplit, max(1, (nblk_all + p.split_len - 1) / p.split_len));
   const int per = (nblk_all + eff - 1) / eff;
   eff = (nblk_all + per - 1) / per;
   if (split >= eff) return;
@@ -474,7 +484,7 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
     AT_FENCE_AFTER();
     // ---- the splits of a row block meet in scratch memory; the last one to arrive goes on ----
     bool finish = true;
-    float m_all = m_ref, inv;
+    float inv;
     const size_t part0 = ((size_t)rb_step * p.nkv + kvh) * p.nsplit;     // this row block's first partial
     constexpr int PSTRIDE = (HD + 2) * 128;   // floats a partial: column-major [HD + 2][128 rows] (O, maximum, sum),
                                               // so that a warp's 32 rows read and write 128 contiguous bytes
@@ -500,16 +510,41 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
       asm volatile("bar.sync 1, 128;" ::: "memory");
       finish = *merge_flag != 0u;
       if (finish) {
+        // The last one to arrive adds the others' partial results to its own, which is still in tensor memory.
+        // Each comes with one bulk copy into the shared memory of the K/V rings and P (free now: every MMA of
+        // this CTA is done) and is added there; reading them from global memory piece by piece was a chain of
+        // 4 x splits trips to L2.  Online merge: the running maximum and sum are rescaled as the partials come.
         __threadfence();
-        float l_all = 0.f;
-        m_all = -INFINITY;
-        for (int q = 0; q < eff; ++q) m_all = fmaxf(m_all, p.scratch[(part0 + q) * PSTRIDE + (size_t)HD * 128 + r]);
+        float* part_s = reinterpret_cast<float*>(kv_s);
+        static_assert(PSTRIDE * 4 <= AT_KS * STAGE_BYTES + P_BYTES, "a partial fits the freed shared memory");
+        float m_cur = m_ref, l_cur = l_run;
+        int round = 0;
         for (int q = 0; q < eff; ++q) {
-          const float* part = p.scratch + (part0 + q) * PSTRIDE + r;
-          const float mq = part[(size_t)HD * 128];
-          l_all += (mq == -INFINITY) ? 0.f : part[(size_t)(HD + 1) * 128] * exp2f(mq - m_all);
+          if (q == split) continue;
+          asm volatile("bar.sync 1, 128;" ::: "memory");   // everybody is done with what the region held before
+          if (tid == 64) {
+            asm volatile("fence.proxy.async;" ::: "memory");
+            at_mbar_expect_tx(q_full, (unsigned)(PSTRIDE * 4));
+            at_bulk_load(at_smem(part_s), p.scratch + (part0 + q) * PSTRIDE, (unsigned)(PSTRIDE * 4), q_full);
+          }
+          at_mbar_wait(q_full, (unsigned)((round + 1) & 1), p.status, dead);   // (phase 0 was the Q tile)
+          const float mq = part_s[HD * 128 + r], lq = part_s[(HD + 1) * 128 + r];
+          const float m_new = fmaxf(m_cur, mq);
+          const float sc_old = (m_cur == -INFINITY) ? 0.f : exp2f(m_cur - m_new);
+          const float sc_q = (mq == -INFINITY) ? 0.f : exp2f(mq - m_new);
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            float v[32];
+            at_ld32(tmem_o + lane_addr + c0, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = fmaf(part_s[(c0 + i) * 128 + r], sc_q, v[i] * sc_old);
+            at_st32(tmem_o + lane_addr + c0, v);
+          }
+          l_cur = l_cur * sc_old + lq * sc_q;
+          m_cur = m_new;
+          ++round;
         }
-        inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+        inv = l_cur > 0.f ? 1.0f / l_cur : 0.f;
       }
     } else {
       inv = l_run > 0.f ? 1.0f / l_run : 0.f;
@@ -520,19 +555,7 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 32) {
         float v[32];
-        if (eff > 1) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0.f;
-          for (int q = 0; q < eff; ++q) {
-            const float* part = p.scratch + (part0 + q) * PSTRIDE + r;
-            const float mq = part[(size_t)HD * 128];
-            const float wq = (mq == -INFINITY) ? 0.f : exp2f(mq - m_all);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = fmaf(part[(size_t)(c0 + i) * 128], wq, v[i]);
-          }
-        } else {
-          at_ld32(tmem_o + lane_addr + c0, v);
-        }
+        at_ld32(tmem_o + lane_addr + c0, v);
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
           const int c = c0 / 8 + cc;
@@ -586,15 +609,15 @@ static at_encode_fn at_encoder() {
 
 // Arguments as ll_attn_prefill (attention_prefill.cu), but the row blocks are counted differently:
 // row_blocks = sum over the entries of ceil(q_len / floor(128 / group)); num_tokens is the number of rows of q.
-// nsplit in 1..8: CTAs a row block's key blocks may be split over; with nsplit > 1, scratch is float32
+// nsplit in 1..8: CTAs a row block's key blocks may be split over, each taking about split_len blocks of 64 keys; with nsplit > 1, scratch is float32
 // [row_blocks * nkv * nsplit * (hd + 2) * 128] and counters int32 [row_blocks * nkv], zero at the first launch
 // (the kernel leaves them zero).
 extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, long q_stride, int num_tokens,
                                   const void* k_cache, const void* v_cache, const int* block_table, int bt_stride,
                                   const int* cu_q, const int* ctx_len, const int* req_slot, int n_entries,
                                   int row_blocks, int nh, int nkv, int hd, int page_size, int num_pages, int window,
-                                  float scale, int nsplit, float* scratch, int* counters, int* status,
-                                  cudaStream_t stream) {
+                                  float scale, int nsplit, int split_len, float* scratch, int* counters,
+                                  int* status, cudaStream_t stream) {
   if (row_blocks <= 0 || n_entries <= 0) return 0;
   if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0 || nkv > 65535 || nh / nkv > 128)
     return (int)cudaErrorInvalidValue;
@@ -602,7 +625,7 @@ extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, lon
     return (int)cudaErrorInvalidValue;
   if ((q_stride % 8) != 0 || (out_stride % 8) != 0 || ((uintptr_t)q % 16) != 0 || ((uintptr_t)out % 16) != 0)
     return (int)cudaErrorInvalidValue;
-  if (nsplit < 1 || nsplit > 8 || (nsplit > 1 && (scratch == nullptr || counters == nullptr || ((uintptr_t)scratch % 16) != 0)))
+  if (nsplit < 1 || nsplit > 8 || split_len < 1 || (nsplit > 1 && (scratch == nullptr || counters == nullptr || ((uintptr_t)scratch % 16) != 0)))
     return (int)cudaErrorInvalidValue;
   at_encode_fn enc = at_encoder();
   if (enc == nullptr) return (int)cudaErrorNotSupported;
@@ -649,7 +672,9 @@ extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, lon
       return (int)cudaErrorInvalidValue;
   }
   const size_t smem = (size_t)128 * hd * 2 + (size_t)AT_KS * 2 * AT_KB * hd * 2 + 128 * AT_KB * 2 + 256;
-  dim3 grid(row_blocks * nsplit, nkv);
+  p.row_blocks = row_blocks;
+  p.split_len = split_len;
+  dim3 grid(row_blocks * nsplit * nkv);
   if (hd == 64) {
     cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ll_launch(attn_prefill_tc_kernel<64>, grid, dim3(AT_THREADS), smem, stream, p, qmap, kmap, vmap);

@@ -334,45 +334,61 @@ def attn_prefill_tc_blocks(q_lens, group: int) -> int:
 _attn_tc_scratch = {}
 
 
-def attn_prefill_tc_plan(entries, group: int, window: Optional[int]):
-    """(row blocks, longest, mean) of a step for ``attn_prefill_tc``.  ``entries``: (cached tokens, new tokens)
-    per entry; a row block takes floor(128 / group) tokens; longest / mean: key blocks of 64 a row block walks."""
+def attn_prefill_tc_plan(entries, group: int, window: Optional[int], num_kv_heads: int = 1, slots: int = 0):
+    """(row blocks, nsplit, split_len) of a step for ``attn_prefill_tc``.  ``entries``: (cached tokens, new tokens)
+    per entry; a row block takes floor(128 / group) tokens and walks n key blocks of 64.
+
+    A CTA's blocks are a chain (scores, softmax, P V: about 1.4 us a block), so a step lasts as long as its
+    longest CTA, and a CTA that finds no room on the SMs at once waits for a whole one to end (the hardware hands
+    CTAs out in order).  So row blocks are cut into splits of at most ``split_len`` blocks, with the smallest
+    ``split_len`` for which all CTAs of the step fit the ``slots`` (two an SM) at once: a whole causal prompt of
+    2,048 tokens (row blocks of 1..32 blocks, 2 kv heads) gets 16, i.e. its longer half is cut in two.  Not below
+    4 blocks a split or over 8 splits (every split's partial result goes through scratch memory); when the
+    unsplit row blocks already exceed the slots, nothing is cut."""
     tpb = 128 // group
-    blocks, longest, total = 0, 0, 0
+    lengths = []
     for ctx, q in entries:
         for first in range(0, q, tpb):
             hi = ctx + min(first + tpb, q) - 1
             lo = max(0, ctx + first - window + 1) if window else 0
-            n = hi // 64 - lo // 64 + 1
-            blocks += 1
-            total += n
-            longest = max(longest, n)
-    return blocks, longest, (total / blocks if blocks else 0.0)
+            lengths.append(hi // 64 - lo // 64 + 1)
+    blocks = len(lengths)
+    if not lengths or slots <= 0 or blocks * num_kv_heads > slots:
+        return blocks, 1, 1 << 20
+    longest = max(lengths)
+    best = longest
+    for t in range(max(4, (longest + 7) // 8), longest + 1):
+        if sum((n + t - 1) // t for n in lengths) * num_kv_heads <= slots:
+            best = t
+            break
+    if best * 5 > longest * 4:      # cutting off less than a fifth of the longest chain does not pay for the merges
+        return blocks, 1, 1 << 20   # (four portions of 512 behind 1,536 tokens: 49 us uncut, 52.5 us cut at 29 of 32)
+    most = (longest + best - 1) // best
+    nsplit = 1 if most <= 1 else 2 if most <= 2 else 4 if most <= 4 else 8
+    return blocks, nsplit, best
 
 
-def attn_prefill_tc_splits(row_blocks: int, num_kv_heads: int, device, longest: float = 0.0, mean: float = 0.0) -> int:
-    """CTAs a row block's keys may be split over.  As many as still fit the SMs (two CTAs each) in one wave when
-    the step has few row blocks (a short portion behind a long context).  When the unsplit CTAs already fill
-    more than half of them, two only if the row blocks are of very different length (a whole causal prompt:
-    the longest walks twice the mean; measured 49 -> 37 us for 2,048 tokens), since equal ones just get a
-    second wave (four portions of 512 behind 1,536 tokens: 49 -> 60 us)."""
+def attn_prefill_tc_splits(row_blocks: int, num_kv_heads: int, device) -> int:
+    """CTAs a row block's keys may be split over when nothing is known about the entries' lengths: as many as
+    still fit the SMs (two CTAs each) at once."""
     ctas = row_blocks * num_kv_heads
     slots = 2 * sm_count(device)
     for n in (8, 4, 2):
         if ctas * n <= slots:
             return n
-    return 2 if (ctas <= slots and longest >= 1.5 * mean and longest >= 16) else 1
+    return 1
 
 
 def attn_prefill_tc(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
                     num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int,
                     page_size: int, window: Optional[int], scale: float, status: Optional[torch.Tensor],
-                    nsplit: Optional[int] = None) -> None:
+                    nsplit: Optional[int] = None, split_len: int = 8) -> None:
     """Paged attention for portions of prompts on the tcgen05 tensor cores (TMA loads, S and O in tensor
     memory).  ``row_blocks`` from ``attn_prefill_tc_blocks``.  Otherwise as ``attn_prefill``.
-    ``nsplit`` (1, 2, 4, 8; default: by the size of the step): the keys of a row block are split over that
-    many CTAs, which merge through scratch memory kept by this module (grown when needed, never shrunk)."""
+    ``nsplit`` (1, 2, 4, 8; default: by the size of the step): the keys of a row block are split over up to that
+    many CTAs of about ``split_len`` blocks of 64 keys each (``attn_prefill_tc_plan`` chooses both), which merge
+    through scratch memory kept by this module (grown when needed, never shrunk)."""
     _need_cuda(out, q, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot)
     for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot")):
         _i32(t, nm)
@@ -404,8 +420,8 @@ def attn_prefill_tc(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: 
         "ll_attn_prefill_tc", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), c_int(q.shape[0]),
         _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.stride(0)), _ptr(cu_q), _ptr(ctx_len),
         _ptr(req_slot), c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
-        c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), c_int(nsplit), _ptr(scratch),
-        _ptr(counters), _ptr(status), _stream())
+        c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), c_int(nsplit), c_int(max(1, int(split_len))),
+        _ptr(scratch), _ptr(counters), _ptr(status), _stream())
 
 
 _sample_scratch = {}

@@ -212,16 +212,15 @@ class GQAttention(Mixer):
                         ctxs = getattr(step, "entry_ctx", None)
                         rest_entries = step.entries[n_single:]
                         if ctxs is not None:
-                            blocks, longest, mean = ops.attn_prefill_tc_plan(
+                            plan = ops.attn_prefill_tc_plan(
                                 [(ctxs[n_single + i], len(e.tokens)) for i, e in enumerate(rest_entries)], group,
-                                self.window)
+                                self.window, self.num_kv_heads, 2 * ops.sm_count(qkv.device))
                         else:
-                            blocks, longest, mean = ops.attn_prefill_tc_blocks(
-                                (len(e.tokens) for e in rest_entries), group), 0.0, 0.0
-                        nsplit = ops.attn_prefill_tc_splits(blocks, self.num_kv_heads, qkv.device, longest, mean)
-                        plan = step.scratch[key] = (blocks, nsplit)
+                            blocks = ops.attn_prefill_tc_blocks((len(e.tokens) for e in rest_entries), group)
+                            plan = (blocks, ops.attn_prefill_tc_splits(blocks, self.num_kv_heads, qkv.device), 8)
+                        step.scratch[key] = plan
                     ops.attn_prefill_tc(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, *rest, plan[0],
-                                        *args, step.status, nsplit=plan[1])
+                                        *args, step.status, nsplit=plan[1], split_len=plan[2])
                 else:
                     key = ("attn_prefill", group)
                     blocks = step.scratch.get(key)

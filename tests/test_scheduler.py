@@ -278,3 +278,31 @@ def test_plan_ahead_declines_when_the_outcome_matters():
     run_step(m, s)                      # 7 prompt tokens: pages full after one more token
     plan = s.plan()
     assert plan and s.plan_ahead(plan) is None
+
+
+def test_prefill_attention_plan_fits_the_ctas_to_the_sms():
+    """The host's plan for the tcgen05 prefill attention: splits of the smallest length for which all CTAs of the
+    step run at once; nothing is cut when that would not shorten the longest chain by a fifth, or when the
+    uncut row blocks already exceed the slots."""
+    from lite_lang_b200 import ops
+
+    def ctas(entries, group, nkv, split_len, nsplit):
+        tpb, total = 128 // group, 0
+        for ctx, q in entries:
+            for first in range(0, q, tpb):
+                n = (ctx + min(first + tpb, q) - 1) // 64 + 1
+                eff = min(nsplit, max(1, -(-n // split_len)))
+                per = -(-n // eff)
+                total += -(-n // per)                       # what the kernel makes of it
+        return total * nkv
+
+    blocks, nsplit, split_len = ops.attn_prefill_tc_plan([(0, 2048)], 6, None, 2, 296)
+    assert (blocks, nsplit, split_len) == (98, 2, 16)
+    assert ctas([(0, 2048)], 6, 2, split_len, nsplit) <= 296 < ctas([(0, 2048)], 6, 2, split_len - 1, 8)
+    assert ops.attn_prefill_tc_plan([(1536, 512)] * 4, 6, None, 2, 296)[1] == 1        # equal chains: no cut
+    assert ops.attn_prefill_tc_plan([(0, 8192)], 6, None, 2, 296)[1] == 1              # more row blocks than slots
+    b, n, s = ops.attn_prefill_tc_plan([(7680, 512)], 6, None, 2, 296)                 # few row blocks, long context
+    assert n == 8 and ctas([(7680, 512)], 6, 2, s, n) <= 296
+    assert ops.attn_prefill_tc_plan([], 6, None, 2, 296) == (0, 1, 1 << 20)
+    # a window shortens the chains
+    assert ops.attn_prefill_tc_plan([(4096, 64)], 4, 256, 2, 296)[2] >= 4
