@@ -113,3 +113,59 @@ def test_long_portion_through_the_two_sm_kernels(model, dtype):
         err = rel_err(lg, ref[len(want) + i:len(want) + i + 1])
         assert err <= TOL[dtype], (i, err)
     runner.check_status()
+
+
+OTHER_SIZES = {
+    "0.5b": dict(hidden_size=896, num_attention_heads=14, num_key_value_heads=2, intermediate_size=4864,
+                 vocab_size=151936, tie_word_embeddings=True),          # head 64, a width that is no multiple of 256
+    "7b": dict(hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, intermediate_size=18944,
+               vocab_size=152064, tie_word_embeddings=False),           # 7 query heads a kv head, its own lm_head
+}
+
+
+@pytest.mark.parametrize("size", sorted(OTHER_SIZES))
+def test_other_model_sizes_in_bfloat16(size, tmp_path):
+    """Two layers at the layer sizes of other Qwen2 models: a prompt in two portions (450 + 250 tokens), then six
+    decoded tokens in captured steps, against the plain formulas (float32, on the device)."""
+    from lite_lang_b200 import ops
+    from lite_lang_b200.cache import CacheManager
+    from lite_lang_b200.config import config_from_dict, load_config
+    from lite_lang_b200.engine.batch import StepEntry
+    from lite_lang_b200.engine.model import CausalLM
+    from lite_lang_b200.engine.runner import ModelRunner
+    from lite_lang_b200.weights import load_weights, write_random_model
+
+    dev = torch.device("cuda:0")
+    folder = str(tmp_path)
+    write_random_model(folder, config_from_dict(dict(CFG, **OTHER_SIZES[size])), seed=3,
+                       scales={"matrix": 0.03, "bias": 0.05, "norm": 0.05})
+    cfg, w = P.read_model_folder(folder, device="cuda:0")
+    n_prompt, cut, n_dec = 700, 450, 6
+    toks = random_tokens(n_prompt + n_dec, cfg["vocab_size"], 5)
+    places = [0, 255, 256, cut - 1, cut, n_prompt - 1] + list(range(n_prompt, n_prompt + n_dec))
+    ops.configure_matmul_precision()
+    h = P.embedding(w["model.embed_tokens.weight"], torch.as_tensor(toks, dtype=torch.long, device=dev))
+    for layer in range(cfg["num_hidden_layers"]):
+        h = P.decoder_layer(h, torch.arange(len(toks), device=dev), w, layer, cfg)
+    head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else w["lm_head.weight"]
+    ref = P.linear(P.rms_norm(h[places], w["model.norm.weight"], float(cfg["rms_norm_eps"])), head).cpu().numpy()
+    del w, h
+
+    m = CausalLM(load_config(folder).model_spec())
+    load_weights(m, folder, torch.bfloat16, dev)
+    mgr = CacheManager(m.cache_groups, [64], 16, 2, 1024)
+    runner = ModelRunner(m, mgr, dev, 1024, cuda_graphs=True)
+    a = mgr.open()
+    assert runner.reserve(a, n_prompt)
+    first = tuple(p for p in places if p < cut)
+    second = tuple(p - cut for p in places if cut <= p < n_prompt)
+    lg1 = runner.step([StepEntry(a, toks[:cut], first)]).float().cpu().numpy()
+    lg2 = runner.step([StepEntry(a, toks[cut:n_prompt], second)]).float().cpu().numpy()
+    assert rel_err(np.concatenate([lg1, lg2]), ref[:len(first) + len(second)]) <= TOL["bfloat16"]
+    for i in range(n_dec):
+        assert runner.reserve(a, 1)
+        lg = runner.step([StepEntry(a, [toks[n_prompt + i]], (0,))]).float().cpu().numpy()
+        k = len(first) + len(second) + i
+        assert rel_err(lg, ref[k:k + 1]) <= TOL["bfloat16"], i
+    runner.check_status()
+    assert runner.graph_replays == n_dec
