@@ -159,7 +159,8 @@ def device_decode(engine, batch, steps, warmup, sampler_on=True):
     for p in prompts:                                   # prefill, untimed
         s = m.open()
         assert s is not None and runner.reserve(s, PROMPT_LEN)
-        runner.step([StepEntry(s, p, ())])
+        for c0 in range(0, PROMPT_LEN, 2048):           # in portions of the step's token limit
+            runner.step([StepEntry(s, p[c0:c0 + 2048], ())])
         slots.append(s)
     torch.cuda.synchronize()
     toks = random_prompts(1, steps + warmup, vocab, 9)[0]
@@ -451,11 +452,19 @@ def main():
                     help="instead of the headline measurement: a whole serving workload through the scheduler "
                          "(Qwen2.5-3B sizes, 40 requests of 600 + 600 tokens; Qwen2-7B sizes, 64 requests with prompts "
                          "of 128..4096 tokens cut into portions of 2,048 a step, 256 new tokens each)")
+    ap.add_argument("--prompt-len", type=int, default=0,
+                    help="with --only decode: another context length than the headline's 2,048 prompt tokens")
     ap.add_argument("--shape", default="", choices=[""] + sorted(WORKLOADS),
                     help="with --only: the layer sizes of that workload's model instead of Qwen2-1.5B's")
     args = ap.parse_args()
     if args.shape and not args.only:
         ap.error("--shape goes with --only (the headline measurement is of the Qwen2-1.5B sizes)")
+    if args.prompt_len:
+        if args.only != "decode":
+            ap.error("--prompt-len goes with --only decode")
+        global PROMPT_LEN, CONTEXT
+        PROMPT_LEN = args.prompt_len
+        CONTEXT = args.prompt_len + args.steps + args.warmup + 64
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not built (this engine has no multi-GPU path)")
         return 2
