@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import ROOT, TINY, make_model_folder, random_tokens, rel_err
+from helpers import ROOT, TINY, TOL, make_model_folder, random_tokens, rel_err
 from plain import qwen2_plain as P
 
 pytestmark = pytest.mark.gpu
@@ -23,6 +23,19 @@ def engine(folder, dtype, name, **kw):
 
 
 @pytest.mark.parametrize("name,lengths", [("A", [5, 11, 17]), ("B", [1, 7, 23, 40]), ("C", [60, 3, 33])])
+def _assert_greedy_or_near_tie(cfg, w, prompt, out, margin):
+    """Every token of ``out`` is the plain argmax, up to the first place where the plain top two
+    logits are closer than ``margin`` of the largest logit (after which the sequences may part)."""
+    seq = list(prompt)
+    for tok in out:
+        logits = P.forward_logits(cfg, w, seq)[-1]
+        top2 = torch.topk(logits, 2).values
+        if float(top2[0] - top2[1]) <= margin * float(logits.abs().max()):
+            return
+        assert tok == int(torch.argmax(logits)), (len(prompt), len(seq))
+        seq.append(tok)
+
+
 def test_greedy_generation_equals_the_plain_continuation(name, lengths):
     """float32: token for token, unless the plain top two logits are closer than the engine's error."""
     folder = make_model_folder(name, scales={"matrix": 0.08})
@@ -44,7 +57,20 @@ def test_greedy_generation_equals_the_plain_continuation(name, lengths):
     assert st["finished"] == len(prompts) and eng.manager.num_free_pages() == eng.manager.total_pages()
 
 
-def test_bfloat16_generation_runs_captured_steps_and_agrees_with_itself():
+def _assert_within_rounding(cfg, w, prompt, out, tol):
+    """Every token of ``out`` is, given the tokens before it, the plain argmax up to the engine's rounding:
+    logits that differ from the plain ones by at most ``tol`` of the largest can only move the argmax to a
+    token whose plain logit lies within 2 * tol of the plain maximum.  The check follows the engine's own
+    tokens, so it holds at every place, whatever was chosen before."""
+    seq = list(prompt)
+    for k, tok in enumerate(out):
+        logits = P.forward_logits(cfg, w, seq)[-1]
+        slack = 2 * tol * float(logits.abs().max())
+        assert float(logits[tok]) >= float(logits.max()) - slack, (len(prompt), k, tok, int(torch.argmax(logits)))
+        seq.append(tok)
+
+
+def test_bfloat16_generation_runs_captured_steps_and_equals_the_plain_continuation_up_to_rounding():
     from lite_lang_b200 import SamplingParams
     folder = make_model_folder("C", scales={"matrix": 0.08})
     cfg, w = P.read_model_folder(folder)
@@ -57,18 +83,11 @@ def test_bfloat16_generation_runs_captured_steps_and_agrees_with_itself():
     a2 = e2.generate(prompts, sp)
     assert a == a2                                     # the same run twice: the same tokens
     assert e2.stats()["graph_replays"] > 0
-    # captured or not, cut differently: the logits agree within bfloat16 rounding, so the greedy
-    # tokens agree wherever the plain top two are clearly apart
+    # captured steps or not, prompts whole or in portions of 16: every token against the plain logits
     for prompt, x, y in zip(prompts, a, b):
-        seq = list(prompt)
-        for tx, ty in zip(x, y):
-            logits = P.forward_logits(cfg, w, seq)[-1]
-            top2 = torch.topk(logits, 2).values
-            if float(top2[0] - top2[1]) > 0.1 * float(logits.abs().max()):
-                assert tx == ty == int(torch.argmax(logits))
-            if tx != ty:
-                break
-            seq.append(tx)
+        assert len(x) == len(y) == 12
+        _assert_within_rounding(cfg, w, prompt, x, TOL["bfloat16"])
+        _assert_within_rounding(cfg, w, prompt, y, TOL["bfloat16"])
 
 
 def test_temperature_sampling_is_seeded_and_independent_of_batching():
@@ -98,8 +117,9 @@ def test_temperature_sampling_is_seeded_and_independent_of_batching():
     mixed = engine(folder, "float32", "B").generate(
         prompts[:2], [SamplingParams(temperature=0.7, do_sample=False, max_new_tokens=4, ignore_eos=True),
                       SamplingParams(temperature=0.0, max_new_tokens=4, ignore_eos=True)])
-    assert mixed[0] == P.greedy_generate(cfg, w, prompts[0], 4) or True
-    assert len(mixed[0]) == 4 and len(mixed[1]) == 4
+    for prompt, out in zip(prompts[:2], mixed):
+        assert len(out) == 4
+        _assert_greedy_or_near_tie(cfg, w, prompt, out, 1e-4)
 
 
 def test_preemption_under_a_small_pool_does_not_change_the_tokens():
@@ -151,7 +171,9 @@ def test_steps_launched_ahead_give_the_same_tokens_and_end_requests_on_time():
     cfg, w = P.read_model_folder(folder)
     prompts = [random_tokens(n, cfg["vocab_size"], 90 + i) for i, n in enumerate([12, 30, 5, 19])]
     plain = [P.greedy_generate(cfg, w, p, 14) for p in prompts]
-    eos = plain[1][6]                                   # request 1 ends in the middle by this id
+    # request 1 ends in the middle by an eos id that the other requests never produce within their limits
+    elsewhere = set(plain[0][:14]) | set(plain[2][:3]) | set(plain[3][:9])
+    eos = next(t for t in plain[1][2:12] if t not in elsewhere)
     with open(os.path.join(folder, "config.json"), "w") as fh:
         json.dump(dict(cfg, eos_token_id=eos), fh)
     params = [SamplingParams(temperature=0.0, max_new_tokens=n) for n in (14, 14, 3, 9)]
@@ -175,17 +197,19 @@ def test_steps_launched_ahead_give_the_same_tokens_and_end_requests_on_time():
     out_a, why_a, st_a = run(True)
     out_b, why_b, st_b = run(False)
     assert out_a == out_b and why_a == why_b
-    assert why_a[:4] == ["length", "eos", "length", "length"] or eos in plain[0][:14] or eos in plain[3][:9]
+    assert why_a[:4] == ["length", "eos", "length", "length"]
     assert out_a[1] == plain[1][:plain[1].index(eos) + 1]
     assert out_a[2] == plain[2][:3]
     assert st_a["graph_replays"] > 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("seed", range(12))
-def test_random_serving_runs_equal_the_plain_continuation(seed):
+def test_random_serving_runs_equal_the_plain_continuation(seed, dtype):
     """Random prompts, limits, an eos id taken from the plain continuations, requests arriving while others run,
     tight page pools (requests leave and are recomputed), steps launched ahead or not: every request's tokens
-    equal the plain greedy continuation, and every page comes back."""
+    equal the plain greedy continuation, and every page comes back.  In bfloat16 every token is checked against
+    the plain logits of the tokens before it, within twice the tolerance of the logits."""
     import random
     from lite_lang_b200 import Engine, EngineConfig, SamplingParams
     rng = random.Random(1000 + seed)
@@ -205,7 +229,7 @@ def test_random_serving_runs_equal_the_plain_continuation(seed):
     ps = TINY[name]["page_size"]
     need = max((len(p) + m + ps) // ps + 1 for p, m in zip(prompts, max_new))
     pages = rng.randint(need, need + 3) if rng.random() < 0.7 else rng.randint(need, need * 3)
-    eng = Engine(folder, EngineConfig(dtype="float32", page_size=ps, num_pages=pages, max_batch_size=rng.choice([2, 4]),
+    eng = Engine(folder, EngineConfig(dtype=dtype, page_size=ps, num_pages=pages, max_batch_size=rng.choice([2, 4]),
                                       max_input_length=100, max_output_length=16,
                                       max_tokens_per_step=rng.choice([8, 16, 64])))
     eng._pipeline = rng.random() < 0.8
@@ -225,6 +249,16 @@ def test_random_serving_runs_equal_the_plain_continuation(seed):
     eng.manager.check_invariants()
     assert eng.manager.num_free_pages() == eng.manager.total_pages()
     for i in range(n_req):
+        if dtype == "bfloat16":
+            got = list(reqs[i].output)
+            if reqs[i].finish_reason == "cache_full":
+                continue
+            _assert_within_rounding(cfg, w, prompts[i], got, TOL["bfloat16"])
+            if eos is not None and eos in got:
+                assert got.index(eos) == len(got) - 1 and reqs[i].finish_reason == "eos"
+            else:
+                assert len(got) == max_new[i] and reqs[i].finish_reason == "length"
+            continue
         want = plain[i]
         if eos is not None and eos in want:
             want = want[:want.index(eos) + 1]
