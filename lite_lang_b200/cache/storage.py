@@ -10,11 +10,17 @@ The block tables are decided on the host (``CacheManager``); ``sync`` pushes the
 rows that changed since the last step and zeroes the state records of request
 slots opened since then.  Rows travel through pinned staging buffers guarded by
 events, so the host may run ahead of the device.
+
+The pools start as zeros.  No kernel may depend on that, nor on what an earlier
+owner left in a page: with ``LITE_LANG_B200_CACHE_FILL=nan`` in the environment
+the pools start as NaN instead, and the results must be the same (the replay
+tests run that way).
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -65,8 +71,9 @@ class CacheStorage:
             spec = manager.groups[g]
             n = manager.allocators[g].num_pages
             shape = (spec.planes, n, spec.num_kv_heads, manager.page_size, spec.head_dim)
-            self.k[g] = torch.zeros(shape, dtype=dtype, device=device)
-            self.v[g] = torch.zeros(shape, dtype=dtype, device=device)
+            fill = float("nan") if os.environ.get("LITE_LANG_B200_CACHE_FILL", "") == "nan" else 0.0
+            self.k[g] = torch.full(shape, fill, dtype=dtype, device=device)
+            self.v[g] = torch.full(shape, fill, dtype=dtype, device=device)
             self.block_table[g] = torch.full((manager.max_requests, manager.max_blocks), -1, dtype=torch.int32,
                                              device=device)
             self._stage[g] = [torch.empty((manager.max_requests, manager.max_blocks), dtype=torch.int32,

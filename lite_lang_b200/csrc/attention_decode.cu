@@ -293,6 +293,18 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
       vv[h][2] = lds16(vst + (2 * c + 8) * ROW_BYTES + piece);
       vv[h][3] = lds16(vst + (2 * c + 9) * ROW_BYTES + piece);
     }
+    // keys that the token may not see have probability 0 by selection, but what their rows of V hold (left by an
+    // earlier owner of the page, possibly Inf or NaN) would still spoil the product: zeros by selection too
+    if (boundary) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = key0 + 2 * c + (i & 1) + 8 * (i >> 1);
+        if (j > pos || j < lo) {
+#pragma unroll
+          for (int h = 0; h < VS; ++h) vv[h][i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    }
     // ---- O^T = O^T * alpha + V^T P^T ----
     const bool rescale = (alpha[0] != 1.f) || (alpha[1] != 1.f);
 #pragma unroll

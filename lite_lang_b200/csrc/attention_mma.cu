@@ -327,6 +327,18 @@ __global__ void __launch_bounds__(NW * 32) attn_mma_kernel(const AttnMmaParams p
     const unsigned pa1 = pack_bf16(s_acc[0][2], s_acc[0][3]);
     const unsigned pa2 = pack_bf16(s_acc[1][0], s_acc[1][1]);
     const unsigned pa3 = pack_bf16(s_acc[1][2], s_acc[1][3]);
+    // keys outside what any row of the block may see have probability 0 by selection, but what their rows of V
+    // hold (left by an earlier owner of the page, possibly Inf or NaN) would still spoil the product: zeros too
+    if (key0 + AM_TILE - 1 > j_hi || key0 < j_lo) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = key0 + 2 * c + (i & 1) + 8 * (i >> 1);
+        if (j > j_hi || j < j_lo) {
+#pragma unroll
+          for (int h = 0; h < VS; ++h) vv[h][i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    }
     // ---- O = O * alpha + P V ----
 #pragma unroll
     for (int h = 0; h < VS; ++h) {

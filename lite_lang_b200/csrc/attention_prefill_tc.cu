@@ -27,8 +27,12 @@
 //
 // Masked places: a key after the row's position, or before its window, gets probability 0 by selection
 // (never by arithmetic on what was read).  Pages that a window has given back (table entry -1) and pages
-// beyond the context are read from page 0 instead and are always masked.  The cache is zero-filled when
-// it is made and only ever holds finite numbers, so 0 x (stale value) stays 0 in PV.
+// beyond the context are read from page 0 instead and are always masked.  What such places hold is
+// whatever an earlier owner of the page left there, possibly Inf or NaN, and 0 x NaN is NaN in P V: so in
+// a block with keys that none of the CTA's rows may see (the last block of the rows, the first one of a
+// window), the softmax warps overwrite those keys' rows of V in shared memory with zeros before the
+// product is issued.  A table entry of a key that a row does see must name a page of the pool; one that
+// does not sets LL_ERR_PAGE_RANGE.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -321,8 +325,13 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
     auto page_of = [&](int j) -> int {   // cache row of this lane's box of block j
       const int kp = (kb_lo + j) * AT_KB + lane * p.box_rows;
       const int lp = kp / p.page_size;
-      int page = (lane < boxes && j < nblk && lp < p.bt_stride) ? bt[lp] : -1;
-      if (page < 0 || page >= p.num_pages) page = 0;   // given back or beyond the context: masked below
+      const bool mine = lane < boxes && j < nblk;
+      int page = (mine && lp < p.bt_stride) ? bt[lp] : -1;
+      if (page < 0 || page >= p.num_pages) {   // given back or beyond the context: masked, and V zeroed, below
+        if (mine && (page >= p.num_pages || (kp <= hi && kp + p.box_rows - 1 >= lo_min)))
+          set_status(p.status, LL_ERR_PAGE_RANGE);   // a key that a row sees has no page of the pool
+        page = 0;
+      }
       return (page * p.nkv + kvh) * p.page_size + kp % p.page_size;
     };
     // order of the copies: K(0), K(1), then V(j) before K(j + 2), the order in which the MMAs want them
@@ -468,6 +477,19 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
             for (int i = 0; i < 32; ++i) v[i] *= factor;
             at_st32(tmem_o + lane_addr + c0, v);
           }
+        }
+      }
+      // keys that no row of the CTA may see: their rows of V (128 bytes for each 64 head-size elements, whole
+      // rows, so the swizzle does not matter) become zeros before the product reads them
+      if (k0 + AT_KB - 1 > hi || k0 < lo_min) {
+        const int s = j % AT_KS;
+        at_mbar_wait(v_full0 + 8 * s, (unsigned)((j / AT_KS) & 1), p.status, dead);
+        unsigned char* v_s = kv_s + s * STAGE_BYTES + KV_BYTES;
+        for (int idx = tid - 64; idx < AT_KB * HB * 8; idx += 128) {
+          const int kk = idx / (HB * 8), rest = idx - kk * (HB * 8);
+          if (k0 + kk > hi || k0 + kk < lo_min)
+            *reinterpret_cast<uint4*>(v_s + (rest >> 3) * (KV_BYTES / HB) + kk * 128 + ((rest & 7) << 4)) =
+                make_uint4(0u, 0u, 0u, 0u);
         }
       }
       // piece c of the row goes to (c ^ (r & 7)) of the swizzled 128-byte row

@@ -94,14 +94,18 @@ def random_tokens(n: int, vocab: int, seed: int) -> List[int]:
 class TraceRun:
     """Drives bin/trace_run as a user would: a process, steps on stdin, logits in files."""
 
-    def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, extra=()):
+    def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, extra=(),
+                 cache_fill: Optional[str] = None):
         self.out = tempfile.mkdtemp(prefix="ll_trace_")
         cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
                "--out", self.out, "--max-tokens", str(max_tokens), "--page-size", str(page_size), *extra]
         self.err_path = os.path.join(self.out, "stderr.txt")
         self._err = open(self.err_path, "w")
+        env = dict(os.environ)
+        if cache_fill is not None:            # what the cache pools hold before anything is written to them
+            env["LITE_LANG_B200_CACHE_FILL"] = cache_fill
         self.proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=self._err,
-                                     text=True, bufsize=1)
+                                     text=True, bufsize=1, env=env)
         self.step_no = 0
         self.vocab = json.load(open(os.path.join(model_dir, "config.json")))["vocab_size"]
 

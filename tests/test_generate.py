@@ -22,7 +22,6 @@ def engine(folder, dtype, name, **kw):
     return Engine(folder, EngineConfig(**cfg))
 
 
-@pytest.mark.parametrize("name,lengths", [("A", [5, 11, 17]), ("B", [1, 7, 23, 40]), ("C", [60, 3, 33])])
 def _assert_greedy_or_near_tie(cfg, w, prompt, out, margin):
     """Every token of ``out`` is the plain argmax, up to the first place where the plain top two
     logits are closer than ``margin`` of the largest logit (after which the sequences may part)."""
@@ -36,6 +35,7 @@ def _assert_greedy_or_near_tie(cfg, w, prompt, out, margin):
         seq.append(tok)
 
 
+@pytest.mark.parametrize("name,lengths", [("A", [5, 11, 17]), ("B", [1, 7, 23, 40]), ("C", [60, 3, 33])])
 def test_greedy_generation_equals_the_plain_continuation(name, lengths):
     """float32: token for token, unless the plain top two logits are closer than the engine's error."""
     folder = make_model_folder(name, scales={"matrix": 0.08})

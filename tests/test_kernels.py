@@ -490,6 +490,103 @@ def test_attn_mma_padding_entries_and_refusals():
                      1.0, 1, None, None, None)
 
 
+def _poison_what_no_query_may_see(c, ps, window):
+    """Inf and NaN in every place of the pools that no query of the case may read: pages nobody owns (page 0
+    among them: the kernels read it in place of a page that is not there), the unwritten ends of last pages,
+    and pages that lie wholly before every query's window, which are also taken out of the block table, as
+    the cache manager does.  That is what an earlier owner with broken weights may have left behind."""
+    bt = c["bt"].cpu().clone()
+    kc, vc = c["kc"].clone(), c["vc"].clone()
+    num_pages = kc.shape[0]
+    owned = set(int(x) for x in bt.flatten().tolist() if x >= 0)
+    if 0 in owned:                                  # page 0 becomes nobody's
+        spare = next(pg for pg in range(num_pages) if pg not in owned)
+        kc[spare], vc[spare] = kc[0], vc[0]
+        bt[bt == 0] = spare
+        owned.discard(0)
+        owned.add(spare)
+    bad = torch.tensor([float("nan"), float("inf"), -float("inf")], device=kc.device).to(kc.dtype)
+
+    def spoil(t):
+        t.copy_(bad[torch.randint(0, 3, t.shape, device=t.device)])
+
+    for pg in range(num_pages):
+        if pg not in owned:
+            spoil(kc[pg])
+            spoil(vc[pg])
+    for i, (l, ql) in enumerate(zip(c["lens"], c["q_lens"])):
+        row = bt[int(c["req_slot"][i])]
+        last = (l - 1) // ps
+        if l % ps:
+            spoil(kc[int(row[last]), :, l % ps:])
+            spoil(vc[int(row[last]), :, l % ps:])
+        if window is not None:
+            first_needed = max(0, (l - ql) - window + 1)
+            for lp in range(first_needed // ps):
+                spoil(kc[int(row[lp])])
+                spoil(vc[int(row[lp])])
+                row[lp] = -1
+    return dict(c, kc=kc, vc=vc, bt=bt.to(c["bt"].device))
+
+
+@pytest.mark.parametrize("kernel", ["generic32", "generic", "mma", "mma_split", "decode", "decode_split", "prefill",
+                                    "prefill_tc"])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attention_kernels_are_blind_to_what_freed_pages_hold(kernel, window):
+    """0 x NaN is NaN: a key that is masked must not enter the products with whatever its page holds."""
+    from lite_lang_b200 import ops
+    d = dev()
+    dtype = torch.float32 if kernel == "generic32" else torch.bfloat16
+    nh, nkv, hd, ps = 12, 2, 128, 16
+    lens = [333, 90, 1, 203]                                  # no length is a multiple of the page size
+    decode = kernel.startswith("decode") or kernel.startswith("mma")
+    q_lens = [1, 1, 1, 1] if decode else [150, 90, 1, 2]
+    c = _paged_case(dtype, nh, nkv, hd, ps, lens, q_lens, window, seed=41)
+    c = _poison_what_no_query_may_see(c, ps, window)
+    status = torch.zeros(1, dtype=torch.int32, device=d)
+    out = torch.full_like(c["q"], 3.0)
+    cu = [0]
+    for ql in q_lens:
+        cu.append(cu[-1] + ql)
+    cu_q = torch.tensor(cu, dtype=torch.int32, device=d)
+    ctx = torch.tensor([l - ql for l, ql in zip(lens, q_lens)], dtype=torch.int32, device=d)
+    group = nh // nkv
+    if kernel.startswith("generic"):
+        ops.paged_attention_generic(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], c["token_req"],
+                                    c["req_slot"], c["positions"], c["q"].shape[0], nh, nkv, hd, ps, window,
+                                    hd ** -0.5, status)
+    elif kernel.startswith("mma"):
+        out = _run_mma(c, nh, nkv, hd, ps, window, 4 if kernel == "mma_split" else 1, cluster=kernel == "mma_split")
+    elif kernel.startswith("decode"):
+        ops.attn_decode(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], ctx, c["req_slot"], len(lens), nh,
+                        nkv, hd, ps, window, hd ** -0.5, 4 if kernel == "decode_split" else 1, status)
+    elif kernel == "prefill":
+        blocks = sum((ql * group + 127) // 128 for ql in q_lens)
+        ops.attn_prefill(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], cu_q, ctx, c["req_slot"], len(lens),
+                         blocks, nh, nkv, hd, ps, window, hd ** -0.5, status)
+    else:
+        for nsplit in (1, 4):
+            out = _run_prefill_tc(c, nh, nkv, hd, ps, lens, q_lens, window, status, nsplit)
+            assert torch.isfinite(out.float()).all(), nsplit
+            assert_close(out, c["ref"], dtype, f"{kernel} nsplit {nsplit}")
+    assert status.item() == 0
+    assert torch.isfinite(out.float()).all()
+    assert_close(out, c["ref"], dtype, kernel)
+
+
+def test_attn_prefill_tc_reports_a_table_entry_outside_the_pool():
+    """A key that a row sees and whose table entry names no page of the pool sets the status word (3) instead
+    of being read from somewhere."""
+    nh, nkv, hd, ps = 8, 2, 64, 16
+    c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, [200], [100], None, seed=42)
+    for bad in (c["kc"].shape[0] + 5, -1):
+        bt = c["bt"].clone()
+        bt[int(c["req_slot"][0]), 3] = bad
+        status = torch.zeros(1, dtype=torch.int32, device=dev())
+        _run_prefill_tc(dict(c, bt=bt), nh, nkv, hd, ps, [200], [100], None, status, 1)
+        assert status.item() == 3, bad
+
+
 def test_padding_entries_write_zeros_and_read_nothing():
     from lite_lang_b200 import ops
     c = _paged_case(torch.float32, 4, 2, 32, 8, [20], [1], None, seed=8)

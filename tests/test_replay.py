@@ -77,7 +77,8 @@ def test_mixed_with_pages_used_again(case, dtype):
     # four live requests of at most 64-rounded lengths: the pool is just large enough for them
     order = [0, 1, 2, 3, 4, 5, 1, 3]
     need = sorted(((len(seqs[i]) + 63) // 64 * 64 for i in order), reverse=True)[:4]
-    tr = TraceRun(folder, dtype, max_tokens=sum(need), page_size=ps)
+    # (the pools start as NaN: nothing may depend on what a page held before its owner wrote to it)
+    tr = TraceRun(folder, dtype, max_tokens=sum(need), page_size=ps, cache_fill="nan")
     rng = np.random.default_rng(7)
     try:
         waiting = list(enumerate(order))

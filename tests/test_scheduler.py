@@ -89,13 +89,91 @@ def test_model_length_ends_a_request():
     assert b.finish_reason == "too_long" and not s.has_work()
 
 
-def test_peak_estimate_is_the_references_formula():
-    # litelang/scheduler/req_queue.py:219-232 on [(held, expected)]
-    rows = [(10, 5), (3, 20), (7, 1)]
-    # sorted by expected desc: (3,20),(10,5),(7,1): cumsum held 3,13,20; + expected*k: 23, 23, 23
-    assert peak_token_estimate(rows) == 23
-    assert peak_token_estimate([(4, 6)]) == 10
+def _anchors():
+    import json
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "scheduler_anchors.json")
+    with open(path) as fh:
+        return json.load(fh)
+
+
+def test_peak_estimate_equals_the_references_answers():
+    """``peak_token_estimate`` on the rows (tokens held, tokens expected) that the reference built gives the
+    reference's own answer (``ReadyQue._can_add_new_req``, litelang/scheduler/req_queue.py:219-232) in every
+    stored case; the file was made by tests/golden/make_scheduler_anchors.py from the reference's code."""
+    cases = _anchors()["admission"]
+    assert len(cases) >= 100 and 0 < sum(c["admitted"] for c in cases) < len(cases)
+    for c in cases:
+        assert (peak_token_estimate([tuple(r) for r in c["rows"]]) <= c["pool"]) == c["admitted"], c
     assert peak_token_estimate([]) == 0
+
+
+def test_admission_equals_the_references_on_its_own_inputs():
+    """The scheduler's own rows and its decision, on the stored inputs.  For requests that have produced
+    nothing yet the rows are the reference's (``Req.need_tokens``, req_queue.py:59-66) and so is the decision.
+    For a request that has produced n tokens the reference keeps expecting its whole guess on top of what the
+    request holds; this scheduler expects the guess less n, the only difference, so its row is the
+    reference's with n taken off (never below zero)."""
+    for c in _anchors()["admission"]:
+        m = CacheManager([PagedGroupSpec(1, 16, None, 1)], [c["pool"]], 1, 16, 10 ** 6)
+        s = Scheduler(m, 64, max_reqs=100, busy_scale=0.6)
+        reqs = []
+        for i, (n_in, n_out, max_out) in enumerate(c["requests"]):
+            r = req(i, n_in, max_out)
+            r.output = [1] * n_out
+            reqs.append(r)
+        s.running = reqs[:-1]
+        s._is_busy = lambda busy=c["busy"]: busy
+        rows = [(r.length, s._expected_new(r, c["busy"])) for r in reqs]
+        want = [(held, max(0, expected - n_out)) for (held, expected), (_, n_out, _) in zip(c["rows"], c["requests"])]
+        assert rows == want, c
+        if all(n_out == 0 for _, n_out, _ in c["requests"]):
+            assert s._fits(reqs[-1]) == c["admitted"], c
+        else:
+            assert s._fits(reqs[-1]) == (peak_token_estimate(want) <= c["pool"])
+            assert s._fits(reqs[-1]) or not c["admitted"]      # whoever the reference admits is admitted here
+
+
+def test_busy_is_the_references_threshold():
+    # litelang/scheduler/req_queue.py:194,213-217: tokens held by running and preempted requests > pool * busy_scale
+    m, s = make(num_pages=25, page_size=4, budget=8)          # 100 tokens, threshold 60
+    a, b = req(0, 30, 5), req(1, 30, 5)
+    s.running = [a]
+    b.preemptions = 1
+    s.waiting.append(b)
+    assert not s._is_busy()                                   # 60 is not more than 60
+    a.output = [1]
+    assert s._is_busy()
+
+
+def test_strategies_order_as_the_references_do():
+    """The four orders in which requests leave (litelang/scheduler/pause_strategy.py:18-39), on the stored
+    inputs.  The reference's LongestFirstStrategy sorts by length ascending and its ShortestFirstStrategy
+    descending; here the same two orders carry names that say what they do.  The requests the reference takes
+    out (``select_swapped_reqs``, :42-55) are the first of that order until more than the missing tokens are
+    covered; this scheduler lets them leave one at a time, in the same order, until the pages suffice."""
+    names = {"FIFOStrategy": "FIFOStrategy", "LIFOStrategy": "LIFOStrategy",
+             "LongestFirstStrategy": "ShortestLeavesFirstStrategy", "ShortestFirstStrategy": "LongestLeavesFirstStrategy"}
+    cases = _anchors()["preemption"]
+    assert len(cases) >= 100
+    for c in cases:
+        reqs = []
+        for i, n in enumerate(c["lengths"]):
+            r = req(i, n, 10)
+            r.arrival = i
+            reqs.append(r)
+        for ref_name, ours in names.items():
+            order = [r.id for r in STRATEGIES[ours](list(reqs))]
+            assert order == c["strategies"][ref_name]["order"], (ref_name, c)
+            out = c["strategies"][ref_name]["out"]
+            assert order[:len(out)] == out
+            # one at a time until the missing tokens are covered: the same requests, or one fewer where the
+            # reference's "more than" takes one more than is needed
+            freed, k = 0, 0
+            while freed < c["need"] and k < len(order):
+                freed += c["lengths"][order[k]]
+                k += 1
+            assert k in (len(out), len(out) - 1), (ref_name, c)
 
 
 def test_admission_waits_for_room_in_the_estimate():
