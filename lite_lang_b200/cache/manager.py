@@ -66,11 +66,25 @@ class PageAllocator:
 @dataclass(frozen=True)
 class PagedGroupSpec:
     num_kv_heads: int
-    head_dim: int
+    head_dim: int               # width of a key
     window: Optional[int]
     planes: int                 # cache planes (one per run-step that writes into this group)
+    value_head_dim: Optional[int] = None   # width of a value; None: head_dim; 0: the group has no value plane
 
     kind = "paged"
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.value_head_dim is None else self.value_head_dim
+
+    def pages_a_request_needs(self, length: int, page_size: int, step_tokens: int) -> int:
+        """The most pages a request of ``length`` tokens holds at a time when it grows by at most
+        ``step_tokens`` a step: all of them without a window; with one, the window, the step's new tokens
+        (pages are given back after the step) and the partly used pages at both ends."""
+        full = (length + page_size - 1) // page_size
+        if self.window is None:
+            return full
+        return min(full, (self.window + step_tokens + page_size - 1) // page_size + 1)
 
 
 @dataclass(frozen=True)
@@ -167,6 +181,37 @@ class CacheManager:
         want = (new_length + self.page_size - 1) // self.page_size
         have = {g: (len(self._requests[slot].pages[g]) if slot is not None else 0) for g in self.paged_ids}
         return {g: max(0, want - have[g]) for g in self.paged_ids}
+
+    def max_reservable(self, slot: int) -> int:
+        """The largest length ``reserve`` would accept for the request now (every group asked)."""
+        req = self._get(slot)
+        most = self.max_model_len
+        for g in self.paged_ids:
+            most = min(most, (len(req.pages[g]) + self.allocators[g].num_free) * self.page_size)
+        return most
+
+    def can_ever_hold(self, length: int, step_tokens: int = 1) -> bool:
+        """Whether a request of ``length`` tokens fits the pools when it is alone (growing by
+        ``step_tokens`` a step at most)."""
+        if length > self.max_model_len:
+            return False
+        return all(self.groups[g].pages_a_request_needs(length, self.page_size, step_tokens)
+                   <= self.allocators[g].num_pages for g in self.paged_ids)
+
+    def capacity_tokens(self) -> int:
+        """Tokens of context the pools hold: what the scheduler's admission estimate is compared with.
+        Groups that keep every position set it; if every group has a window, the number of requests
+        whose windows fit, times the longest request."""
+        full = [self.allocators[g].num_pages * self.page_size for g in self.paged_ids
+                if self.groups[g].window is None]
+        if full:
+            return min(full)
+        if not self.paged_ids:
+            return self.max_requests * self.max_model_len
+        fit = min(self.allocators[g].num_pages //
+                  max(1, self.groups[g].pages_a_request_needs(self.max_model_len, self.page_size, 1))
+                  for g in self.paged_ids)
+        return fit * self.max_model_len
 
     def can_reserve(self, slot: Optional[int], new_length: int) -> bool:
         if new_length > self.max_model_len:

@@ -1,8 +1,9 @@
 """Device side of the cache: page pools, block-table mirrors, state records.
 
 Layout of a paged group: keys and values are separate tensors
-``[planes, num_pages, kv_heads, page_size, head_dim]`` so that the keys of one
-(page, kv head) are one contiguous tile.  The reference stores
+``[planes, num_pages, kv_heads, page_size, width]`` so that the keys of one
+(page, kv head) are one contiguous tile; the width of the values may differ from
+the keys', and a group whose mixers keep one vector per token has no value tensor.  The reference stores
 ``[layers, tokens, 2*kv_heads, head_dim]`` with one token per slot
 (``litelang/models/cache.py:196-205``).
 
@@ -35,7 +36,7 @@ class PagedKVView:
     """What a mixer sees of its cache plane during one step."""
 
     k: torch.Tensor              # [num_pages, kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    v: Optional[torch.Tensor]    # [num_pages, kv_heads, page_size, value width], None if the group keeps no values
     block_table: torch.Tensor    # int32 [request slots, max_blocks]
     slot_map: Optional[torch.Tensor]   # int32 [tokens]: where each new token's k/v go
     page_size: int
@@ -70,10 +71,11 @@ class CacheStorage:
         for g in manager.paged_ids:
             spec = manager.groups[g]
             n = manager.allocators[g].num_pages
-            shape = (spec.planes, n, spec.num_kv_heads, manager.page_size, spec.head_dim)
+            shape = (spec.planes, n, spec.num_kv_heads, manager.page_size)
             fill = float("nan") if os.environ.get("LITE_LANG_B200_CACHE_FILL", "") == "nan" else 0.0
-            self.k[g] = torch.full(shape, fill, dtype=dtype, device=device)
-            self.v[g] = torch.full(shape, fill, dtype=dtype, device=device)
+            self.k[g] = torch.full(shape + (spec.head_dim,), fill, dtype=dtype, device=device)
+            if spec.value_dim > 0:
+                self.v[g] = torch.full(shape + (spec.value_dim,), fill, dtype=dtype, device=device)
             self.block_table[g] = torch.full((manager.max_requests, manager.max_blocks), -1, dtype=torch.int32,
                                              device=device)
             self._stage[g] = [torch.empty((manager.max_requests, manager.max_blocks), dtype=torch.int32,
@@ -125,7 +127,8 @@ class CacheStorage:
                 self._stage_events[g][turn].record()
 
     def paged_view(self, group: int, plane: int, slot_map: Optional[torch.Tensor], writable: bool) -> PagedKVView:
-        return PagedKVView(self.k[group][plane], self.v[group][plane], self.block_table[group],
+        v = self.v.get(group)
+        return PagedKVView(self.k[group][plane], None if v is None else v[plane], self.block_table[group],
                            slot_map if writable else None, self.manager.page_size, writable, group, plane)
 
     def state_view(self, group: int, plane: int, writable: bool = True) -> StateView:

@@ -26,13 +26,16 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement (``block``) of a mixer, a feed-forward and norms."""
+    """One layer: an arrangement (``block``) and the parts it arranges, by role.
+
+    Which roles there are is the block kind's business: the pre-norm block takes ``mixer``,
+    ``feed_forward``, ``mixer_norm`` and ``feed_forward_norm``; a block with norms after its parts, or with
+    two mixers, names its own.  The block kind also says which family (mixer, feed_forward, norm) each
+    role's part is built from.
+    """
 
     block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    parts: Mapping[str, PartSpec]
 
 
 @dataclass(frozen=True)

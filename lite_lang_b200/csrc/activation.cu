@@ -44,17 +44,31 @@ __global__ void silu_mul_bf16x8_kernel(bf16* __restrict__ out, const bf16* __res
   }
 }
 
+// SMs of the current device (asked once per device): the grid-stride kernels launch 16 blocks an SM at most
+static int silu_device_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 extern "C" int ll_silu_mul(int dtype, void* out, const void* gate_up, int num_tokens, int inter, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const long total = (long)num_tokens * inter;
+  const long most = (long)silu_device_sms() * 16;
   if (dtype == LL_DTYPE_BF16 && (inter % 8) == 0) {
     const long total8 = total / 8;
-    const int blocks = (int)min((total8 + 255) / 256, (long)148 * 16);
+    const int blocks = (int)min((total8 + 255) / 256, most);
     ll_launch(silu_mul_bf16x8_kernel, dim3(blocks), dim3(256), 0, stream, (bf16*)out, (const bf16*)gate_up, total8,
               inter / 8);
     return LL_LAUNCH_RESULT();
   }
-  const int blocks = (int)min((total + 255) / 256, (long)148 * 16);
+  const int blocks = (int)min((total + 255) / 256, most);
   LL_DISPATCH_DTYPE(dtype, ll_launch(silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)out,
                                      (const T*)gate_up, total, inter));
   return LL_LAUNCH_RESULT();

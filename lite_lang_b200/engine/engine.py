@@ -18,6 +18,7 @@ import torch
 
 from .. import models as _models  # noqa: F401  (registers the architectures)
 from ..cache.manager import CacheManager
+from ..cache.sizing import plan_pages
 from ..config.base import ModelConfig, load_config
 from ..config.engine import EngineConfig
 from ..sampling.sampler import Sampler, SamplingParams, uniform_for
@@ -29,14 +30,6 @@ from .runner import ModelRunner
 from .scheduler import RUNNING, PlannedEntry, Request, Scheduler
 
 _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
-
-
-def cache_bytes_per_page(model: CausalLM, page_size: int, elt: int) -> int:
-    n = 0
-    for g in model.cache_groups:
-        if g.kind == "paged":
-            n += g.planes * 2 * g.num_kv_heads * page_size * g.head_dim * elt
-    return n
 
 
 class _Launched:
@@ -77,17 +70,17 @@ class Engine:
                                  device=str(self.device))
             self.model.load(fetch, self.dtype, self.device)
         self.max_model_len = min(self.cfg.model_len, spec.max_positions)
-        num_pages = self.cfg.num_pages
-        if num_pages is None:
+        n_paged = sum(1 for g in self.model.cache_groups if g.kind == "paged")
+        if self.cfg.num_pages is not None:
+            pages = [self.cfg.num_pages] * n_paged
+        else:
+            # a share of the free memory, less the fixed-size state records, shared out over the groups
             torch.cuda.synchronize(self.device)
             free, _total = torch.cuda.mem_get_info(self.device)
-            per_page = cache_bytes_per_page(self.model, self.cfg.page_size, 2 if self.dtype == torch.bfloat16 else 4)
-            num_pages = max(1, int(free * self.cfg.mem_usage) // max(1, per_page))
-            # no more than every request slot could ever use
-            most = self.cfg.max_batch_size * ((self.max_model_len + self.cfg.page_size - 1) // self.cfg.page_size)
-            num_pages = min(num_pages, most)
-        n_paged = sum(1 for g in self.model.cache_groups if g.kind == "paged")
-        self.manager = CacheManager(self.model.cache_groups, [num_pages] * n_paged, self.cfg.page_size,
+            pages = plan_pages(self.model.cache_groups, int(free * self.cfg.mem_usage), self.cfg.page_size,
+                               2 if self.dtype == torch.bfloat16 else 4, self.cfg.max_batch_size, self.max_model_len,
+                               self.cfg.max_tokens_per_step)
+        self.manager = CacheManager(self.model.cache_groups, pages, self.cfg.page_size,
                                     self.cfg.max_batch_size, self.max_model_len)
         self.runner = ModelRunner(self.model, self.manager, self.device, self.cfg.max_tokens_per_step,
                                   self.cfg.cuda_graphs)

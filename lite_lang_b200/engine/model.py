@@ -27,11 +27,34 @@ from ..parts.base import PagedKVNeed, StateNeed, TensorDecl, build_part, part_cl
 
 
 @dataclass(frozen=True)
-class PlannedStep:
-    layer: int
+class PlannedCache:
     group: Optional[int]     # cache group, None if the mixer keeps nothing
     plane: int
     writable: bool
+
+
+@dataclass(frozen=True)
+class PlannedStep:
+    """A run-step with the cache plane of each of its block's mixers (by role)."""
+
+    layer: int
+    caches: Dict[str, PlannedCache]
+
+    def _first(self) -> PlannedCache:
+        return next(iter(self.caches.values())) if self.caches else PlannedCache(None, 0, False)
+
+    # a block with one mixer (the usual case): that mixer's plane
+    @property
+    def group(self) -> Optional[int]:
+        return self._first().group
+
+    @property
+    def plane(self) -> int:
+        return self._first().plane
+
+    @property
+    def writable(self) -> bool:
+        return self._first().writable
 
 
 class CausalLM:
@@ -41,14 +64,15 @@ class CausalLM:
         self.spec = spec
         self.embedding = build_part("embedding", spec.embedding)
         self.blocks = []
-        for ls in spec.layers:
+        for i, ls in enumerate(spec.layers):
             block_cls = part_class("block", ls.block)
-            self.blocks.append(block_cls(
-                build_part("mixer", ls.mixer),
-                build_part("feed_forward", ls.feed_forward),
-                build_part("norm", ls.mixer_norm),
-                build_part("norm", ls.feed_forward_norm),
-            ))
+            roles = dict(block_cls.roles)
+            missing = sorted(set(roles) - set(ls.parts))
+            unexpected = sorted(set(ls.parts) - set(roles))
+            if missing or unexpected:
+                raise ValueError(f"layer {i}: a {ls.block!r} block is made of {sorted(roles)}; "
+                                 f"missing {missing}, unexpected {unexpected}")
+            self.blocks.append(block_cls({role: build_part(family, ls.parts[role]) for role, family in roles.items()}))
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
         self.plan, self.cache_groups = self._plan_cache()
@@ -63,31 +87,35 @@ class CausalLM:
         for i, rs in enumerate(self.spec.order):
             if not (0 <= rs.layer < len(self.blocks)):
                 raise ValueError(f"run order entry {i} names layer {rs.layer}, which does not exist")
-            need = self.blocks[rs.layer].mixer.cache_need()
-            if need is None:
-                plan.append(PlannedStep(rs.layer, None, 0, False))
-                continue
-            if rs.cache is not None:
-                if not (0 <= rs.cache < i):
-                    raise ValueError(f"run order entry {i} reads the cache of entry {rs.cache}, which is not earlier")
-                src = plan[rs.cache]
-                if src.group is None or keys[src.group] != need or not src.writable:
-                    raise ValueError(f"run order entry {i} cannot read the cache of entry {rs.cache}: "
-                                     "the needs differ or that entry owns no plane")
-                plan.append(PlannedStep(rs.layer, src.group, src.plane, False))
-                continue
-            if need in keys:
-                g = keys.index(need)
-            else:
-                keys.append(need)
-                planes.append(0)
-                g = len(keys) - 1
-            plan.append(PlannedStep(rs.layer, g, planes[g], True))
-            planes[g] += 1
+            if rs.cache is not None and not (0 <= rs.cache < i):
+                raise ValueError(f"run order entry {i} reads the cache of entry {rs.cache}, which is not earlier")
+            caches: Dict[str, PlannedCache] = {}
+            for role, mixer in self.blocks[rs.layer].mixers():
+                need = mixer.cache_need()
+                if need is None:
+                    caches[role] = PlannedCache(None, 0, False)
+                    continue
+                if rs.cache is not None:
+                    src = plan[rs.cache].caches.get(role)
+                    if src is None or src.group is None or keys[src.group] != need or not src.writable:
+                        raise ValueError(f"run order entry {i} cannot read the cache of entry {rs.cache}: "
+                                         "the needs differ or that entry owns no plane")
+                    caches[role] = PlannedCache(src.group, src.plane, False)
+                    continue
+                if need in keys:
+                    g = keys.index(need)
+                else:
+                    keys.append(need)
+                    planes.append(0)
+                    g = len(keys) - 1
+                caches[role] = PlannedCache(g, planes[g], True)
+                planes[g] += 1
+            plan.append(PlannedStep(rs.layer, caches))
         groups: List[object] = []
         for need, n in zip(keys, planes):
             if isinstance(need, PagedKVNeed):
-                groups.append(PagedGroupSpec(need.num_kv_heads, need.head_dim, need.window, n))
+                vd = need.head_dim if need.value_head_dim is None else need.value_head_dim
+                groups.append(PagedGroupSpec(need.num_kv_heads, need.head_dim, need.window, n, vd))
             elif isinstance(need, StateNeed):
                 groups.append(StateGroupSpec(tuple(need.shape), need.dtype, n))
             else:
@@ -125,7 +153,8 @@ class CausalLM:
                 raise ValueError(f"the head is tied to {tied}, which is not the embedding table")
             self.head.tie(self.embedding.weight)
         for b in self.blocks:
-            b.mixer.prepare(device, dtype)
+            for _role, mixer in b.mixers():
+                mixer.prepare(device, dtype)
 
     def kernel_libraries(self) -> List[str]:
         libs: List[str] = []
@@ -156,14 +185,15 @@ class CausalLM:
         h = self.embedding.forward(step.token_ids, n, step.status)
         delta = None
         for ps in self.plan:
-            cache = None
-            if ps.group is not None:
-                gspec = self.cache_groups[ps.group]
-                if gspec.kind == "paged":
-                    cache = storage.paged_view(ps.group, ps.plane, step.slot_maps[ps.group], ps.writable)
+            caches = {}
+            for role, pc in ps.caches.items():
+                if pc.group is None:
+                    caches[role] = None
+                elif self.cache_groups[pc.group].kind == "paged":
+                    caches[role] = storage.paged_view(pc.group, pc.plane, step.slot_maps[pc.group], pc.writable)
                 else:
-                    cache = storage.state_view(ps.group, ps.plane, ps.writable)
-            h, delta = self.blocks[ps.layer].forward(h, delta, step, cache)
+                    caches[role] = storage.state_view(pc.group, pc.plane, pc.writable)
+            h, delta = self.blocks[ps.layer].forward(h, delta, step, caches)
         if step.num_logits == 0:
             return None
         x = self.final_norm.add_forward(h, delta, rows=step.logit_rows)

@@ -158,7 +158,7 @@ class Scheduler:
     # ------------------------------------------------------------------
     @property
     def capacity_tokens(self) -> int:
-        return self.manager.total_pages() * self.manager.page_size
+        return self.manager.capacity_tokens()
 
     def add(self, req: Request) -> bool:
         """Queue a request.  False when the waiting queue is full (``max_reqs``)."""
@@ -252,8 +252,7 @@ class Scheduler:
             # 3. new requests while the estimate, the slots and the budget allow
             while self.waiting and budget > 0 and m.num_free_slots > 0:
                 cand = self.waiting[0]
-                if cand.length + 1 > m.max_model_len or \
-                        (cand.length + m.page_size - 1) // m.page_size > m.total_pages():
+                if cand.length + 1 > m.max_model_len or not m.can_ever_hold(cand.length):
                     self.waiting.popleft()
                     self._finish(cand, "too_long" if cand.length + 1 > m.max_model_len else "cache_full")
                     continue
@@ -327,10 +326,8 @@ class Scheduler:
         if count <= 0:
             return None
         if not m.reserve(req.slot, req.computed + count):
-            # shrink to the pages that are free (whole pages beyond the last partly used one)
-            have = len(m.pages_of(m.paged_ids[0], req.slot)) * m.page_size if m.paged_ids else 10 ** 9
-            room = have + m.num_free_pages() * m.page_size - req.computed
-            count = min(count, room)
+            # shrink to what the pools can take now (every cache group is asked)
+            count = min(count, m.max_reservable(req.slot) - req.computed)
             if count <= 0 or not m.reserve(req.slot, req.computed + count):
                 return None
         return PlannedEntry(req, req.computed, count, req.computed + count == req.length)

@@ -195,10 +195,12 @@ class Qwen2Config(ModelConfig):
             layers.append(
                 LayerSpec(
                     block="pre_norm",
-                    mixer=mixer,
-                    feed_forward=ffn,
-                    mixer_norm=PartSpec("rms_norm", norm, p + "input_layernorm."),
-                    feed_forward_norm=PartSpec("rms_norm", norm, p + "post_attention_layernorm."),
+                    parts={
+                        "mixer": mixer,
+                        "feed_forward": ffn,
+                        "mixer_norm": PartSpec("rms_norm", norm, p + "input_layernorm."),
+                        "feed_forward_norm": PartSpec("rms_norm", norm, p + "post_attention_layernorm."),
+                    },
                 )
             )
         return ModelSpec(

@@ -142,39 +142,39 @@ class GQAttention(Mixer):
         self.attend(attn, qkv, step, cache)
         return self._project_out(attn, residual)
 
-    SM_COUNT = 148
-
-    def _plan_mma(self, step, entries, max_kv_len):
-        """Row blocks, splits and warps of the decode kernel for ``entries`` single-token entries."""
+    def _plan_mma(self, step, entries, max_kv_len, sms):
+        """Row blocks, splits and warps of the decode kernel for ``entries`` single-token entries on a
+        device of ``sms`` SMs."""
         group = self.num_heads // self.num_kv_heads
         max_tiles = (max_kv_len + 15) // 16
         if group <= 8:
-            # attn_decode: one CTA per (entry, kv head, split).  Measured on a B200 (1.5B sizes, context 2k,
-            # batch 1..64): about 128 CTAs are best, as splits of 8, 4, 2 or none, with at least 8 tiles
+            # attn_decode: one CTA per (entry, kv head, split).  Measured on a B200 (148 SMs; 1.5B sizes, context
+            # 2k, batch 1..64): about 7/8 of the SMs in CTAs are best, as splits of 8, 4, 2 or none, with at least 8 tiles
             # (128 keys) a split; 8 warps a CTA, except that many clusters of 8 such CTAs do not find room
             # side by side (batch 8: 4 warps 1.19 ms a step, 8 warps 1.32 ms).  The same choices were the best or
             # within 1 % of it at context 8k (batch 2 and 8).
             base = entries * self.num_kv_heads
+            most = (sms * 7) // 8
             nsplit = 1
             for n in (8, 4, 2):
-                if base * n <= 128 and n <= max(1, max_tiles // 8):
+                if base * n <= most and n <= max(1, max_tiles // 8):
                     nsplit = n
                     break
-            warps = 4 if (nsplit == 8 and base * nsplit > 64) else 8
+            warps = 4 if (nsplit == 8 and base * nsplit > most // 2) else 8
             return entries, nsplit, True, warps
         blocks = entries * ((group + 15) // 16)
         ctas = blocks * self.num_kv_heads
         # attn_mma: one wave of CTAs at most, and at least 8 tiles (128 keys) a split: with less, merging the
         # splits costs more than the split saves.  The splits of a row block form a thread-block cluster
         # and merge through distributed shared memory: no scratch memory, no counters.
-        want = max(1, min((2 * self.SM_COUNT) // ctas, max(1, max_tiles // 8)))
+        want = max(1, min((2 * sms) // ctas, max(1, max_tiles // 8)))
         # (clusters of 16, the non-portable size, were measured slower than 8: placement costs more
         # than the shorter key ranges save)
         nsplit = 8 if want >= 8 else 4 if want >= 4 else 2 if want >= 2 else 1
         # 8 warps a CTA when the step has very few row blocks: more warps to hide instruction latency
         # behind.  Not beyond half the SMs: 8-warp CTAs fit one an SM, and clusters of 8 of them then
         # no longer find room in one wave
-        warps = 8 if ctas * nsplit <= self.SM_COUNT // 2 and max_tiles >= 16 * nsplit else 4
+        warps = 8 if ctas * nsplit <= sms // 2 and max_tiles >= 16 * nsplit else 4
         return blocks, nsplit, group <= 16, warps
 
     def attend(self, out, qkv, step, cache) -> None:
@@ -191,7 +191,7 @@ class GQAttention(Mixer):
                 key = ("attn_mma", self.num_heads, self.num_kv_heads, self.head_dim)
                 plan = step.scratch.get(key)
                 if plan is None:
-                    plan = step.scratch[key] = self._plan_mma(step, n_single, step.max_kv_len)
+                    plan = step.scratch[key] = self._plan_mma(step, n_single, step.max_kv_len, ops.sm_count(qkv.device))
                 blocks, nsplit, single, warps = plan
                 if self.num_heads // self.num_kv_heads <= 8:
                     # keys on the M side, the group's heads on the N side of the MMA: half the work a tile

@@ -47,11 +47,17 @@ class TensorDecl:
 
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """Per-token keys and values in pages.  Planes with equal needs share a cache group."""
+    """Per-token memory in pages: a key plane and a value plane.  Planes with equal needs share a cache group.
+
+    The two planes may have different widths (``value_head_dim``; None: as wide as the keys), and a mixer
+    that keeps one vector per token only (a latent that serves as key and value) asks for
+    ``value_head_dim=0``: its group then has no value plane at all.
+    """
 
     num_kv_heads: int
-    head_dim: int
-    window: Optional[int] = None   # None: every earlier position stays readable
+    head_dim: int                          # width of a key
+    window: Optional[int] = None           # None: every earlier position stays readable
+    value_head_dim: Optional[int] = None   # width of a value; None: head_dim; 0: no value plane
 
 
 @dataclass(frozen=True)
@@ -123,7 +129,23 @@ class PositionEncoding(Part):
 
 
 class StepView:
-    """What a part may know about the step that is running.  See engine/batch.py."""
+    """What a part may know about the step that is running (``engine/batch.py`` fills it in).
+
+    On the device, valid in every step, captured in a CUDA graph or not (int32 tensors):
+      ``token_ids [tokens]``, ``positions [tokens]`` (place of each token in its request),
+      ``token_req [tokens]`` (entry of each token), ``cu_q [entries + 1]`` (first token of each entry),
+      ``ctx_len [entries]`` (tokens of the request cached before this step), ``req_slot [entries]``
+      (the request's slot: the row of its block table and of its state record; -1 marks a padding entry,
+      which a part skips or gives a defined output), ``status [1]`` (error word).
+    On the host: ``num_tokens``, ``num_entries`` (padding included), ``num_single`` (the leading entries
+    that bring exactly one token: single-token entries always come first), ``max_kv_len``, ``scratch`` (a
+    dict that lives as long as the step, for plans shared by all layers).
+    Only in steps that are not captured: ``entries`` (the host's list of entries, with their tokens) and
+    ``entry_ctx``.  A step made of single-token entries only may be captured once and replayed with other
+    contents of the device arrays: then ``captured`` is true, the arrays are padded to the bucket's size,
+    and whatever a part does must depend on the device arrays alone: no host list, no ``.item()``, no
+    shape that depends on the step's contents.  A portion of several tokens is never captured.
+    """
 
 
 class Mixer(Part):
@@ -141,8 +163,19 @@ class Mixer(Part):
     accumulates = False
 
     def forward(self, x: torch.Tensor, step: "StepView", cache: Any) -> torch.Tensor:
-        """x [tokens, hidden] -> [tokens, hidden].  ``cache`` is the view of this run-step's plane."""
+        """x [tokens, hidden] -> [tokens, hidden].  ``cache`` is the view of this run-step's plane.
+
+        The result may also be float32 partial sums [parts, tokens, hidden] of a last product that was
+        split over its inner dimension: ``Norm.add_forward`` adds them up with the residual; a block that
+        does anything else with the result passes it through ``whole_output`` first."""
         raise NotImplementedError
+
+
+def whole_output(out: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """A part's output as one [tokens, hidden] tensor of ``dtype`` (partial sums added up)."""
+    if out.dim() == 3:
+        return out.sum(0).to(dtype)
+    return out
 
 
 class FeedForward(Part):
@@ -154,25 +187,32 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    """Arrangement of a mixer, a feed-forward and their norms.
+    """An arrangement of parts in a layer.
 
-    ``forward`` gets the residual stream ``h`` and a pending ``delta`` that has
-    not been added to it yet (so that the sum can be fused into the next norm)
-    and returns the same pair.
+    ``roles`` names the parts a block kind is made of and the family each is built from; the layer's
+    ``LayerSpec.parts`` gives a ``PartSpec`` for every role.  Every built part is also an attribute of the
+    block under its role's name.  ``forward`` gets the residual stream ``h``, a pending ``delta`` that has not
+    been added to it yet (so that the sum can be fused into the next norm), and ``caches``: for every role
+    of the mixer family, the view of that mixer's cache plane in this run-step (None if it keeps nothing).
+    It returns ``(h, delta)`` again.
     """
 
     kind_family = "block"
+    roles: Mapping[str, str] = {}      # role -> family ("mixer", "feed_forward", "norm")
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
-        self.mixer = mixer
-        self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+    def __init__(self, parts: Mapping[str, Part]):
+        self.named: Dict[str, Part] = dict(parts)
+        for role, part in self.named.items():
+            setattr(self, role, part)
 
     def parts(self) -> List[Part]:
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        return [self.named[role] for role in self.roles]
 
-    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], step: "StepView", cache: Any):
+    def mixers(self) -> List[Tuple[str, "Mixer"]]:
+        """The block's mixers with their roles, in the order of ``roles``."""
+        return [(role, self.named[role]) for role, family in self.roles.items() if family == "mixer"]
+
+    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], step: "StepView", caches: Mapping[str, Any]):
         raise NotImplementedError
 
 

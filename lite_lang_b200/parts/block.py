@@ -11,7 +11,10 @@ from .base import Block, register_part
 
 
 class PreNormBlock(Block):
-    def forward(self, h, delta, step, cache):
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+
+    def forward(self, h, delta, step, caches):
+        cache = caches["mixer"]
         x = self.mixer_norm.add_forward(h, delta)
         # a part that can add its output to h in its last product (portions of prompts) returns None
         a = (self.mixer.forward(x, step, cache, residual=h) if self.mixer.accumulates

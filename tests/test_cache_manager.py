@@ -165,3 +165,48 @@ def test_random_orders_keep_the_invariants(seed, num_pages, window):
     m.check_invariants()
     assert m.num_free_pages(0) == num_pages and m.num_free_pages(1) == num_pages
     assert m.num_free_slots == 4
+
+
+def test_groups_may_have_different_page_counts_and_every_group_is_asked():
+    """A group with a window needs few pages; the most a request may grow to is what every group can take."""
+    groups = [PagedGroupSpec(2, 16, None, 2), PagedGroupSpec(2, 16, 8, 1)]
+    m = CacheManager(groups, [10, 4], 4, 4, 64)
+    assert m.capacity_tokens() == 40                    # the group that keeps every position sets it
+    s = m.open()
+    assert m.max_reservable(s) == 16                    # the windowed group has 4 pages
+    assert not m.reserve(s, 17) and m.reserve(s, 16)
+    m.advance(s, 16)                                    # the window is 8: pages of positions < 9 go back
+    assert m.pages_of(1, s)[:2] == [-1, -1] and m.num_free_pages(1) == 2
+    assert m.max_reservable(s) == 24                    # 4 logical pages so far + 2 free
+    assert m.reserve(s, 24)
+    m.advance(s, 24)
+    assert m.max_reservable(s) == 32
+    # a request of 40 tokens fits alone (in steps of 4 tokens the windowed group needs 4 pages), one of 41 does not
+    assert m.can_ever_hold(40, step_tokens=4) and not m.can_ever_hold(44, step_tokens=4)
+    assert not m.can_ever_hold(40, step_tokens=12)      # 8 + 12 tokens of window and step need 6 pages
+    m.check_invariants()
+    only_windows = CacheManager([PagedGroupSpec(1, 8, 8, 1)], [9], 4, 4, 64)
+    assert only_windows.capacity_tokens() == (9 // 4) * 64     # requests whose windows fit, times the longest
+
+
+def test_pages_are_shared_out_from_a_budget_of_bytes():
+    from lite_lang_b200.cache.sizing import page_bytes, plan_pages, state_bytes
+    full = PagedGroupSpec(2, 16, None, 3)                      # keys and values 16 wide, 3 planes
+    narrow = PagedGroupSpec(2, 16, None, 1, value_head_dim=8)  # values half as wide as the keys
+    latent = PagedGroupSpec(1, 24, None, 1, value_head_dim=0)  # one vector a token, no value plane
+    windowed = PagedGroupSpec(2, 16, 8, 2)
+    state = StateGroupSpec((5, 3), "float32", 2)
+    assert page_bytes(full, 4, 2) == 3 * 2 * 4 * 32 * 2
+    assert page_bytes(narrow, 4, 2) == 2 * 4 * 24 * 2 and page_bytes(latent, 4, 2) == 1 * 4 * 24 * 2
+    assert state_bytes(state, 4, 2) == 2 * 4 * 15 * 4
+    # without a window every group gets the same number of pages, and the state records come off the budget
+    budget = 100 * (page_bytes(full, 4, 2) + page_bytes(narrow, 4, 2)) + state_bytes(state, 4, 2) + 7
+    assert plan_pages([full, state, narrow], budget, 4, 2, 4, 10 ** 6, 8) == [100, 100]
+    # a windowed group stops at what its request slots can ever use; the others get what that leaves
+    cap = 4 * windowed.pages_a_request_needs(10 ** 6, 4, 8)    # 4 slots x (ceil((8 + 8) / 4) + 1) pages
+    assert cap == 20
+    budget = 100 * page_bytes(full, 4, 2) + cap * page_bytes(windowed, 4, 2)
+    assert plan_pages([full, windowed], budget, 4, 2, 4, 10 ** 6, 8) == [100, 20]
+    # nobody gets more than every slot at full length needs; never fewer than one page
+    assert plan_pages([full], 10 ** 12, 4, 2, 4, 40, 8) == [40]
+    assert plan_pages([full, windowed], 10, 4, 2, 4, 40, 8) == [1, 1]

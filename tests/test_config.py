@@ -47,13 +47,14 @@ def test_model_spec_carries_constants_as_parameters():
     cfg = config_from_dict(TINY["C"]["config"])
     spec = cfg.model_spec()
     assert len(spec.layers) == 4 and [s.layer for s in spec.order] == [0, 1, 2, 3]
-    m0, m1 = spec.layers[0].mixer, spec.layers[1].mixer
+    m0, m1 = spec.layers[0].parts["mixer"], spec.layers[1].parts["mixer"]
     assert m0.kind == "gqa_attention" and m0.params["window"] is None and m1.params["window"] == 40
     assert m0.params["head_dim"] == 64 and m0.params["num_kv_heads"] == 2
     assert m0.params["position"].params["theta"] == 50000.0
-    assert spec.layers[0].mixer_norm.params["eps"] == 3e-6
-    assert spec.layers[2].feed_forward.params["intermediate_size"] == 208
+    assert spec.layers[0].parts["mixer_norm"].params["eps"] == 3e-6
+    assert spec.layers[2].parts["feed_forward"].params["intermediate_size"] == 208
     assert spec.head.params["tied_to"] is None
+    assert sorted(spec.layers[0].parts) == ["feed_forward", "feed_forward_norm", "mixer", "mixer_norm"]
     specA = config_from_dict(TINY["A"]["config"]).model_spec()
     assert specA.head.params["tied_to"] == "model.embed_tokens.weight"
 

@@ -287,3 +287,52 @@ def test_command_line():
     assert out["outputs"][0] == P.greedy_generate(cfg, w, prompt, 5)
     bad = subprocess.run(cmd + ["--tp", "2"], capture_output=True, text=True, cwd=ROOT, timeout=600)
     assert bad.returncode != 0 and "tp" in (bad.stderr + bad.stdout)
+
+
+def _write_word_tokenizer(folder, vocab_size):
+    """A word-level tokenizer made on the spot (no download): word ``w<i>`` is token i, token 0 is unknown."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    vocab = {"[UNK]": 0}
+    for i in range(1, vocab_size):
+        vocab[f"w{i}"] = i
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="[UNK]"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tok.save(os.path.join(folder, "tokenizer.json"))
+    with open(os.path.join(folder, "tokenizer_config.json"), "w") as fh:
+        json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "unk_token": "[UNK]"}, fh)
+
+
+def test_text_prompts_go_through_the_folders_tokenizer():
+    """Text in, text out (the reference tokenizes every request: litelang/scheduler/tokenizer/tokenizer.py:4-31);
+    here the tokenizer is loaded only when a prompt is text."""
+    try:
+        import tokenizers  # noqa: F401
+        from transformers import AutoTokenizer  # noqa: F401
+    except ImportError:
+        pytest.skip("text prompts need the transformers and tokenizers packages")
+    from lite_lang_b200 import SamplingParams
+    folder = make_model_folder("A", scales={"matrix": 0.08})
+    cfg, w = P.read_model_folder(folder)
+    _write_word_tokenizer(folder, cfg["vocab_size"])
+    ids = [t or 1 for t in random_tokens(7, cfg["vocab_size"], 21)]          # (token 0 is the unknown word)
+    text = " ".join(f"w{t}" for t in ids)
+    eng = engine(folder, "float32", "A")
+    assert eng._tokenizer is None                       # not loaded before a text prompt asks for it
+    sp = SamplingParams(temperature=0.0, max_new_tokens=5, ignore_eos=True)
+    out_ids = eng.generate([ids], sp)[0]
+    assert eng._tokenizer is None
+    out_text = eng.generate_text([text], sp)[0]
+    assert eng._tokenizer is not None
+    want = P.greedy_generate(cfg, w, ids, 5)
+    _assert_greedy_or_near_tie(cfg, w, ids, out_ids, 1e-4)
+    assert out_text == eng.tokenizer().decode(out_ids)
+    if out_ids == want:
+        assert out_text.split() == [("[UNK]" if t == 0 else f"w{t}") for t in want]
+    # the command line with --prompt TEXT
+    cmd = [sys.executable, "-m", "lite_lang_b200.cli", "--model_path", folder, "--prompt", text, "--dtype", "fp32",
+           "--max_output_length", "5", "--page_size", "4", "--num_pages", "32", "--max_batch_size", "2",
+           "--temperature", "0", "--ignore_eos"]
+    res = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    out = json.loads(res.stdout.strip().splitlines()[-1])
+    assert out["outputs"][0] == out_ids and out["texts"][0] == out_text

@@ -872,9 +872,30 @@ def test_gemm_pair_refuses_what_it_cannot_do():
         ops.gemm_pair(x[:, :64], w[:, :64].contiguous(), torch.empty(256, 128, dtype=torch.float32, device=dev()))
 
 
+def _assert_qkv_equals_the_plain_formulas(x, w, bias, pos, slots, q, kc, vc, nh, nkv, hd, ps, theta):
+    """q, and the cache rows of the tokens that have a slot, against projection with bias (P.linear) and
+    half-split rotation of q and k (P.rope_tables, P.apply_rope) in float32."""
+    m = x.shape[0]
+    qkv = P.linear(x.float().cpu(), w.float().cpu(), None if bias is None else bias.float().cpu())
+    cos, sin = P.rope_tables(hd, theta, pos.cpu())
+    q_ref = P.apply_rope(qkv[:, :nh * hd].reshape(m, nh, hd), cos, sin).reshape(m, nh * hd)
+    k_ref = P.apply_rope(qkv[:, nh * hd:(nh + nkv) * hd].reshape(m, nkv, hd), cos, sin)
+    v_ref = qkv[:, (nh + nkv) * hd:].reshape(m, nkv, hd)
+    scale = float(qkv.abs().max())
+    assert float((q.float().cpu() - q_ref).abs().max()) / scale <= tol(torch.bfloat16), "q against the plain formulas"
+    if kc is None:
+        return
+    sl = slots.cpu().long()
+    has = sl >= 0
+    k_got = kc.float().cpu()[sl[has] // ps, :, sl[has] % ps]          # [tokens with a slot, nkv, hd]
+    v_got = vc.float().cpu()[sl[has] // ps, :, sl[has] % ps]
+    assert float((k_got - k_ref[has]).abs().max()) / scale <= tol(torch.bfloat16), "cached keys against the plain formulas"
+    assert float((v_got - v_ref[has]).abs().max()) / scale <= tol(torch.bfloat16), "cached values against the plain formulas"
+
+
 @pytest.mark.parametrize("m,hidden,nh,nkv,hd,ps", [(8, 1536, 12, 2, 128, 16), (1, 256, 3, 1, 64, 32), (19, 512, 4, 4, 32, 16),
                                                    (32, 768, 6, 2, 128, 64)])
-def test_gemm_stream_qkv_rope_equals_the_three_kernels_it_replaces(m, hidden, nh, nkv, hd, ps):
+def test_gemm_stream_qkv_rope_equals_the_plain_formulas_and_the_three_kernels_it_replaces(m, hidden, nh, nkv, hd, ps):
     from lite_lang_b200 import ops
     from lite_lang_b200.parts.rope import rope_table
     g = torch.Generator().manual_seed(30)
@@ -906,11 +927,12 @@ def test_gemm_stream_qkv_rope_equals_the_three_kernels_it_replaces(m, hidden, nh
         err = float((got.float() - want.float()).abs().max()) / scale
         assert err <= 1.6e-2, (what, err)       # same roundings; only the order of the float32 sums differs
     assert float((kc.float().abs().sum(dim=(1, 3)) > 0).sum()) == float((kc_ref.float().abs().sum(dim=(1, 3)) > 0).sum())
+    _assert_qkv_equals_the_plain_formulas(x, w, bias, pos, slots, q, kc, vc, nh, nkv, hd, ps, 10000.0)
 
 
 @pytest.mark.parametrize("m,hidden,nh,nkv,hd,ps", [(2048, 1536, 12, 2, 128, 16), (300, 264, 3, 1, 64, 32),
                                                    (257, 512, 5, 5, 64, 16), (520, 328, 2, 1, 256, 64), (1, 64, 1, 1, 128, 16)])
-def test_gemm_pair_qkv_rope_equals_the_two_kernels_it_replaces(m, hidden, nh, nkv, hd, ps):
+def test_gemm_pair_qkv_rope_equals_the_plain_formulas_and_the_two_kernels_it_replaces(m, hidden, nh, nkv, hd, ps):
     from lite_lang_b200 import ops
     from lite_lang_b200.parts.rope import rope_table
     g = torch.Generator().manual_seed(31)
@@ -944,12 +966,14 @@ def test_gemm_pair_qkv_rope_equals_the_two_kernels_it_replaces(m, hidden, nh, nk
     assert bool((q[m:] == 7).all()) and bool((q[:, nh * hd:] == 7).all())
     written = lambda c: c.float().abs().sum(dim=(1, 3)) > 0
     assert bool((written(kc) == written(kc_ref)).all()) and bool((written(vc) == written(vc_ref)).all())
+    _assert_qkv_equals_the_plain_formulas(x, w, bias, pos, slots, q[:m, :nh * hd], kc, vc, nh, nkv, hd, ps, 10000.0)
     # no bias, no cache write: q only
     q2 = torch.empty(m, nh * hd, dtype=torch.bfloat16, device=d)
     ops.gemm_pair_qkv_rope(q2, x, w, None, pos, table, nh, nkv, hd, None, None, None, ps, status)
     ref2 = torch.mm(x, w.t())
     ops.bias_rope_store(ref2, None, pos, table, nh, nkv, hd, None, None, None, ps, status)
     assert float((q2.float() - ref2[:, :nh * hd].float()).abs().max()) / scale <= 1.6e-2
+    _assert_qkv_equals_the_plain_formulas(x, w, None, pos, None, q2, None, None, nh, nkv, hd, ps, 10000.0)
     # a position outside the table is reported
     bad = pos.clone()
     bad[0] = max_pos

@@ -102,9 +102,9 @@ def _spec(order, mixers=None, hidden=48, layers=2, ffns=None):
         p = f"model.layers.{i}."
         mixer = mixers[i](p) if mixers else _attention_spec(p, hidden, 4, 2, 16)
         ffn = ffns[i](p) if ffns else PartSpec("gated_mlp", {"hidden_size": hidden, "intermediate_size": 80}, p + "mlp.")
-        ls.append(LayerSpec("pre_norm", mixer, ffn,
-                            PartSpec("rms_norm", norm, p + "input_layernorm."),
-                            PartSpec("rms_norm", norm, p + "post_attention_layernorm.")))
+        ls.append(LayerSpec("pre_norm", {"mixer": mixer, "feed_forward": ffn,
+                                         "mixer_norm": PartSpec("rms_norm", norm, p + "input_layernorm."),
+                                         "feed_forward_norm": PartSpec("rms_norm", norm, p + "post_attention_layernorm.")}))
     return ModelSpec("Test", hidden, 97, 256,
                      PartSpec("token_embedding", {"vocab_size": 97, "hidden_size": hidden}, "model.embed_tokens."),
                      tuple(ls), tuple(order), PartSpec("rms_norm", norm, "model.norm."),
@@ -246,6 +246,16 @@ def test_toy_mixer_with_state_needs_no_change_to_the_framework():
             return StateNeed((self.hidden,), "float32")
 
         def forward(self, x, step, cache):
+            if step.num_single == step.num_entries:
+                # single tokens only: from the step's device arrays alone, so that the step may be captured
+                # and replayed (token i belongs to entry i; a slot of -1 marks a padding entry)
+                slot = step.req_slot.long()
+                live = (slot >= 0).unsqueeze(1)
+                idx = slot.clamp(min=0)
+                s_old = cache.state[idx]
+                s_new = self.decay * s_old + x.float()
+                cache.state.index_add_(0, idx, torch.where(live, s_new - s_old, torch.zeros_like(s_new)))
+                return torch.where(live, s_new @ self.w.float().t(), torch.zeros_like(s_new)).to(x.dtype)
             out = torch.empty_like(x)
             t = 0
             for e in step.entries:                      # portions of a request arrive in order
@@ -305,6 +315,25 @@ def test_toy_mixer_with_state_needs_no_change_to_the_framework():
     assert runner.reserve(a, 10) and runner.reserve(b, T)
     out = runner.step([StepEntry(a, toks[:10], (9,)), StepEntry(b, toks, (T - 1,))]).float().cpu().numpy()
     assert rel_err(out, ref[[9, T - 1]]) <= 1e-4
+
+    # the same model with captured decode steps: a portion each, then single tokens side by side, replayed
+    # from CUDA graphs, in which the mixer sees the device arrays only (padding entries included: 3 entries
+    # in a bucket of 4 at first, then 2 and 1 as requests end)
+    model, mgr, runner, w = _build_runner(cfg.model_spec(), torch.float32, graphs=True)
+    slots = [mgr.open() for _ in range(3)]
+    starts = [9, 4, 14]
+    assert all(runner.reserve(s, n) for s, n in zip(slots, starts))
+    runner.step([StepEntry(s, toks[:n], ()) for s, n in zip(slots, starts)])
+    at = list(starts)
+    while any(n < T for n in at):
+        live = [i for i in range(3) if at[i] < T]
+        assert all(runner.reserve(slots[i], 1) for i in live)
+        out = runner.step([StepEntry(slots[i], [toks[at[i]]], (0,)) for i in live]).float().cpu().numpy()
+        assert rel_err(out, ref[[at[i] for i in live]]) <= 1e-4, at
+        for i in live:
+            at[i] += 1
+    runner.check_status()
+    assert runner.graph_replays >= T - 4 and sorted(runner._graphs) == [1, 2, 4]
 
 
 # ---------------------------------------------------------------------------
@@ -425,3 +454,124 @@ def test_toy_routed_feed_forward_and_another_position_encoding_need_no_change_to
     whole, cut = _run_whole_and_cut(runner, mgr, toks)
     assert rel_err(whole, ref) <= 1e-4 and rel_err(cut, ref) <= 1e-4
     assert len({int(e) for e in idx.flatten()}) >= 3          # the routing really spreads the tokens
+
+
+# ---------------------------------------------------------------------------
+# a toy block with a norm after its mixer, and a toy mixer whose values are half as wide as its keys
+# ---------------------------------------------------------------------------
+
+def test_toy_block_with_a_third_norm_and_toy_mixer_with_narrow_values_need_no_change_to_the_framework():
+    """Layer 0 is arranged by a block kind of this file that has five parts (a norm after the mixer as well as
+    before it); layer 1's mixer, also of this file, keeps keys of 16 and values of 8 numbers a head in pages
+    of its own.  The framework builds both from the spec, gives the mixer a cache group with planes of those
+    widths, and steps them."""
+    from lite_lang_b200.config import LayerSpec, ModelSpec, PartSpec, RunStep
+    from lite_lang_b200.parts import Block, Mixer, PagedKVNeed, TensorDecl, register_part, whole_output
+
+    H, NH, NKV, HK, HV = 48, 4, 2, 16, 8
+
+    class SandwichBlock(Block):
+        """h += post_norm(mixer(norm(h))); h += feed_forward(norm(h))."""
+        roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm",
+                 "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+
+        def forward(self, h, delta, step, caches):
+            x = self.mixer_norm.add_forward(h, delta)
+            a = whole_output(self.mixer.forward(x, step, caches["mixer"]), h.dtype)
+            a = self.mixer_post_norm.forward(a)
+            x = self.feed_forward_norm.add_forward(h, a)
+            return h, self.feed_forward.forward(x, step)
+
+    class NarrowValueAttention(Mixer):
+        """Causal attention without position encoding; keys HK wide, values HV wide, in the paged cache."""
+
+        def tensors(self):
+            return {"q.weight": TensorDecl((NH * HK, H)), "k.weight": TensorDecl((NKV * HK, H)),
+                    "v.weight": TensorDecl((NKV * HV, H)), "o.weight": TensorDecl((H, NH * HV))}
+
+        def load(self, fetch, dtype, device):
+            self.w = {n: fetch(n + ".weight").to(dtype).to(device) for n in "qkvo"}
+
+        def cache_need(self):
+            return PagedKVNeed(NKV, HK, None, value_head_dim=HV)
+
+        def forward(self, x, step, cache):
+            T, ps = x.shape[0], cache.page_size
+            q = (x @ self.w["q"].t()).view(T, NH, HK)
+            k = (x @ self.w["k"].t()).view(T, NKV, HK)
+            v = (x @ self.w["v"].t()).view(T, NKV, HV)
+            where = cache.slot_map.long()
+            cache.k[where // ps, :, where % ps] = k          # pages are [page, kv head, place, width]
+            cache.v[where // ps, :, where % ps] = v
+            out = torch.empty(T, NH * HV, dtype=x.dtype, device=x.device)
+            t = 0
+            for e, ctx in zip(step.entries, step.entry_ctx):
+                n, total = len(e.tokens), ctx + len(e.tokens)
+                pages = cache.block_table[e.slot, :(total + ps - 1) // ps].long()
+                keys = cache.k[pages].transpose(1, 2).reshape(-1, NKV, HK)[:total].float()
+                vals = cache.v[pages].transpose(1, 2).reshape(-1, NKV, HV)[:total].float()
+                for a in range(NH):
+                    g = a // (NH // NKV)
+                    sc = (q[t:t + n, a].float() @ keys[:, g].t()) * HK ** -0.5
+                    seen = torch.arange(total, device=x.device)[None, :] <= (ctx + torch.arange(n, device=x.device))[:, None]
+                    pr = torch.softmax(sc.masked_fill(~seen, float("-inf")), dim=-1)
+                    out[t:t + n, a * HV:(a + 1) * HV] = (pr @ vals[:, g]).to(x.dtype)
+                t += n
+            return out @ self.w["o"].t()
+
+    register_part("block", "toy_sandwich", SandwichBlock)
+    register_part("mixer", "toy_narrow_values", NarrowValueAttention)
+
+    norm = {"hidden_size": H, "eps": 1e-6}
+    p0, p1 = "model.layers.0.", "model.layers.1."
+    layers = (
+        LayerSpec("toy_sandwich", {
+            "mixer": _attention_spec(p0, H, 4, 2, 16), "mixer_norm": PartSpec("rms_norm", norm, p0 + "input_layernorm."),
+            "mixer_post_norm": PartSpec("rms_norm", norm, p0 + "post_mixer_layernorm."),
+            "feed_forward_norm": PartSpec("rms_norm", norm, p0 + "post_attention_layernorm."),
+            "feed_forward": PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": 80}, p0 + "mlp.")}),
+        LayerSpec("pre_norm", {
+            "mixer": PartSpec("toy_narrow_values", {}, p1 + "narrow."),
+            "mixer_norm": PartSpec("rms_norm", norm, p1 + "input_layernorm."),
+            "feed_forward_norm": PartSpec("rms_norm", norm, p1 + "post_attention_layernorm."),
+            "feed_forward": PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": 80}, p1 + "mlp.")}),
+    )
+    base = _spec([RunStep(0), RunStep(1)], hidden=H)
+    spec = ModelSpec("Test", H, 97, 256, base.embedding, layers, (RunStep(0), RunStep(1)), base.final_norm, base.head)
+    model, mgr, runner, w = _build_runner(spec, torch.float32)
+    assert "model.layers.0.post_mixer_layernorm.weight" in model.declared_tensors()
+    narrow = model.cache_groups[1]
+    assert (narrow.head_dim, narrow.value_dim) == (HK, HV)
+    assert runner.storage.k[1].shape[-1] == HK and runner.storage.v[1].shape[-1] == HV
+    with pytest.raises(ValueError, match="missing \\['mixer_post_norm'\\]"):
+        from lite_lang_b200.engine.model import CausalLM
+        CausalLM(ModelSpec("Test", H, 97, 256, base.embedding,
+                           (LayerSpec("toy_sandwich", dict(layers[1].parts)),), (RunStep(0),), base.final_norm, base.head))
+
+    toks = [int(t) for t in np.random.default_rng(6).integers(0, 97, 27)]
+    T = len(toks)
+    cfgd = {"num_attention_heads": 4, "num_key_value_heads": 2, "hidden_size": H, "head_dim": 16,
+            "rope_theta": 10000.0, "rms_norm_eps": 1e-6}
+    h = P.embedding(w["model.embed_tokens.weight"], torch.tensor(toks))
+    x = P.rms_norm(h, w[p0 + "input_layernorm.weight"], 1e-6)
+    a = P.attention_block(x, torch.arange(T), w, p0 + "self_attn.", cfgd, None)
+    h = h + P.rms_norm(a, w[p0 + "post_mixer_layernorm.weight"], 1e-6)
+    x = P.rms_norm(h, w[p0 + "post_attention_layernorm.weight"], 1e-6)
+    h = h + P.gated_mlp(x, w[p0 + "mlp.gate_proj.weight"], w[p0 + "mlp.up_proj.weight"], w[p0 + "mlp.down_proj.weight"])
+    x = P.rms_norm(h, w[p1 + "input_layernorm.weight"], 1e-6)
+    q = P.linear(x, w[p1 + "narrow.q.weight"]).view(T, NH, HK)
+    k = P.linear(x, w[p1 + "narrow.k.weight"]).view(T, NKV, HK)
+    v = P.linear(x, w[p1 + "narrow.v.weight"]).view(T, NKV, HV)
+    o = torch.zeros(T, NH, HV)
+    causal = torch.arange(T)[None, :] <= torch.arange(T)[:, None]
+    for a_ in range(NH):
+        g = a_ // (NH // NKV)
+        sc = (q[:, a_].double() @ k[:, g].double().t()) * HK ** -0.5
+        o[:, a_] = (torch.softmax(sc.masked_fill(~causal, float("-inf")), dim=-1) @ v[:, g].double()).float()
+    h = h + P.linear(o.reshape(T, NH * HV), w[p1 + "narrow.o.weight"])
+    x = P.rms_norm(h, w[p1 + "post_attention_layernorm.weight"], 1e-6)
+    h = h + P.gated_mlp(x, w[p1 + "mlp.gate_proj.weight"], w[p1 + "mlp.up_proj.weight"], w[p1 + "mlp.down_proj.weight"])
+    ref = P.linear(P.rms_norm(h, w["model.norm.weight"], 1e-6), w["lm_head.weight"]).numpy()
+
+    whole, cut = _run_whole_and_cut(runner, mgr, toks)
+    assert rel_err(whole, ref) <= 1e-4 and rel_err(cut, ref) <= 1e-4

@@ -384,3 +384,22 @@ def test_prefill_attention_plan_fits_the_ctas_to_the_sms():
     assert ops.attn_prefill_tc_plan([], 6, None, 2, 296) == (0, 1, 1 << 20)
     # a window shortens the chains
     assert ops.attn_prefill_tc_plan([(4096, 64)], 4, 256, 2, 296)[2] >= 4
+
+
+def test_a_portion_shrinks_to_what_every_cache_group_can_take():
+    """Two groups, the windowed one with few pages: a long prompt runs in portions that the smaller pool
+    can hold, the window's pages come back after every step, and the prompt gets through."""
+    groups = [PagedGroupSpec(1, 16, None, 1), PagedGroupSpec(1, 16, 8, 1)]
+    m = CacheManager(groups, [16, 5], 4, 4, 64)
+    s = Scheduler(m, 32, max_reqs=100, busy_scale=0.6)
+    assert s.capacity_tokens == 64
+    a = req(0, 50, 3)
+    s.add(a)
+    counts = []
+    while s.has_work():
+        plan, _ = run_step(m, s)
+        counts.append([p.count for p in plan])
+        assert len(counts) < 40
+    assert counts[0] == [20]                      # the windowed group's 5 pages, not the budget of 32
+    assert sum(c[0] for c in counts[:-2]) == 50 and a.finish_reason == "length" and len(a.output) == 3
+    assert m.num_free_pages(0) == 16 and m.num_free_pages(1) == 5

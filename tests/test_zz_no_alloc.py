@@ -5,8 +5,11 @@ that handed all free memory to its own pools at start-up, or a plug-in inside a 
 whose allocator it cannot use.  For them the library exports one C entry point that takes
 its scratch memory from a fixed array inside the library.  This test calls that entry point
 through its exported C symbol, twice in a row, and compares each result with the ordinary
-entry point, which is given scratch memory by the caller.  It also checks that a launch that
-would not fit the built-in array is refused with a message, and that nothing else changed.
+entry point, which is given scratch memory by the caller, and with the plain attention formula.
+That nothing is allocated is read from the driver (cudaMemGetInfo: the free memory of the device
+is the same before and after a call), not from torch's own allocator, which cannot see what a
+library loaded beside it does.  It also checks that a launch that would not fit the built-in array
+is refused with a message, and that nothing else changed.
 
 The file sorts last so that a run that stops at the first failure has run everything else.
 """
@@ -16,12 +19,14 @@ from ctypes import c_float, c_int, c_long, c_void_p
 import pytest
 import torch
 
+from plain import qwen2_plain as P
+
 pytestmark = pytest.mark.gpu
 
 TOO_LARGE = 100001
 
 
-def _case(seed, nh, nkv, hd, ps, lens, q_lens):
+def _case(seed, nh, nkv, hd, ps, lens, q_lens, with_plain=True):
     """Cached keys and values in scattered pages and the step's queries (all bfloat16)."""
     d = torch.device("cuda:0")
     g = torch.Generator().manual_seed(seed)
@@ -39,7 +44,18 @@ def _case(seed, nh, nkv, hd, ps, lens, q_lens):
     cu = [0]
     for ql in q_lens:
         cu.append(cu[-1] + ql)
+    # the plain formula on each request's keys and values, gathered from its pages
+    ref, row = [], 0
+    for i, (l, ql) in enumerate(zip(lens, q_lens) if with_plain else ()):
+        pages = [int(x) for x in bt[i, :(l + ps - 1) // ps]]
+        k = torch.cat([kc[pg].float().cpu().transpose(0, 1) for pg in pages])[:l]      # [l, nkv, hd]
+        v = torch.cat([vc[pg].float().cpu().transpose(0, 1) for pg in pages])[:l]
+        qq = torch.zeros(l, nh, hd)
+        qq[l - ql:] = q[row:row + ql].float().cpu().view(ql, nh, hd)
+        ref.append(P.attention(qq, k, v)[l - ql:].reshape(ql, nh * hd))
+        row += ql
     return dict(q=q, kc=kc, vc=vc, bt=bt.to(d), cu_q=torch.tensor(cu, dtype=torch.int32, device=d),
+                plain=torch.cat(ref) if ref else None,
                 ctx=torch.tensor([l - ql for l, ql in zip(lens, q_lens)], dtype=torch.int32, device=d),
                 slots=torch.arange(n, dtype=torch.int32, device=d),
                 blocks=sum((ql * (nh // nkv) + 15) // 16 for ql in q_lens))
@@ -70,16 +86,24 @@ def test_static_scratch_entry_point_equals_the_ordinary_one():
         counters = torch.zeros(c["blocks"] * nkv, dtype=torch.int32, device=c["q"].device)
         ops.attn_mma(want, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], c["cu_q"], c["ctx"], c["slots"],
                      len(lens), c["blocks"], nh, nkv, hd, ps, None, hd ** -0.5, nsplit, scratch, counters, None)
-        for attempt in range(2):
-            got = torch.full_like(c["q"], 5.0)
-            before = torch.cuda.memory_allocated()
+        outs = [torch.full_like(c["q"], 5.0) for _ in range(3)]
+        # (the first call may load the kernel's code and look up the array's address: it is not measured)
+        assert _call_static(lib, c, outs[0], nh, nkv, hd, ps, nsplit) == 0, lib.ll_attn_mma_static_error()
+        torch.cuda.synchronize()
+        for attempt in (1, 2):
+            got = outs[attempt]
+            free_before, _ = torch.cuda.mem_get_info()
             rc = _call_static(lib, c, got, nh, nkv, hd, ps, nsplit)
             assert rc == 0, lib.ll_attn_mma_static_error()
             torch.cuda.synchronize()
-            assert torch.cuda.memory_allocated() == before
+            free_after, _ = torch.cuda.mem_get_info()
+            assert free_after == free_before, "the device's free memory changed during the call"
             scale = float(want.float().abs().max())
             err = float((got.float() - want.float()).abs().max()) / scale
             assert err <= 1.6e-2, (seed, attempt, err)       # the tolerance of the kernel tests for bfloat16
+            plain = c["plain"]
+            err = float((got.float().cpu() - plain).abs().max()) / float(plain.abs().max())
+            assert err <= 1.6e-2, (seed, attempt, err)
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
@@ -88,7 +112,7 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     lib = ctypes.CDLL(build_library("attn_mma_static"))
     lib.ll_attn_mma_static_error.restype = ctypes.c_char_p
     nh, nkv, hd, ps = 12, 2, 128, 16
-    c = _case(33, nh, nkv, hd, ps, [4000] * 8, [1] * 8)
+    c = _case(33, nh, nkv, hd, ps, [4000] * 8, [1] * 8, with_plain=False)
     out = torch.full_like(c["q"], 5.0)
     rc = _call_static(lib, c, out, nh, nkv, hd, ps, 64)       # 8 * 2 * 64 * 16 * 130 floats > 8 MiB
     assert rc == TOO_LARGE
