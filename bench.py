@@ -13,10 +13,13 @@ context of 4,096.  One JSON line is printed:
              steps (index arrays are uploaded every step, tokens are not read back);
   e2e        the same through the Python entry point (scheduler, sampling, token ids
              from the host and back to it every step);
-  prefill    one request of 2,048 tokens in one step, logits of its last token;
+  prefill    one request of 2,048 tokens in one step, logits of its last token: median and minimum over at
+             least 20 repeats (about a second of them), with the SM clock sampled meanwhile;
   roofline   bytes a decode step has to read (every weight once, the cache of the live
              requests) over its time, against the measured copy bandwidth;
-  points     decode at batch 1 and 64.
+  points     decode at batch 1 and 64, on the device and through the entry point; host_ms: what the host
+             spends a step (scheduler, batch, launches) while not waiting for the device;
+  workloads  the two serving workloads named beside the headline configuration, through the scheduler.
 
 A decode step reads about 3.1 GB of weights, far more than the 126 MB L2, so
 iterations need no L2 flush.
@@ -30,6 +33,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -68,14 +72,14 @@ class ClockSampler:
 
     def __init__(self):
         self.proc = None
-        self.path = os.path.join(ROOT, "gpurun_out", "bench_clocks.csv")
+        self.path = None
 
     def start(self):
         try:
-            os.makedirs(os.path.dirname(self.path), exist_ok=True)
-            self.fh = open(self.path, "w")
+            fd, self.path = tempfile.mkstemp(prefix="lite_lang_b200_clocks_", suffix=".csv")
+            self.fh = os.fdopen(fd, "w")
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.fh,
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=self.fh,
                                          stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -92,7 +96,13 @@ class ClockSampler:
         self.fh.close()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in open(self.path):
+        with open(self.path) as fh:
+            lines = fh.readlines()
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        for line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -193,7 +203,9 @@ def device_decode(engine, batch, steps, warmup, sampler_on=True):
 
 
 def e2e_decode(engine, batch, steps, warmup):
-    """The same through Engine.step(): scheduler, sampling, tokens to the host every step."""
+    """The same through Engine.step(): scheduler, sampling, tokens to the host every step.
+    Returns tokens a second, bytes up and down a step, ms a step, and the host's own ms a step (wall clock
+    less the time it waited for the device)."""
     import torch
     from lite_lang_b200 import SamplingParams
 
@@ -205,11 +217,13 @@ def e2e_decode(engine, batch, steps, warmup):
         engine.step()
     torch.cuda.synchronize()
     n0 = sum(len(r.output) for r in reqs)
+    wait0 = engine.host_wait_s
     t0 = time.perf_counter()
     for _ in range(steps):
         engine.step()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    host_ms = (dt - (engine.host_wait_s - wait0)) / steps * 1e3
     n1 = sum(len(r.output) for r in reqs)
     while engine.scheduler.has_work():                      # drain: give the cache back
         for r in list(engine.scheduler.running):
@@ -217,17 +231,20 @@ def e2e_decode(engine, batch, steps, warmup):
         engine.step()
     h2d = engine.runner.single_builder.total * 4
     d2h = engine._result_hosts[0].numel() * 4
-    return (n1 - n0) / dt, h2d, d2h, dt / steps * 1e3
+    return (n1 - n0) / dt, h2d, d2h, dt / steps * 1e3, host_ms
 
 
-def prefill_once(engine, repeats=3):
+def prefill_once(engine, repeats=20, seconds=1.0):
+    """A 2,048-token prompt in one step, again and again: at least ``repeats`` times and for about ``seconds``,
+    after three warm-ups, each timed with CUDA events; the SM clock is sampled meanwhile.  (The step reads
+    3 GB of weights, far more than the L2 holds, so nothing is flushed between repeats.)"""
     import torch
     from lite_lang_b200.engine.batch import StepEntry
 
     m, runner = engine.manager, engine.runner
     prompt = random_prompts(1, PROMPT_LEN, engine.model.spec.vocab_size, 11)[0]
-    best = None
-    for _ in range(repeats + 2):
+
+    def once():
         s = m.open()
         assert runner.reserve(s, PROMPT_LEN)
         torch.cuda.synchronize()
@@ -236,10 +253,19 @@ def prefill_once(engine, repeats=3):
         runner.step([StepEntry(s, prompt, (PROMPT_LEN - 1,))])
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
         m.close(s)
-        best = ms if best is None else min(best, ms)
-    return best
+        return e0.elapsed_time(e1)
+
+    for _ in range(3):
+        once()
+    clocks = ClockSampler()
+    clocks.start()
+    times = []
+    t0 = time.perf_counter()
+    while len(times) < repeats or (time.perf_counter() - t0 < seconds and len(times) < 400):
+        times.append(once())
+    clk = clocks.stop()
+    return {"ms": statistics.median(times), "ms_min": min(times), "repeats": len(times), "clocks": clk}
 
 
 def kernel_times(engine, batch, steps):
@@ -310,21 +336,35 @@ def run_ours(args):
         print(kernel_times(engine, batch, max(4, min(args.steps, 20))))
         return 0
     if args.only == "prefill":
-        ms = prefill_once(engine, repeats=max(1, args.steps))
-        print(json.dumps({"only": "prefill", "layers": layers, "tokens": PROMPT_LEN, "ms": round(ms, 3)}))
+        r = prefill_once(engine, repeats=max(1, args.steps), seconds=0.0)
+        print(json.dumps({"only": "prefill", "layers": layers, "tokens": PROMPT_LEN, "ms": round(r["ms"], 3),
+                          "ms_min": round(r["ms_min"], 3), "repeats": r["repeats"]}))
         return 0
 
-    points = {}
+    points, host_ms = {}, {}
     for b in (1, 64):
         ms, _ = device_decode(engine, b, max(16, args.steps // 4), max(3, args.warmup))
         points[f"decode_b{b}"] = round(b / ms * 1e3, 1)
+        v, _, _, _, hm = e2e_decode(engine, b, max(16, args.steps // 4), max(3, args.warmup))
+        points[f"e2e_b{b}"] = round(v, 1)
+        host_ms[f"b{b}"] = round(hm, 4)
 
-    prefill_ms = prefill_once(engine)
+    pre = prefill_once(engine)
+    prefill_ms = pre["ms"]
     pf = prefill_flops(cfg, PROMPT_LEN)
+    pclk = pre["clocks"]
+    prefill = {"value": round(PROMPT_LEN / prefill_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(prefill_ms, 3),
+               "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "ms_min": round(pre["ms_min"], 3), "repeats": pre["repeats"], "flops": pf,
+               "sm_mhz": pclk.get("sm_mhz"), "sm_max_mhz": pclk.get("sm_max_mhz"), "reasons": pclk.get("reasons")}
+    if pclk.get("sm_mhz") and pclk.get("sm_max_mhz"):
+        # what the median would be at the highest clock, if the time went with the clock alone
+        prefill["ms_at_max_clock"] = round(prefill_ms * pclk["sm_mhz"] / pclk["sm_max_mhz"], 3)
+    if "bf16_tflops_sustained" in pk:
+        prefill["frac_of_sustained"] = round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
 
     clocks = ClockSampler()
     clocks.start()
-    launches0 = kbuild.LAUNCHES
     ms, ctx = device_decode(engine, batch, args.steps, args.warmup)
     clk = clocks.stop()
     bucket = engine.runner._bucket(batch)
@@ -333,7 +373,8 @@ def run_ours(args):
     step_bytes = weight_bytes + batch * ctx * kvb
     achieved = step_bytes / (ms * 1e-3) / 1e9
 
-    e2e_value, h2d, d2h, e2e_ms = e2e_decode(engine, batch, args.steps, args.warmup)
+    e2e_value, h2d, d2h, e2e_ms, hm = e2e_decode(engine, batch, args.steps, args.warmup)
+    host_ms[f"b{batch}"] = round(hm, 4)
 
     out = {
         "metric": "decode tok/s (Qwen2-1.5B shape, 1xB200)", "value": round(value, 1), "unit": "tokens/s",
@@ -351,13 +392,26 @@ def run_ours(args):
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4)},
         "gpu_launches": per_step_kernels * args.steps,
         "gpu_launches_per_step": per_step_kernels,
-        "prefill": {"value": round(PROMPT_LEN / prefill_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(prefill_ms, 3),
-                    "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "step_bytes": int(step_bytes)},
         "points": points,
+        "host_ms_per_step": host_ms,
         "clocks": clk,
     }
+    if not args.no_workloads and not args.layers:
+        # the two serving workloads, each with a model of its own (this one's memory is given back first)
+        del engine
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        out["workloads"] = {}
+        for name in sorted(WORKLOADS):
+            r = workload_result(name, 0)
+            out["workloads"][name] = {k: r[k] for k in ("seconds", "new_tokens_per_s", "all_tokens_per_s", "steps",
+                                                        "preemptions")}
+            gc.collect()
+            torch.cuda.empty_cache()
     print(json.dumps(out))
     return 0
 
@@ -393,7 +447,7 @@ WORKLOADS = {
 }
 
 
-def run_workload(args):
+def workload_result(name, layers_arg):
     """A whole serving workload through Engine.step(): admission, prompts cut into portions of at most 2,048
     tokens a step beside the decode tokens of the others, sampling, finishing.  Wall clock around all of it."""
     import numpy as np
@@ -401,9 +455,9 @@ def run_workload(args):
     from lite_lang_b200 import Engine, EngineConfig, SamplingParams
     from lite_lang_b200.config import config_from_dict
 
-    w = WORKLOADS[args.workload]
+    w = WORKLOADS[name]
     layers_full = w["model"]["num_hidden_layers"]
-    layers = args.layers or layers_full
+    layers = layers_arg or layers_full
     cfg = config_from_dict(dict(w["model"], num_hidden_layers=layers))
     lo, hi = w["prompt"]
     rng = np.random.default_rng(11)
@@ -428,12 +482,16 @@ def run_workload(args):
     dt = time.perf_counter() - t0
     new = sum(len(r.output) for r in reqs)
     st = engine.stats()
-    print(json.dumps({"workload": args.workload, "impl": "ours", "layers": layers, "layers_full": layers_full,
-                      "requests": len(reqs), "prompt_tokens": sum(lengths), "new_tokens": new,
-                      "seconds": round(dt, 3), "steps": steps, "new_tokens_per_s": round(new / dt, 1),
-                      "all_tokens_per_s": round((new + sum(lengths)) / dt, 1),
-                      "preemptions": st.get("preemptions", 0), "graph_replays": st.get("graph_replays", 0),
-                      "dtype": "bf16", "data": "synthetic"}))
+    return {"workload": name, "impl": "ours", "layers": layers, "layers_full": layers_full,
+            "requests": len(reqs), "prompt_tokens": sum(lengths), "new_tokens": new,
+            "seconds": round(dt, 3), "steps": steps, "new_tokens_per_s": round(new / dt, 1),
+            "all_tokens_per_s": round((new + sum(lengths)) / dt, 1),
+            "preemptions": st.get("preemptions", 0), "graph_replays": st.get("graph_replays", 0),
+            "dtype": "bf16", "data": "synthetic"}
+
+
+def run_workload(args):
+    print(json.dumps(workload_result(args.workload, args.layers)))
     return 0
 
 
@@ -452,6 +510,8 @@ def main():
                     help="instead of the headline measurement: a whole serving workload through the scheduler "
                          "(Qwen2.5-3B sizes, 40 requests of 600 + 600 tokens; Qwen2-7B sizes, 64 requests with prompts "
                          "of 128..4096 tokens cut into portions of 2,048 a step, 256 new tokens each)")
+    ap.add_argument("--no-workloads", action="store_true", dest="no_workloads",
+                    help="leave the two serving workloads out of the headline run")
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="with --only decode: another context length than the headline's 2,048 prompt tokens")
     ap.add_argument("--shape", default="", choices=[""] + sorted(WORKLOADS),

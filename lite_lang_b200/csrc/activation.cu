@@ -6,8 +6,8 @@
 
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, long total, int inter) {
-  LL_PDL_WAIT();
   LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
   const long idx0 = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const long step = (long)gridDim.x * blockDim.x;
   for (long idx = idx0; idx < total; idx += step) {
@@ -21,8 +21,8 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, l
 
 // 8 bf16 values a thread; needs inter % 8 == 0.
 __global__ void silu_mul_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restrict__ gu, long total8, int inter8) {
-  LL_PDL_WAIT();
   LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
   const long idx0 = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const long step = (long)gridDim.x * blockDim.x;
   for (long idx = idx0; idx < total8; idx += step) {

@@ -119,6 +119,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   const int g = lane >> 2, c = lane & 3;
   const int e = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   if (e >= p.n_entries) return;
+  LL_PDL_TRIGGER();   // the kernel after this one may move in and fetch its weights while this one works
   // What the step's index arrays say (slot, context length, block table) was uploaded before the step's
   // first kernel and is read before the wait for the kernel before this one; q and the new token's key
   // and value are that kernel's output and are read after it.
@@ -136,9 +137,26 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   const bool bt_cached = nt_split <= AD_BT_CACHE;
   if (bt_cached && slot >= 0)
     for (int i = tid; i < nt_split; i += (NW * 32)) sm_bt[i] = bt[((t_begin + i) * AD_TILE) / p.page_size];
-  LL_PDL_WAIT();
-  LL_PDL_TRIGGER();
   __syncthreads();
+  // The kernel before this one writes the new token's key and value only: every tile but the one that holds
+  // position `pos` was written by earlier steps and may be asked for before that kernel has finished.  Each
+  // lane asks L2 for one of the warp's tiles (K and V, contiguous within a page), so that the tile loop
+  // below meets L2's latency instead of memory's; the last tile is left alone.  Only while the step's keys
+  // and values are a small part of L2 (few requests, where the loop is a chain of latencies; with many, the
+  // loop is bound by bandwidth and L2 could not hold what was asked for).
+  constexpr unsigned TILE_B = AD_TILE * HD * 2;
+  if (slot >= 0 && (long)gridDim.x * gridDim.y * gridDim.z * nt_split * 2 * TILE_B <= (48l << 20)) {
+    for (int t = t_begin + warp + lane * NW; t < t_end; t += 32 * NW) {
+      if (t == t_last) continue;
+      const int key0 = t * AD_TILE;
+      const int page = bt_cached ? sm_bt[t - t_begin] : bt[key0 / p.page_size];
+      if (page < 0 || page >= p.num_pages) continue;
+      const long off = (((long)page * p.nkv + kvh) * p.page_size + (key0 % p.page_size)) * HD;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.k_cache + off), "r"(TILE_B) : "memory");
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.v_cache + off), "r"(TILE_B) : "memory");
+    }
+  }
+  LL_PDL_WAIT();
   // ---- Q^T fragments: thread (g, c) holds head g, dims 32 s + 8 c .. + 7 ----
   uint4 qf[KS];
   {

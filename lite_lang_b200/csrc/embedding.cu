@@ -8,8 +8,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ table,
                                     const int* __restrict__ ids, int hidden, int vocab, int* status) {
-  LL_PDL_WAIT();
   LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = (id >= 0 && id < vocab);
@@ -40,8 +40,8 @@ extern "C" int ll_embed_gather(int dtype, void* out, const void* table, const in
 // result buffer this way.  A feed index outside [0, max_results) leaves ids[i] as the host wrote it.
 __global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ feed, const int* __restrict__ results,
                                    int n, int max_results) {
-  LL_PDL_WAIT();
   LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
     const int f = feed[i];

@@ -16,8 +16,8 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x, con
                                float eps, int hidden, long x_stride, long out_stride) {
   extern __shared__ float row[];
   __shared__ float scratch[32];
-  LL_PDL_WAIT();
   LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
   const int r = blockIdx.x;
   const T* xr = x + (size_t)r * x_stride;
   float ss = 0.f;
@@ -39,8 +39,8 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ out, T* __restrict__ residual
                                    const int* __restrict__ rows, int write_residual) {
   extern __shared__ float row[];
   __shared__ float scratch[32];
-  LL_PDL_WAIT();
   LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
   const int i_out = blockIdx.x;
   const int r = rows ? rows[i_out] : i_out;
   T* res = residual + (size_t)r * hidden;
@@ -86,8 +86,8 @@ add_rmsnorm_bf16x8_kernel(bf16* __restrict__ out, bf16* __restrict__ residual, c
     wa = *reinterpret_cast<const float4*>(w + i0);
     wb = *reinterpret_cast<const float4*>(w + i0 + 4);
   }
-  LL_PDL_WAIT();
   LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
   const int i_out = blockIdx.x;
   const int r = rows ? rows[i_out] : i_out;
   float v[8];

@@ -25,8 +25,8 @@ __global__ void bias_rope_store_kernel(T* __restrict__ qkv, long qkv_stride, con
                                        const int* __restrict__ slot_map, T* __restrict__ k_cache,
                                        T* __restrict__ v_cache, int page_size, long num_slots, int write_q,
                                        int* status) {
-  LL_PDL_WAIT();
   LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
   const int t = blockIdx.x;
   T* row = qkv + (size_t)t * qkv_stride;
   int pos = positions ? positions[t] : 0;
@@ -111,8 +111,8 @@ bias_rope_store_bf16x8_kernel(bf16* __restrict__ qkv, long qkv_stride, const flo
                               const int* __restrict__ positions, const float* __restrict__ cos_sin, int max_pos, int nh,
                               int nkv, int hd, const int* __restrict__ slot_map, bf16* __restrict__ k_cache,
                               bf16* __restrict__ v_cache, int page_size, long num_slots, int* status) {
-  LL_PDL_WAIT();
   LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
   const int t = blockIdx.x;
   bf16* row = qkv + (size_t)t * qkv_stride;
   int pos = positions[t];

@@ -81,8 +81,8 @@ sample_stage1_kernel(const float* __restrict__ logits, long row_stride, const fl
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ float s_sum[32];
-  LL_PDL_WAIT();
   LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
   const int chunk = blockIdx.x, r = blockIdx.y;
   const int c0 = chunk * SM_CHUNK, n = min(SM_CHUNK, vocab - c0);
   const float* row = logits + (size_t)r * row_stride + c0;
@@ -112,8 +112,8 @@ sample_stage2_kernel(const float* __restrict__ logits, long row_stride, const fl
   __shared__ float s_M;
   __shared__ int s_arg, s_chunk;
   __shared__ float s_before, s_target;
-  LL_PDL_WAIT();
   LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
   const int r = blockIdx.x;
   const float* pr = part + (size_t)r * nchunks * 3;
   const float temp = temperature ? temperature[r] : 0.f;

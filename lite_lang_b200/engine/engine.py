@@ -12,6 +12,7 @@ explicit page count, and ``generate`` drives the scheduler to completion.
 from __future__ import annotations
 
 import os
+import time
 from typing import Dict, List, Optional, Sequence, Union
 
 import torch
@@ -95,6 +96,7 @@ class Engine:
         self._result_events = [torch.cuda.Event() for _ in self._result_hosts]
         self._result_turn = 0
         self._ahead: Optional[_Launched] = None
+        self.host_wait_s = 0.0          # seconds the host has spent waiting for steps' results
         self._pipeline = os.environ.get("LITE_LANG_B200_PIPELINE", "1") != "0"
 
     # ------------------------------------------------------------------
@@ -176,7 +178,10 @@ class Engine:
         return _Launched(plan, rows, host, self._result_events[turn])
 
     def _collect(self, launched: "_Launched") -> List[Request]:
-        launched.event.synchronize()
+        if not launched.event.query():
+            t0 = time.perf_counter()
+            launched.event.synchronize()
+            self.host_wait_s += time.perf_counter() - t0
         host = launched.host.numpy()
         if host[-1] != 0:
             self.runner.check_status()
