@@ -130,7 +130,9 @@ def build_engine(layers, max_batch, dtype="bfloat16", model=None):
     ecfg = EngineConfig(dtype=dtype, page_size=16, num_pages=max_batch * pages_per_req + 8,
                         max_batch_size=max_batch, max_input_length=PROMPT_LEN, max_output_length=CONTEXT - PROMPT_LEN,
                         max_model_len=CONTEXT, max_tokens_per_step=2048, cuda_graphs=True, seed=0)
-    return Engine(config=cfg, engine_config=ecfg, random_seed=1234)
+    engine = Engine(config=cfg, engine_config=ecfg, random_seed=1234)
+    engine.runner.capture_all()        # every batch-size bucket's decode step, before anything is timed
+    return engine
 
 
 def random_prompts(n, length, vocab, seed):
@@ -211,7 +213,9 @@ def e2e_decode(engine, batch, steps, warmup):
 
     vocab = engine.model.spec.vocab_size
     prompts = random_prompts(batch, PROMPT_LEN, vocab, 7)
-    sp = SamplingParams(temperature=0.0, max_new_tokens=steps + warmup + 8, ignore_eos=True)
+    # (a prompt is admitted a step: the first request is `batch` tokens ahead of the last, and nobody may end
+    # inside the timed steps)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=steps + warmup + batch + 8, ignore_eos=True)
     reqs = [engine.add_request(p, sp) for p in prompts]
     while any(len(r.output) < 1 + warmup for r in reqs):    # prefill and warm-up decode steps
         engine.step()
