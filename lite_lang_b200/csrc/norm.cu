@@ -153,6 +153,82 @@ add_rmsnorm_bf16x8_kernel(bf16* __restrict__ out, bf16* __restrict__ residual, c
   }
 }
 
+// Many bfloat16 rows (portions of prompts): a warp a row, eight rows a block.  A lane holds every 32nd
+// 16-byte piece of the row in registers (all of them asked for at once, so that a row is a few loads in
+// flight per lane instead of one), the sum of squares goes through the warp's shuffles, nothing through
+// shared memory and there is no block barrier.  Same arithmetic and the same roundings as the kernels
+// above; only the order of the float32 sum of squares differs.  MAXC: pieces a lane holds (rows of up to
+// 256 MAXC values).
+template <int MAXC>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(bf16* __restrict__ out, bf16* __restrict__ residual, const bf16* __restrict__ delta,
+                        const float* __restrict__ w, float eps, int hidden, const int* __restrict__ rows, int n_out,
+                        int write_residual) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const int lane = threadIdx.x & 31;
+  const int i_out = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (i_out >= n_out) return;
+  const int r = rows ? rows[i_out] : i_out;
+  bf16* res = residual + (size_t)r * hidden;
+  uint4 rv[MAXC], dv[MAXC];
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int i0 = (c * 32 + lane) * 8;
+    rv[c] = make_uint4(0u, 0u, 0u, 0u);
+    dv[c] = make_uint4(0u, 0u, 0u, 0u);
+    if (i0 < hidden) {
+      rv[c] = *reinterpret_cast<const uint4*>(res + i0);
+      if (delta) dv[c] = *reinterpret_cast<const uint4*>(delta + (size_t)r * hidden + i0);
+    }
+  }
+  float v[MAXC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int i0 = (c * 32 + lane) * 8;
+    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv[c]);
+    const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv[c]);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(r2[k]);
+      v[c][2 * k] = f.x;
+      v[c][2 * k + 1] = f.y;
+      if (delta) {
+        const float2 g = __bfloat1622float2(d2[k]);
+        v[c][2 * k] = round_to<bf16>(f.x + g.x);
+        v[c][2 * k + 1] = round_to<bf16>(f.y + g.y);
+      }
+    }
+    if (delta && write_residual && i0 < hidden) {
+      uint4 ov;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) o2[k] = __floats2bfloat162_rn(v[c][2 * k], v[c][2 * k + 1]);
+      *reinterpret_cast<uint4*>(res + i0) = ov;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += v[c][k] * v[c][k];
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  bf16* o = out + (size_t)i_out * hidden;
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int i0 = (c * 32 + lane) * 8;
+    if (i0 < hidden) {
+      const float4 wa = __ldg(reinterpret_cast<const float4*>(w + i0)), wb = __ldg(reinterpret_cast<const float4*>(w + i0 + 4));
+      const float ww[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+      uint4 ov;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        o2[k] = __floats2bfloat162_rn(v[c][2 * k] * inv * ww[2 * k], v[c][2 * k + 1] * inv * ww[2 * k + 1]);
+      *reinterpret_cast<uint4*>(o + i0) = ov;
+    }
+  }
+}
+
 static int norm_threads(int hidden) {
   int t = 32;
   while (t < 512 && t * 4 < hidden) t <<= 1;
@@ -181,6 +257,19 @@ extern "C" int ll_add_rmsnorm(int dtype, void* out, void* residual, const void* 
                               int parts, long part_stride, const float* w, float eps, int n_out, int hidden,
                               const int* rows, int write_residual, cudaStream_t stream) {
   if (n_out <= 0) return 0;
+  if (dtype == LL_DTYPE_BF16 && (hidden % 8) == 0 && hidden <= 4096 && partial == nullptr && n_out >= 64) {
+    // many rows: a warp a row
+    const dim3 grid((n_out + 7) / 8);
+#define LL_ROWS_LAUNCH(C)                                                                                          \
+  ll_launch(add_rmsnorm_rows_kernel<C>, grid, dim3(256), 0, stream, (bf16*)out, (bf16*)residual, (const bf16*)delta, \
+            w, eps, hidden, rows, n_out, write_residual)
+    if (hidden <= 512) LL_ROWS_LAUNCH(2);
+    else if (hidden <= 1024) LL_ROWS_LAUNCH(4);
+    else if (hidden <= 2048) LL_ROWS_LAUNCH(8);
+    else LL_ROWS_LAUNCH(16);
+#undef LL_ROWS_LAUNCH
+    return LL_LAUNCH_RESULT();
+  }
   if (dtype == LL_DTYPE_BF16 && (hidden % 8) == 0 && hidden <= 8 * 1024 && (part_stride % 4) == 0) {
     const int threads = ((hidden / 8 + 31) / 32) * 32;
     ll_launch(add_rmsnorm_bf16x8_kernel, dim3(n_out), dim3(threads), 0, stream, (bf16*)out, (bf16*)residual,
