@@ -79,7 +79,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(prefix="lite_lang_b200_clocks_", suffix=".csv")
             self.fh = os.fdopen(fd, "w")
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=self.fh,
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.fh,
                                          stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
