@@ -6,10 +6,11 @@
 //     S^T[16 keys x 8 heads] = K[16 x hd] Q^T[hd x 8],      O^T[hd x 8 heads] += V^T[hd x 16 keys] P^T[16 x 8],
 // which halves the MMAs, the accumulator registers and the softmax work per tile (8 columns instead of
 // 16 rows) and leaves room for three CTAs an SM.  P^T moves from the accumulator layout to the B-operand
-// layout with two movmatrix transposes.  Keys and values come through a ring of two tiles a warp in
-// shared memory, filled with cp.async one tile ahead (loads straight into registers kept too few bytes
-// in flight: the compiler holds them back behind the softmax of the tile before), and are read from it
-// with 16-byte loads by the same freedom as in attention_mma.cu: the contraction index is mapped to 8
+// layout with two movmatrix transposes.  Keys and values come through a ring of DEPTH tiles a warp in
+// shared memory, filled with cp.async DEPTH tiles ahead (loads straight into registers kept too few bytes
+// in flight: the compiler holds them back behind the softmax of the tile before); the ring's first round
+// is asked for before the wait for the kernel before this one, which writes the new token's row only.
+// They are read from the ring with 16-byte loads by the same freedom as in attention_mma.cu: the contraction index is mapped to 8
 // contiguous head dimensions per thread (Q K^T), and the output rows of an MMA tile are mapped so that a
 // thread's eight values of a key row serve four tiles (P V; two keys are paired by a byte permute).  The
 // 16-byte chunks of a row are XOR-swizzled by the row so that both read patterns are conflict-free.
@@ -138,22 +139,65 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   if (bt_cached && slot >= 0)
     for (int i = tid; i < nt_split; i += (NW * 32)) sm_bt[i] = bt[((t_begin + i) * AD_TILE) / p.page_size];
   __syncthreads();
+  // ---- the warp's ring of tiles in shared memory ----
+  // A warp's tiles (16 keys: 16 rows of K and of V, HD * 2 bytes each) are copied into its own ring of
+  // DEPTH stages with cp.async, 16 bytes a lane and instruction, DEPTH tiles ahead of the one being
+  // worked on: with a few hundred keys a split the loop is a chain of memory latencies, and the ring
+  // shortens it by that factor; with many requests it keeps enough bytes in flight for the bandwidth.
+  // The 16-byte piece j of row r sits at piece j ^ swizzle(r), chosen so that the fragment reads below
+  // (K: rows g, g + 8, pieces 4 s + c; V: rows 2 c (+1, +8, +9), pieces 8 h + g) hit all banks once.
+  constexpr int ROW_BYTES = HD * 2, CH = HD / 8;           // pieces a row
+  constexpr int TILE_BYTES = AD_TILE * ROW_BYTES;           // K (or V) of a tile
+  extern __shared__ __align__(16) unsigned char ad_ring[];
+  unsigned char* my_ring = ad_ring + (size_t)warp * DEPTH * 2 * TILE_BYTES;
+  const unsigned ring_addr = (unsigned)__cvta_generic_to_shared(my_ring);
+  auto tile_base = [&](int t) -> long {   // < 0: the table's entry is no page of the pool
+    const int key0 = t * AD_TILE;
+    const int page = bt_cached ? sm_bt[t - t_begin] : bt[key0 / p.page_size];
+    if (page < 0 || page >= p.num_pages) return -1;
+    return (((long)page * p.nkv + kvh) * p.page_size + (key0 % p.page_size)) * HD;
+  };
+  auto issue_tile = [&](int stage, int t) {   // the whole warp; always one group, empty beyond the split's end
+    const long tb = (t < t_end) ? tile_base(t) : -1;
+    if (tb >= 0) {
+      const unsigned kdst = ring_addr + stage * 2 * TILE_BYTES, vdst = kdst + TILE_BYTES;
+#pragma unroll
+      for (int i = 0; i < AD_TILE * CH / 32; ++i) {
+        const int idx = lane + 32 * i, r = idx / CH, j = idx % CH;
+        const bf16* ksrc = p.k_cache + tb + (long)r * HD + 8 * j;
+        const bf16* vsrc = p.v_cache + tb + (long)r * HD + 8 * j;
+        const unsigned kd = kdst + r * ROW_BYTES + ((j ^ (4 * (r & 1))) << 4);
+        const unsigned vd = vdst + r * ROW_BYTES + ((j ^ (2 * ((r >> 1) & 3))) << 4);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kd), "l"(ksrc) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vd), "l"(vsrc) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
   // The kernel before this one writes the new token's key and value only: every tile but the one that holds
-  // position `pos` was written by earlier steps and may be asked for before that kernel has finished.  Each
-  // lane asks L2 for one of the warp's tiles (K and V, contiguous within a page), so that the tile loop
-  // below meets L2's latency instead of memory's; the last tile is left alone.  Only while the step's keys
-  // and values are a small part of L2 (few requests, where the loop is a chain of latencies; with many, the
-  // loop is bound by bandwidth and L2 could not hold what was asked for).
+  // position `pos` was written by earlier steps and may be asked for before that kernel has finished.  The
+  // ring's first round goes out here (with few keys a split that is all of them: the loop below then finds its
+  // tiles in shared memory instead of meeting a memory latency a tile), and each lane asks L2 for one of the
+  // warp's later tiles (K and V, contiguous within a page), so that those meet L2's latency instead of
+  // memory's; the last tile is left alone.  L2 is only asked while the step's keys and values are a small part
+  // of it (few requests, where the loop is a chain of latencies; with many, the loop is bound by bandwidth and
+  // L2 could not hold what was asked for).
   constexpr unsigned TILE_B = AD_TILE * HD * 2;
-  if (slot >= 0 && (long)gridDim.x * gridDim.y * gridDim.z * nt_split * 2 * TILE_B <= (48l << 20)) {
-    for (int t = t_begin + warp + lane * NW; t < t_end; t += 32 * NW) {
-      if (t == t_last) continue;
-      const int key0 = t * AD_TILE;
-      const int page = bt_cached ? sm_bt[t - t_begin] : bt[key0 / p.page_size];
-      if (page < 0 || page >= p.num_pages) continue;
-      const long off = (((long)page * p.nkv + kvh) * p.page_size + (key0 % p.page_size)) * HD;
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.k_cache + off), "r"(TILE_B) : "memory");
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.v_cache + off), "r"(TILE_B) : "memory");
+  int filled = 0;   // tiles of the ring's first round that are under way
+  if (slot >= 0) {
+    for (; filled < DEPTH; ++filled) {
+      const int t = t_begin + warp + filled * NW;
+      if (t >= t_end || t == t_last) break;
+      issue_tile(filled, t);
+    }
+    if ((long)gridDim.x * gridDim.y * gridDim.z * nt_split * 2 * TILE_B <= (48l << 20)) {
+      for (int t = t_begin + warp + (DEPTH + lane) * NW; t < t_end; t += 32 * NW) {
+        if (t == t_last) continue;
+        const long off = tile_base(t);
+        if (off < 0) continue;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.k_cache + off), "r"(TILE_B) : "memory");
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.v_cache + off), "r"(TILE_B) : "memory");
+      }
     }
   }
   LL_PDL_WAIT();
@@ -174,46 +218,6 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   // The cluster's merge below writes into the other CTAs' shared memory, which needs them to have started:
   // every CTA says so here and checks it only when it gets there (by then it costs nothing).
   if (p.nsplit > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
-  auto tile_base = [&](int t) -> long {
-    const int key0 = t * AD_TILE;
-    const int page = bt_cached ? sm_bt[t - t_begin] : bt[key0 / p.page_size];
-    if (page < 0 || page >= p.num_pages) {
-      if (lane == 0) set_status(p.status, LL_ERR_PAGE_RANGE);
-      return -1;
-    }
-    return (((long)page * p.nkv + kvh) * p.page_size + (key0 % p.page_size)) * HD;
-  };
-  // ---- the warp's ring of tiles in shared memory ----
-  // A warp's tiles (16 keys: 16 rows of K and of V, HD * 2 bytes each) are copied into its own ring of
-  // DEPTH stages with cp.async, 16 bytes a lane and instruction, DEPTH - 1 tiles ahead of the one being
-  // worked on: with a few hundred keys a split the loop is a chain of memory latencies, and the ring
-  // shortens it by that factor; with many requests it keeps enough bytes in flight for the bandwidth.
-  // The 16-byte piece j of row r sits at piece j ^ swizzle(r), chosen so that the fragment reads below
-  // (K: rows g, g + 8, pieces 4 s + c; V: rows 2 c (+1, +8, +9), pieces 8 h + g) hit all banks once.
-  // (DEPTH 2; 3 for long streams without splits, where more bytes in flight are worth the shared memory.  With
-  //  few keys a CTA deeper rings were measured no faster, and their shared memory keeps the next product's
-  //  CTAs, which stream their weights ahead, from moving in beside this kernel.)
-  constexpr int ROW_BYTES = HD * 2, CH = HD / 8;           // pieces a row
-  constexpr int TILE_BYTES = AD_TILE * ROW_BYTES;           // K (or V) of a tile
-  extern __shared__ __align__(16) unsigned char ad_ring[];
-  unsigned char* my_ring = ad_ring + (size_t)warp * DEPTH * 2 * TILE_BYTES;
-  const unsigned ring_addr = (unsigned)__cvta_generic_to_shared(my_ring);
-  auto issue_tile = [&](int stage, long tb) {   // the whole warp; tb < 0: nothing to copy (still a group)
-    if (tb >= 0) {
-      const unsigned kdst = ring_addr + stage * 2 * TILE_BYTES, vdst = kdst + TILE_BYTES;
-#pragma unroll
-      for (int i = 0; i < AD_TILE * CH / 32; ++i) {
-        const int idx = lane + 32 * i, r = idx / CH, j = idx % CH;
-        const bf16* ksrc = p.k_cache + tb + (long)r * HD + 8 * j;
-        const bf16* vsrc = p.v_cache + tb + (long)r * HD + 8 * j;
-        const unsigned kd = kdst + r * ROW_BYTES + ((j ^ (4 * (r & 1))) << 4);
-        const unsigned vd = vdst + r * ROW_BYTES + ((j ^ (2 * ((r >> 1) & 3))) << 4);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kd), "l"(ksrc) : "memory");
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vd), "l"(vsrc) : "memory");
-      }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
   auto lds16 = [&](unsigned addr) -> uint4 {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -225,32 +229,20 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   for (int t = 0; t < MT; ++t) o_acc[t][0] = o_acc[t][1] = o_acc[t][2] = o_acc[t][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // heads 2c and 2c + 1
 
-  // tiles t_begin + warp, + NW, ...: the first DEPTH - 1 are asked for now, one more in every iteration
-  long tbase[DEPTH];   // cache offset of the tile in each stage (< 0: an invalid page, skipped)
-#pragma unroll
-  for (int d = 0; d < DEPTH - 1; ++d) {
-    const int td = t_begin + warp + d * NW;
-    tbase[d] = (td < t_end) ? tile_base(td) : -1;
-    issue_tile(d, tbase[d]);
-  }
+  // tiles t_begin + warp, + NW, ...: the rest of the ring's first round (the tile with the new token, and
+  // empty groups beyond the split's end, so that group i is tile i's)
+  for (; filled < DEPTH; ++filled) issue_tile(filled, t_begin + warp + filled * NW);
   int it = 0;
   for (int t = t_begin + warp; t < t_end; t += NW, ++it) {
     const int stage = it % DEPTH;
-    asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 2) : "memory");   // this lane's copies of tile `it` are in
+    asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");   // this lane's copies of tile `it` are in
     __syncwarp();                                                           // and so are the other lanes'
-    {   // the stage freed in the iteration before takes the tile DEPTH - 1 ahead
-      const int ta = t + (DEPTH - 1) * NW, sa = (it + DEPTH - 1) % DEPTH;
-      const long tba = (ta < t_end) ? tile_base(ta) : -1;
-#pragma unroll
-      for (int d = 0; d < DEPTH; ++d)
-        if (d == sa) tbase[d] = tba;
-      issue_tile(sa, tba);
+    const long tb = tile_base(t);
+    if (tb < 0) {   // (nothing was copied; the stage takes the tile DEPTH ahead like any other)
+      if (lane == 0) set_status(p.status, LL_ERR_PAGE_RANGE);
+      issue_tile(stage, t + DEPTH * NW);
+      continue;
     }
-    long tb = -1;
-#pragma unroll
-    for (int d = 0; d < DEPTH; ++d)
-      if (d == stage) tb = tbase[d];
-    if (tb < 0) continue;
     const unsigned kst = ring_addr + stage * 2 * TILE_BYTES, vst = kst + TILE_BYTES;
     uint4 ka[KS], kb[KS], vv[VS][4];
 #pragma unroll
@@ -311,6 +303,9 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
       vv[h][2] = lds16(vst + (2 * c + 8) * ROW_BYTES + piece);
       vv[h][3] = lds16(vst + (2 * c + 9) * ROW_BYTES + piece);
     }
+    // the stage's rows are in registers: it takes the tile DEPTH ahead
+    __syncwarp();
+    issue_tile(stage, t + DEPTH * NW);
     // keys that the token may not see have probability 0 by selection, but what their rows of V hold (left by an
     // earlier owner of the page, possibly Inf or NaN) would still spoil the product: zeros by selection too
     if (boundary) {
@@ -470,11 +465,14 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
 // One new token per entry: q row e (head h at q + e*q_stride + h*hd) attends to the cached keys of
 // the request in req_slot[e] up to position ctx_len[e] (its own key is already in the cache).
 // nsplit in {1, 2, 4, 8}: CTAs per (entry, kv head), launched as one cluster; warps in {4, 8}: warps a CTA
-// (they take the split's 16-key tiles in turn).
+// (they take the split's 16-key tiles in turn); depth: tiles of a warp's ring, 2..4 for 4 warps, 2 or 3 for 8
+// (0: 3, but 2 for 8 warps in clusters).  Measured in a decode step at batch 8 (4 warps, 17 tiles a CTA): rings
+// of 3 tiles 1.108 ms, of 2 tiles 1.125-1.157 ms, of 4 tiles (128 KB a CTA, which no longer sits beside the
+// products around it while they stream their weights ahead) 1.24-1.27 ms.
 extern "C" int ll_attn_decode(void* out, long out_stride, const void* q, long q_stride, const void* k_cache,
                               const void* v_cache, const int* block_table, int bt_stride, const int* ctx_len,
                               const int* req_slot, int n_entries, int nh, int nkv, int hd, int page_size,
-                              int num_pages, int window, float scale, int nsplit, int warps, int* status,
+                              int num_pages, int window, float scale, int nsplit, int warps, int depth, int* status,
                               cudaStream_t stream) {
   if (n_entries <= 0) return 0;
   if ((hd != 64 && hd != 128) || page_size % AD_TILE != 0 || nkv <= 0 || nh % nkv != 0 || nkv > 65535)
@@ -504,20 +502,26 @@ extern "C" int ll_attn_decode(void* out, long out_stride, const void* q, long q_
   p.nsplit = nsplit;
   p.status = status;
   dim3 grid(n_entries, nkv, nsplit);
-  // the warps' rings: two stages of a K and a V tile each; three for 8 warps that run through all keys
-  const int depth = (warps == 8 && nsplit == 1) ? 3 : 2;
+  if (depth == 0) depth = (warps == 4 || nsplit == 1) ? 3 : 2;
+  if (!((warps == 4 && depth >= 2 && depth <= 4) || (warps == 8 && (depth == 2 || depth == 3))))
+    return (int)cudaErrorInvalidValue;
   const size_t ring = (size_t)warps * depth * 2 * AD_TILE * hd * 2;
 #define AD_LAUNCH(HD_, NW_, DEPTH_)                                                                                  \
   do {                                                                                                               \
     cudaFuncSetAttribute(attn_decode_kernel<HD_, NW_, DEPTH_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring); \
     ll_launch_cluster(attn_decode_kernel<HD_, NW_, DEPTH_>, grid, dim3(NW_ * 32), ring, stream, nsplit, p);          \
   } while (0)
-  if (hd == 64 && warps == 4) AD_LAUNCH(64, 4, 2);
-  else if (hd == 64 && depth == 2) AD_LAUNCH(64, 8, 2);
-  else if (hd == 64) AD_LAUNCH(64, 8, 3);
-  else if (warps == 4) AD_LAUNCH(128, 4, 2);
-  else if (depth == 2) AD_LAUNCH(128, 8, 2);
-  else AD_LAUNCH(128, 8, 3);
+#define AD_PICK(HD_)                                       \
+  do {                                                     \
+    if (warps == 4 && depth == 2) AD_LAUNCH(HD_, 4, 2);    \
+    else if (warps == 4 && depth == 3) AD_LAUNCH(HD_, 4, 3); \
+    else if (warps == 4) AD_LAUNCH(HD_, 4, 4);             \
+    else if (depth == 2) AD_LAUNCH(HD_, 8, 2);             \
+    else AD_LAUNCH(HD_, 8, 3);                             \
+  } while (0)
+  if (hd == 64) AD_PICK(64);
+  else AD_PICK(128);
+#undef AD_PICK
 #undef AD_LAUNCH
   return LL_LAUNCH_RESULT();
 }

@@ -274,10 +274,11 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
 def attn_decode(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
                 block_table: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor, num_entries: int,
                 num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
-                scale: float, nsplit: int, status: Optional[torch.Tensor], warps: int = 4) -> None:
+                scale: float, nsplit: int, status: Optional[torch.Tensor], warps: int = 4, depth: int = 0) -> None:
     """Tensor-core decode attention (bfloat16), transposed product: one new token per entry, groups of at
     most 8 query heads.  ``nsplit`` in (1, 2, 4, 8) CTAs per (entry, kv head) form a cluster; ``warps`` (4 or 8)
-    a CTA take the split's tiles in turn."""
+    a CTA take the split's tiles in turn through rings of ``depth`` tiles a warp (0: the kernel's choice; 2 to 4
+    for 4 warps, 2 or 3 for 8)."""
     _need_cuda(out, q, k_cache, v_cache, block_table, ctx_len, req_slot)
     for t, nm in ((block_table, "block_table"), (ctx_len, "ctx_len"), (req_slot, "req_slot")):
         _i32(t, nm)
@@ -295,7 +296,7 @@ def attn_decode(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torc
         "ll_attn_decode", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), _ptr(k_cache), _ptr(v_cache),
         _ptr(block_table), c_int(block_table.stride(0)), _ptr(ctx_len), _ptr(req_slot), c_int(num_entries),
         c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size), c_int(k_cache.shape[0]),
-        c_int(window or 0), c_float(scale), c_int(nsplit), c_int(warps), _ptr(status), _stream())
+        c_int(window or 0), c_float(scale), c_int(nsplit), c_int(warps), c_int(depth), _ptr(status), _stream())
 
 
 def attn_prefill(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -309,12 +309,14 @@ def test_attn_decode(nh, nkv, hd, ps, lens, window, nsplit):
     c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, lens, [1] * len(lens), window, seed=27)
     d = dev()
     ctx = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=d)
-    out = torch.full_like(c["q"], 3.0)
     status = torch.zeros(1, dtype=torch.int32, device=d)
-    ops.attn_decode(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], ctx, c["req_slot"], len(lens), nh, nkv,
-                    hd, ps, window, hd ** -0.5, nsplit, status)
-    assert status.item() == 0
-    assert_close(out, c["ref"], torch.bfloat16, "attn_decode")
+    # 4 or 8 warps a CTA, rings of 2 to 4 tiles a warp (0: the kernel's choice): more or fewer tiles than the ring holds
+    for warps, depth in ((4, 0), (4, 2), (4, 4), (8, 0), (8, 3)):
+        out = torch.full_like(c["q"], 3.0)
+        ops.attn_decode(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], ctx, c["req_slot"], len(lens), nh, nkv,
+                        hd, ps, window, hd ** -0.5, nsplit, status, warps=warps, depth=depth)
+        assert status.item() == 0
+        assert_close(out, c["ref"], torch.bfloat16, f"attn_decode with {warps} warps, rings of {depth}")
 
 
 @pytest.mark.parametrize("nsplit", [1, 8])
