@@ -247,6 +247,7 @@ MMA_SHAPES = [
     (8, 2, 64, 16, [3000], [1], None, 16),
     (8, 2, 64, 16, [500, 90], [1, 30], None, 4),
     (3, 1, 128, 32, [257, 300], [100, 1], 120, 2),
+    (12, 2, 128, 16, [4500, 60], [1, 1], None, 1),               # more tiles than the block table's shared-memory copy holds
 ]
 
 
@@ -299,6 +300,7 @@ DECODE_SHAPES = [
     (3, 3, 128, 32, [257, 16, 15], None),            # group 1
     (14, 2, 64, 64, [300, 900], None),               # group 7, page 64
     (12, 2, 128, 16, [500, 77, 3000], 120),          # window
+    (12, 2, 128, 16, [4700, 100], None),             # more tiles a split than the block table's shared-memory copy holds
 ]
 
 
