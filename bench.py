@@ -318,6 +318,37 @@ def kernel_times(engine, batch, steps):
     return "\n".join(lines)
 
 
+def layer_timeline(engine, batch, steps, warmup):
+    """Decode steps of a timeline build (LITE_LANG_B200_TIMELINE=1: the kernels stamp %globaltimer), and a table of
+    the last layer's products and attention: for each the earliest, median and latest CTA's start, release (its
+    wait for the kernel before is over) and end, in microseconds from the q|k|v projection's release."""
+    import numpy as np
+    if engine.runner.timeline() is None:
+        return "not a timeline build: set LITE_LANG_B200_TIMELINE=1 (the libraries are built a second time for it)"
+    ms, ctx = device_decode(engine, batch, steps, warmup)
+    tl = engine.runner.timeline()
+    base = tl["qkv"][:, 1].min() if "qkv" in tl else 0.0
+    lines = [f"batch {batch}, context {ctx:.0f}: {ms:.4f} ms a step with the stamps compiled in; us from q|k|v's release",
+             f"{'kernel':10s} {'CTAs':>5s} | {'started: first median last':>27s} | {'released':>27s} | {'ended':>27s}"]
+
+    def three(v):
+        v = v[v > 0] - base
+        return f"{v.min():8.2f} {np.median(v):8.2f} {v.max():8.2f}" if len(v) else " " * 26
+
+    for name, ev in tl.items():
+        if abs(ev[:, 1].min() - base) > 1000.0:      # stamps of an earlier step: this step's did not come from that kernel
+            lines.append(f"{name:10s}       | (not one of this step's kernels: its product went to another kernel)")
+            continue
+        lines.append(f"{name:10s} {len(ev):5d} | {three(ev[:, 0])}  | {three(ev[:, 1])}  | {three(ev[:, 2])}")
+    if "attention" in tl and "qkv" in tl:
+        ev = tl["attention"]
+        late = ev[:, 0] - base > 0
+        lines.append(f"attention: {int(late.sum())} of {len(ev)} CTAs started only after q|k|v's release; tile loop over "
+                     f"at {np.median(ev[~late, 3] - base) if (~late).any() else float('nan'):.2f} (median of the others), "
+                     f"{(ev[:, 3] - base).max():.2f} (last)")
+    return "\n".join(lines)
+
+
 def run_ours(args):
     import torch
     from lite_lang_b200.csrc import build as kbuild
@@ -338,6 +369,9 @@ def run_ours(args):
         return 0
     if args.only == "kernels":
         print(kernel_times(engine, batch, max(4, min(args.steps, 20))))
+        return 0
+    if args.only == "timeline":
+        print(layer_timeline(engine, batch, args.steps, args.warmup))
         return 0
     if args.only == "prefill":
         r = prefill_once(engine, repeats=max(1, args.steps), seconds=0.0)
@@ -507,9 +541,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (reported in config)")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "kernels"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "kernels", "timeline"],
                     help="a small case for profilers: only the decode steps or only the prefill (prints a short "
-                         "line), or 'kernels': the decode step's kernels timed inside its graph by torch.profiler")
+                         "line), or 'kernels': the decode step's kernels timed inside its graph by torch.profiler, or "
+                         "'timeline' (with LITE_LANG_B200_TIMELINE=1): when the CTAs of the last layer's kernels "
+                         "started, were let go by the kernel before, and ended, inside the captured decode step")
     ap.add_argument("--workload", default="", choices=[""] + sorted(WORKLOADS),
                     help="instead of the headline measurement: a whole serving workload through the scheduler "
                          "(Qwen2.5-3B sizes, 40 requests of 600 + 600 tokens; Qwen2-7B sizes, 64 requests with prompts "

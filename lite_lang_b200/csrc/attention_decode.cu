@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   const int e = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   if (e >= p.n_entries) return;
   LL_PDL_TRIGGER();   // the kernel after this one may move in and fetch its weights while this one works
+  LL_TIMELINE_STAMP(p.status, 1, 0);
   // What the step's index arrays say (slot, context length, block table) was uploaded before the step's
   // first kernel and is read before the wait for the kernel before this one; q and the new token's key
   // and value are that kernel's output and are read after it.
@@ -201,6 +202,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
     }
   }
   LL_PDL_WAIT();
+  LL_TIMELINE_STAMP(p.status, 1, 1);
   // ---- Q^T fragments: thread (g, c) holds head g, dims 32 s + 8 c .. + 7 ----
   uint4 qf[KS];
   {
@@ -346,6 +348,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
+  LL_TIMELINE_STAMP(p.status, 1, 3);   // (the tile loop is over)
 
   // ---- merge the four warps (rows of the merge = heads) ----
 #pragma unroll
@@ -403,6 +406,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
       for (int d = 0; d < DPT; d += 2)
         *reinterpret_cast<unsigned*>(orow + d) = ad_pack(acc[d] * inv, acc[d + 1] * inv);
     }
+    LL_TIMELINE_STAMP(p.status, 1, 2);
     return;
   }
   // ---- the splits are the CTAs of one cluster: each finishes a slice of the dims of all heads ----
@@ -460,6 +464,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
     for (int k = 0; k < 4; ++k)
       if (k < per) o2[k] = __float2bfloat16_rn(fin[k] * inv);
   }
+  LL_TIMELINE_STAMP(p.status, 1, 2);
 }
 
 // One new token per entry: q row e (head h at q + e*q_stride + h*hd) attends to the cached keys of

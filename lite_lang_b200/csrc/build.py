@@ -142,16 +142,33 @@ def _run(cmd: List[str], what: str) -> None:
         _say(out)
 
 
-def library_path(name: str) -> str:
+def timeline_build() -> bool:
+    """LITE_LANG_B200_TIMELINE=1: the libraries are built with the kernels' time stamps compiled in (a build of
+    its own beside the ordinary one; see ``LL_TIMELINE_STAMP`` in common.cuh)."""
+    return os.environ.get("LITE_LANG_B200_TIMELINE", "0") == "1"
+
+
+def _library(name: str):
     sources, definitions = LIBRARIES[name]
-    return os.path.join(_build_dir(), f"liblitelang_{name}_{_digest(sources, definitions)}.so")
+    if timeline_build():
+        definitions = tuple(definitions) + ("-DLL_TIMELINE",)
+    return sources, definitions
+
+
+def _file_prefix(name: str) -> str:
+    return f"liblitelang_{name}-timeline_" if timeline_build() else f"liblitelang_{name}_"
+
+
+def library_path(name: str) -> str:
+    sources, definitions = _library(name)
+    return os.path.join(_build_dir(), f"{_file_prefix(name)}{_digest(sources, definitions)}.so")
 
 
 def build_library(name: str, verbose: bool = True) -> str:
     """Compile ``name`` if needed and return the path of its shared object."""
     if name not in LIBRARIES:
         raise BuildError(f"unknown kernel library {name!r}; known: {sorted(LIBRARIES)}")
-    sources, definitions = LIBRARIES[name]
+    sources, definitions = _library(name)
     target = library_path(name)
     if os.path.isfile(target):
         return target
@@ -174,7 +191,7 @@ def build_library(name: str, verbose: bool = True) -> str:
     tmp = target + f".{os.getpid()}.tmp"
     _run([nvcc, *ARCH_FLAGS, "-shared", "-Xcompiler", "-fPIC", "-o", tmp, *objs], f"link {name}")
     os.replace(tmp, target)
-    prefix = f"liblitelang_{name}_"
+    prefix = _file_prefix(name)
     for old in os.listdir(bdir):  # shared objects of this library built from older sources
         if (old.startswith(prefix) and old.endswith(".so") and len(old) == len(prefix) + 16 + 3
                 and os.path.join(bdir, old) != target):

@@ -102,6 +102,32 @@ __device__ __forceinline__ void set_status(int* status, int code) {
 #define LL_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
 #define LL_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
 
+// ---------------------------------------------------------------------------------------
+// Timeline build (LITE_LANG_B200_TIMELINE=1 when the libraries are built and loaded; off otherwise, and then
+// nothing of it is compiled).  Thread 0 of every CTA of the decode step's products and of the decode attention
+// writes %globaltimer at three places (the CTA has started, the wait for the kernel before is over, the CTA is
+// done) into the words behind the status word: 64-bit slot ((kernel * 512 + CTA) * 4 + event), plain stores that
+// nobody waits for.  Later launches of a kernel overwrite earlier ones, so what is read back afterwards is the
+// last layer of the last step.  Kernels: 0 q|k|v, 1 decode attention, 2 narrow product to bfloat16 (o), 3 gated,
+// 4 narrow product to float32 partial sums (down), 5 wide (logits).
+// ---------------------------------------------------------------------------------------
+#define LL_TIMELINE_KERNELS 6
+#define LL_TIMELINE_CTAS 512
+#ifdef LL_TIMELINE
+__device__ __forceinline__ void ll_timeline_stamp(int* status, int kernel, int event) {
+  if (threadIdx.x == 0 && status != nullptr) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const unsigned cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (cta < LL_TIMELINE_CTAS)
+      reinterpret_cast<unsigned long long*>(status + 4)[((size_t)kernel * LL_TIMELINE_CTAS + cta) * 4 + event] = t;
+  }
+}
+#define LL_TIMELINE_STAMP(status, kernel, event) ll_timeline_stamp(status, kernel, event)
+#else
+#define LL_TIMELINE_STAMP(status, kernel, event)
+#endif
+
 #include <stdlib.h>
 #include <utility>
 static inline bool ll_pdl_enabled() {

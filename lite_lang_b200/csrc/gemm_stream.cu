@@ -195,6 +195,8 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
   }
   __syncthreads();
   LL_PDL_TRIGGER();
+  constexpr int TL_KERNEL = MODE == GT_MODE_QKV_ROPE ? 0 : MODE == GT_MODE_GATED ? 3 : MODE == GT_MODE_WIDE ? 5 : (sizeof(OutT) == 2 ? 2 : 4);
+  LL_TIMELINE_STAMP(p.status, TL_KERNEL, 0);
 
   const int kchunks = p.K / S::KC;
 
@@ -271,6 +273,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
   // the token rows are written by the kernel before this one; the producer warp does not wait (it
   // only reads weights), the consumers do, so no CTA exits before the kernel before has finished
   LL_PDL_WAIT();
+  LL_TIMELINE_STAMP(p.status, TL_KERNEL, 1);
 
   // k boxes of a stage this warp works on, and where its two A rows sit inside a box
   constexpr bool KSPLIT_WARPS = (MODE == GT_MODE_NARROW || MODE == GT_MODE_QKV_ROPE);  // warps split k
@@ -469,6 +472,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
       gt_consumer_sync();
     }
   }
+  LL_TIMELINE_STAMP(p.status, TL_KERNEL, 2);
 }
 
 typedef CUresult (*gt_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

@@ -66,6 +66,13 @@ class ModelRunner:
         # last element: the kernels' status word; the rest: sampled tokens (see sampling/)
         self.result_buf = torch.zeros(manager.max_requests + 1, dtype=torch.int32, device=device)
         self.status = self.result_buf[manager.max_requests:]
+        self._timeline = None
+        if ops.timeline_build():
+            # a timeline build's kernels write their time stamps behind the status word, which then heads a
+            # buffer of its own (kernels that are given no status word find it through ops)
+            self._timeline = torch.zeros(4 + 2 * ops.TIMELINE_SLOTS, dtype=torch.int32, device=device)
+            self.status = self._timeline[:1]
+            ops.TIMELINE_STATUS = self.status
         self.builder = BatchBuilder(manager, max_tokens_per_step, manager.max_requests, device, self.status)
         self.single_builder = BatchBuilder(manager, manager.max_requests, manager.max_requests, device, self.status)
         self.use_graphs = bool(cuda_graphs)
@@ -156,6 +163,23 @@ class ModelRunner:
         return logits[:batch.real_logits]
 
     # ------------------------------------------------------------------
+    def timeline(self):
+        """A timeline build's time stamps of the last layer of the last step, in microseconds from the first
+        stamp: {kernel name: float array [CTAs that ran, 4 events]} with the events started, released (the wait
+        for the kernel before is over), done, and for the attention the end of its tile loop; 0 where a CTA wrote
+        none.  None in an ordinary build."""
+        if self._timeline is None:
+            return None
+        import numpy as np
+        raw = self._timeline[4:].cpu().numpy().view(np.uint64).reshape(len(ops.TIMELINE_KERNELS), -1, 4)
+        t0 = raw[raw > 0].min() if (raw > 0).any() else 0
+        out = {}
+        for name, block in zip(ops.TIMELINE_KERNELS, raw):
+            ran = block[block[:, 0] > 0]
+            if len(ran):
+                out[name] = np.where(ran > 0, (ran.astype(np.int64) - np.int64(t0)) / 1000.0, 0.0)
+        return out
+
     def check_status(self) -> None:
         """Raise if a kernel met an index out of range (synchronises)."""
         code = int(self.status.item())

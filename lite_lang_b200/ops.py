@@ -577,7 +577,7 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: 
     load_library("gemm_stream").call(
         "ll_gemm_stream", _ptr(out), c_long(out_stride), c_int(1 if out.dtype == torch.float32 else 0), _ptr(x),
         c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(mode), c_int(ksplit),
-        c_int(sm_count(x.device)), _ptr(status), _stream())
+        c_int(sm_count(x.device)), _ptr(status if status is not None else TIMELINE_STATUS), _stream())
     return out
 
 
@@ -617,6 +617,18 @@ def gemm_stream_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w_qkv: torch.Tens
         c_int(m), c_int(k), _ptr(bias), _ptr(positions), _ptr(cos_sin), c_int(cos_sin.shape[0]), c_int(num_heads),
         c_int(num_kv_heads), c_int(head_dim), _ptr(slot_map), _ptr(k_cache), _ptr(v_cache), c_int(page_size),
         c_long(num_slots), c_int(sm_count(x.device)), _ptr(status), _stream())
+
+
+# A timeline build (LITE_LANG_B200_TIMELINE=1, see csrc/common.cuh): the kernels stamp the clock behind the status
+# word that the runner hands out; those that a caller gives no status word get the runner's.
+TIMELINE_KERNELS = ("qkv", "attention", "o", "gated", "down", "logits")
+TIMELINE_SLOTS = len(TIMELINE_KERNELS) * 512 * 4
+TIMELINE_STATUS = None
+
+
+def timeline_build() -> bool:
+    from .csrc.build import timeline_build as on
+    return on()
 
 
 TC_M = 128          # most tokens the tcgen05 weight-streaming kernel takes
