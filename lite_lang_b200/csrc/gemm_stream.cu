@@ -147,8 +147,22 @@ struct GtParams {
   bf16* v_cache;
   int page_size;
   long num_slots;
+  // A norm between two products, split between them.  The product before the norm (NARROW to bfloat16, k not
+  // split) adds its result to the residual rows, writes them back, writes them times the norm's weight as its
+  // output (what the product after the norm multiplies), and leaves the sum of squares of each row's 16 values
+  // of a unit in sumsq_out[unit][32].  The product after the norm (GATED) adds the units' sums of a row in a
+  // fixed order and scales the row of its result by 1 / sqrt(sum / hidden + eps): the norm's reduction is off
+  // the path between the two, and its kernel, a link of the chain of dependent launches, is gone.
+  bf16* res;               // residual rows [M, N], row stride res_stride: read, added to, written
+  long res_stride;
+  const float* norm_w;     // float32 [N]
+  float* sumsq_out;        // float32 [N / 16][32]
+  const float* sumsq_in;   // float32 [sumsq_units][32]; null: no row factor
+  int sumsq_units;
+  float norm_eps, norm_inv_n;
   int* status;
 };
+#define GT_SUMSQ_ROWS 32   // rows of a sums-of-squares record: the most tokens the kernel takes
 
 // What a stage holds and how many there are.  The token rows of the stage's k range travel with the weights
 // (boxes of 8 MT rows x 64 k through a tensor map of x), so the consumers read both operands from shared
@@ -164,8 +178,10 @@ template <int MODE, int MT> struct GtStage {
   static constexpr int STAGES = FIT < S::STAGES ? FIT : S::STAGES;
 };
 
-template <int MODE, int MT, typename OutT>
-__global__ void __launch_bounds__(GT_THREADS)
+// SPLIT: the kernel's part of a norm that is split between the products around it (see GtParams): the NARROW product
+// before the norm, or the GATED product after it, which then has a sixth warp that makes the rows' factors.
+template <int MODE, int MT, typename OutT, bool SPLIT>
+__global__ void __launch_bounds__(GT_THREADS + ((SPLIT && MODE == GT_MODE_GATED) ? 32 : 0))
 gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap) {
   using S = GtShape<MODE>;
   using G = GtStage<MODE, MT>;
@@ -177,8 +193,9 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
   // the swizzle pattern repeats every 1024 bytes: stages start on a 1024-byte boundary
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
-  float* red = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 2 * STAGES * 8);
-  const unsigned full0 = gt_smem(bars), empty0 = gt_smem(bars + STAGES);
+  float* red = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 2 * STAGES * 8);   // (GATED has none of it:
+  const unsigned full0 = gt_smem(bars), empty0 = gt_smem(bars + STAGES);                  //  its place holds the
+  const unsigned scale_bar = gt_smem(bars + 2 * STAGES);                                   //  row factors' barrier)
   const unsigned stage0 = gt_smem(smem);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -191,14 +208,48 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
       gt_mbar_init(full0 + 8 * s, 1);
       gt_mbar_init(empty0 + 8 * s, GT_CONSUMERS);
     }
+    if (SPLIT && MODE == GT_MODE_GATED) gt_mbar_init(scale_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
   LL_PDL_TRIGGER();
-  constexpr int TL_KERNEL = MODE == GT_MODE_QKV_ROPE ? 0 : MODE == GT_MODE_GATED ? 3 : MODE == GT_MODE_WIDE ? 5 : (sizeof(OutT) == 2 ? 2 : 4);
+  [[maybe_unused]] constexpr int TL_KERNEL = MODE == GT_MODE_QKV_ROPE ? 0 : MODE == GT_MODE_GATED ? 3 : MODE == GT_MODE_WIDE ? 5 : (sizeof(OutT) == 2 ? 2 : 4);
   LL_TIMELINE_STAMP(p.status, TL_KERNEL, 0);
 
   const int kchunks = p.K / S::KC;
+
+  // ---- the rows' factors of the norm before a GATED product (SPLIT): a warp of its own adds the units' sums of
+  // squares of each token in a fixed order while the others stream and multiply, and the consumers find
+  // 1 / sqrt(mean + eps) in shared memory when they come to their epilogue.  Lanes: 2 MT consecutive ones hold
+  // the 8 MT tokens of a unit as 16-byte pieces, so 16 / MT units are on their way at once. ----
+  __shared__ float row_scale[(SPLIT && MODE == GT_MODE_GATED) ? GT_SUMSQ_ROWS : 1];
+  if (SPLIT && MODE == GT_MODE_GATED && warp == GT_CONSUMERS + 1) {
+    LL_PDL_WAIT();
+    constexpr int LPU = 2 * MT, UPAR = 32 / LPU;   // lanes a unit, units at once
+    const int piece = lane % LPU, usub = lane / LPU;
+    float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int un = usub; un < p.sumsq_units; un += UPAR) {
+      const float4 v = *reinterpret_cast<const float4*>(p.sumsq_in + (size_t)un * GT_SUMSQ_ROWS + 4 * piece);
+      tot.x += v.x; tot.y += v.y; tot.z += v.z; tot.w += v.w;
+    }
+#pragma unroll
+    for (int d = LPU; d < 32; d <<= 1) {   // the units' groups of lanes meet (the same order in every CTA and launch)
+      tot.x += __shfl_xor_sync(0xffffffffu, tot.x, d);
+      tot.y += __shfl_xor_sync(0xffffffffu, tot.y, d);
+      tot.z += __shfl_xor_sync(0xffffffffu, tot.z, d);
+      tot.w += __shfl_xor_sync(0xffffffffu, tot.w, d);
+    }
+    if (usub == 0) {
+      row_scale[4 * piece] = 1.0f / sqrtf(tot.x * p.norm_inv_n + p.norm_eps);
+      row_scale[4 * piece + 1] = 1.0f / sqrtf(tot.y * p.norm_inv_n + p.norm_eps);
+      row_scale[4 * piece + 2] = 1.0f / sqrtf(tot.z * p.norm_inv_n + p.norm_eps);
+      row_scale[4 * piece + 3] = 1.0f / sqrtf(tot.w * p.norm_inv_n + p.norm_eps);
+    }
+    __syncwarp();
+    if (lane == 0) gt_mbar_arrive(scale_bar);   // (an arrival releases what the warp wrote before it)
+    return;
+  }
 
   if (warp == GT_CONSUMERS) {
     // ------------------------------ producer ------------------------------
@@ -274,7 +325,6 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
   // only reads weights), the consumers do, so no CTA exits before the kernel before has finished
   LL_PDL_WAIT();
   LL_TIMELINE_STAMP(p.status, TL_KERNEL, 1);
-
   // k boxes of a stage this warp works on, and where its two A rows sit inside a box
   constexpr bool KSPLIT_WARPS = (MODE == GT_MODE_NARROW || MODE == GT_MODE_QKV_ROPE);  // warps split k
   constexpr int MYBOXES = KSPLIT_WARPS ? 1 : KBOXES;
@@ -334,6 +384,20 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
         }
       }
     }
+    // NARROW into the residual stream: the residual values and the norm's weights of this thread's places in the
+    // unit's epilogue (token idx / 16, feature idx % 16) are asked for now, too
+    constexpr bool FUSE_OK = SPLIT && MODE == GT_MODE_NARROW && sizeof(OutT) == 2;
+    float fr_res[MT], fr_w[MT];
+    if (FUSE_OK) {
+#pragma unroll
+      for (int e = 0; e < MT; ++e) {
+        const int idx = tid + e * GT_CONSUMERS * 32;
+        const int t = idx >> 4, n = u * 16 + (idx & 15);
+        const bool ok = t < p.M && n < p.N;
+        fr_res[e] = ok ? __bfloat162float(p.res[(size_t)t * p.res_stride + n]) : 0.f;
+        fr_w[e] = ok ? p.norm_w[n] : 0.f;
+      }
+    }
     const int kc_end = min(kchunks, (kp + 1) * p.cpp);
     for (int kc = kp * p.cpp; kc < kc_end; ++kc, ++it) {
       const int s = (int)(it % STAGES);
@@ -385,6 +449,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
       }
     } else if (MODE == GT_MODE_GATED) {
       const int f = u * 32 + 8 * warp + g;
+      if (SPLIT) gt_mbar_wait(scale_bar, 0, p.status);   // the rows' factors are in shared memory (long since)
       if (f < p.N) {
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
@@ -393,8 +458,9 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
             const int t = 8 * j + 2 * c + h;
             if (t < p.M) {
               // gate and up are rounded to bfloat16 first, as the unfused path does between product and activation
-              const float gt = __bfloat162float(__float2bfloat16_rn(acc[j][h]));
-              const float up = __bfloat162float(__float2bfloat16_rn(acc[j][2 + h]));
+              const float rs = SPLIT ? row_scale[t] : 1.0f;
+              const float gt = __bfloat162float(__float2bfloat16_rn(acc[j][h] * rs));
+              const float up = __bfloat162float(__float2bfloat16_rn(acc[j][2 + h] * rs));
               out[(size_t)t * p.out_stride + f] = gt_out<OutT>(gt / (1.0f + expf(-gt)) * up);
             }
           }
@@ -458,6 +524,30 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
             }
           }
         }
+      } else if (FUSE_OK) {
+        // h += product (both rounded as the separate kernels round them: the product to bfloat16, then the sum);
+        // out = h * w, what the product after the norm multiplies; the 16 lanes of a token add their squares
+#pragma unroll
+        for (int e = 0; e < MT; ++e) {
+          const int idx = tid + e * GT_CONSUMERS * 32;
+          const int t = idx >> 4, f = idx & 15;
+          const bool ok = t < p.M && u * 16 + f < p.N;
+          float sum = 0.f;
+#pragma unroll
+          for (int wi = 0; wi < GT_CONSUMERS; ++wi) sum += red[((size_t)wi * 16 + f) * TOK + t];
+          float hn = 0.f;
+          if (ok) {
+            hn = __bfloat162float(__float2bfloat16_rn(fr_res[e] + __bfloat162float(__float2bfloat16_rn(sum))));
+            p.res[(size_t)t * p.res_stride + u * 16 + f] = __float2bfloat16_rn(hn);
+            out[(size_t)t * p.out_stride + u * 16 + f] = gt_out<OutT>(hn * fr_w[e]);
+          }
+          float sq = hn * hn;
+          sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+          if (f == 0) p.sumsq_out[(size_t)u * GT_SUMSQ_ROWS + t] = sq;   // (t < 8 MT <= 32; rows beyond M hold 0)
+        }
       } else {
         for (int idx = tid; idx < 16 * TOK; idx += GT_CONSUMERS * 32) {
           const int t = idx >> 4, f = idx & 15;
@@ -506,7 +596,7 @@ static int gt_make_map(CUtensorMap* map, const void* w, long rows, long K, int b
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int MODE, int MT, typename OutT>
+template <int MODE, int MT, typename OutT, bool SPLIT>
 static int gt_launch(const GtParams& p, const void* w, int sm_count, cudaStream_t stream) {
   using S = GtShape<MODE>;
   using G = GtStage<MODE, MT>;
@@ -516,20 +606,21 @@ static int gt_launch(const GtParams& p, const void* w, int sm_count, cudaStream_
   if (rc != 0) return rc;
   rc = gt_make_map(&xmap, p.x, p.M, p.K, 8 * MT, p.x_stride);   // token rows: boxes of 8 MT rows, zeros beyond M
   if (rc != 0) return rc;
-  const size_t smem = 1024 + (size_t)G::STAGES * G::STAGE_BYTES + 2 * G::STAGES * 8 +
+  const size_t smem = 1024 + (size_t)G::STAGES * G::STAGE_BYTES + 2 * G::STAGES * 8 + 8 +   // (+ the row factors' barrier)
                       ((MODE == GT_MODE_NARROW || MODE == GT_MODE_QKV_ROPE) ? sizeof(float) * GT_CONSUMERS * 16 * 8 * MT : 0);
-  cudaFuncSetAttribute(gemm_stream_kernel<MODE, MT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaFuncSetAttribute(gemm_stream_kernel<MODE, MT, OutT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   // two CTAs an SM (one an SM, so that the next product's CTAs could move in early, was measured slower)
   const int grid = p.units < 2 * sm_count ? p.units : 2 * sm_count;
-  ll_launch(gemm_stream_kernel<MODE, MT, OutT>, dim3(grid), dim3(GT_THREADS), smem, stream, p, map, xmap);
+  const int threads = GT_THREADS + ((SPLIT && MODE == GT_MODE_GATED) ? 32 : 0);
+  ll_launch(gemm_stream_kernel<MODE, MT, OutT, SPLIT>, dim3(grid), dim3(threads), smem, stream, p, map, xmap);
   return LL_LAUNCH_RESULT();
 }
 
-template <int MODE, typename OutT>
+template <int MODE, typename OutT, bool SPLIT = false>
 static int gt_dispatch_m(const GtParams& p, const void* w, int sm_count, cudaStream_t stream) {
-  if (p.M <= 8) return gt_launch<MODE, 1, OutT>(p, w, sm_count, stream);
-  if (p.M <= 16) return gt_launch<MODE, 2, OutT>(p, w, sm_count, stream);
-  if (p.M <= 32) return gt_launch<MODE, 4, OutT>(p, w, sm_count, stream);
+  if (p.M <= 8) return gt_launch<MODE, 1, OutT, SPLIT>(p, w, sm_count, stream);
+  if (p.M <= 16) return gt_launch<MODE, 2, OutT, SPLIT>(p, w, sm_count, stream);
+  if (p.M <= 32) return gt_launch<MODE, 4, OutT, SPLIT>(p, w, sm_count, stream);
   return (int)cudaErrorInvalidValue;
 }
 
@@ -580,6 +671,62 @@ extern "C" int ll_gemm_stream(void* out, long out_stride, int out_f32, const voi
                    : gt_dispatch_m<GT_MODE_NARROW, bf16>(p, w, sm_count, stream);
   }
   return (int)cudaErrorInvalidValue;
+}
+
+// The product before a norm and the product after it, with the norm split between them (see GtParams).
+// ll_gemm_stream_into_norm: res[M, N] += x W^T (bfloat16, rounded as a separate product and sum would be), out[M, N] =
+// res * norm_w, sumsq[N / 16][32] = the sums of squares of each row's 16 values of a unit.  K % 256 == 0, N % 16 == 0.
+// ll_gemm_stream_gated_scaled: the gated product of rows that are only multiplied by the norm's weight yet; each
+// row of the result is scaled by 1 / sqrt(sum over units of sumsq[unit][row] / hidden + eps) before the activation.
+extern "C" int ll_gemm_stream_into_norm(void* out, long out_stride, void* res, long res_stride, const float* norm_w,
+                                        float* sumsq, const void* x, long x_stride, const void* w, int M, int N, int K,
+                                        int sm_count, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 32 || K <= 0 || (K % 256) != 0 || (N % 16) != 0 || (x_stride % 8) != 0 || sm_count <= 0 || res == nullptr ||
+      norm_w == nullptr || sumsq == nullptr)
+    return (int)cudaErrorInvalidValue;
+  GtParams p = {};
+  p.x = (const bf16*)x;
+  p.out = out;
+  p.x_stride = x_stride;
+  p.out_stride = out_stride;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.status = status;
+  p.cpp = K / 256;
+  p.ksplit = 1;
+  p.units = N / 16;
+  p.res = (bf16*)res;
+  p.res_stride = res_stride;
+  p.norm_w = norm_w;
+  p.sumsq_out = sumsq;
+  return gt_dispatch_m<GT_MODE_NARROW, bf16, true>(p, w, sm_count, stream);
+}
+
+extern "C" int ll_gemm_stream_gated_scaled(void* out, long out_stride, const void* x, long x_stride, const void* w,
+                                           int M, int N, int K, const float* sumsq, int sumsq_units, float eps,
+                                           int sm_count, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 32 || K <= 0 || (K % 128) != 0 || (x_stride % 8) != 0 || sm_count <= 0 || sumsq == nullptr || sumsq_units <= 0)
+    return (int)cudaErrorInvalidValue;
+  GtParams p = {};
+  p.x = (const bf16*)x;
+  p.out = out;
+  p.x_stride = x_stride;
+  p.out_stride = out_stride;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.status = status;
+  p.cpp = K / 128;
+  p.ksplit = 1;
+  p.units = (N + 31) / 32;
+  p.sumsq_in = sumsq;
+  p.sumsq_units = sumsq_units;
+  p.norm_eps = eps;
+  p.norm_inv_n = 1.0f / (float)K;
+  return gt_dispatch_m<GT_MODE_GATED, bf16, true>(p, w, sm_count, stream);
 }
 
 // The fused q|k|v projection of an attention layer (mode QKV_ROPE): qkv = x W^T (+ bias), q and k

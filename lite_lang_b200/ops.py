@@ -581,6 +581,64 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: 
     return out
 
 
+SUMSQ_ROWS = 32     # rows of a sums-of-squares record (the most tokens ``gemm_stream`` takes)
+NORM_SPLIT = os.environ.get("LITE_LANG_B200_NORM_SPLIT", "1") != "0"   # 0: the norm between two streaming products
+                                                                        # stays a kernel of its own (for comparisons)
+
+
+def norm_split_supported(x: torch.Tensor, w_before: torch.Tensor, residual: torch.Tensor,
+                         w_after: torch.Tensor) -> bool:
+    """Whether the norm between the product ``x @ w_before.T`` (added to ``residual``) and the gated product with
+    ``w_after`` can be split between the two (``gemm_stream_into_norm``, ``gemm_stream_gated_scaled``): both
+    streaming products of a decode step, the first with units of 16 features and an unsplit k."""
+    n = w_before.shape[0]
+    return (NORM_SPLIT and stream_mode(x, w_before) == 2 and n % 16 == 0 and residual.dtype == torch.bfloat16
+            and residual.dim() == 2 and tuple(residual.shape) == (x.shape[0], n) and residual.stride(1) == 1
+            and w_after.dtype == torch.bfloat16 and w_after.shape[1] == n and n % 128 == 0 and w_after.is_contiguous()
+            and w_after.data_ptr() % 16 == 0 and not tc_preferred(residual, w_after, gated=True))
+
+
+def gemm_stream_into_norm(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor,
+                          status: Optional[torch.Tensor] = None):
+    """residual += x @ weight.T (rounded as the separate product and sum would be); returns (u, sumsq): u = the new
+    residual rows times ``norm_weight`` (bfloat16), sumsq float32 [out / 16, 32] = the sums of squares of each
+    row's 16 values of a unit.  With ``gemm_stream_gated_scaled`` after it, this is the residual sum, the RMS norm
+    and the two products around them in two kernels instead of three."""
+    _need_cuda(x, weight, residual, norm_weight, status)
+    m, k = x.shape
+    n = weight.shape[0]
+    _need(stream_mode(x, weight) == 2 and n % 16 == 0, "gemm_stream_into_norm: bfloat16, at most 32 tokens, K % 256 == 0, N % 16 == 0")
+    _need(residual.dtype == torch.bfloat16 and tuple(residual.shape) == (m, n) and residual.stride(1) == 1,
+          "gemm_stream_into_norm: residual is bfloat16 [tokens, out]")
+    _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == n and norm_weight.is_contiguous(),
+          "gemm_stream_into_norm: the norm's weight is float32 [out]")
+    u = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    sumsq = torch.empty((n // 16, SUMSQ_ROWS), dtype=torch.float32, device=x.device)
+    load_library("gemm_stream").call(
+        "ll_gemm_stream_into_norm", _ptr(u), c_long(u.stride(0)), _ptr(residual), c_long(residual.stride(0)),
+        _ptr(norm_weight), _ptr(sumsq), _ptr(x), c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k),
+        c_int(sm_count(x.device)), _ptr(status if status is not None else TIMELINE_STATUS), _stream())
+    return u, sumsq
+
+
+def gemm_stream_gated_scaled(u: torch.Tensor, w_gate_up: torch.Tensor, sumsq: torch.Tensor, eps: float,
+                             status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(g) * up of the rows x = u / sqrt(mean of squares + eps), where u is already multiplied by the norm's
+    weight and ``sumsq`` [units, 32] holds the rows' sums of squares in parts (``gemm_stream_into_norm``)."""
+    _need_cuda(u, w_gate_up, sumsq, status)
+    m, k = u.shape
+    inter = w_gate_up.shape[0] // 2
+    _need(stream_mode(u, w_gate_up, gated=True) == 1, "gemm_stream_gated_scaled: bfloat16, at most 32 tokens, K % 128 == 0")
+    _need(sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.shape[1] == SUMSQ_ROWS and sumsq.is_contiguous(),
+          "gemm_stream_gated_scaled: sums of squares are float32 [units, 32]")
+    act = torch.empty((m, inter), dtype=torch.bfloat16, device=u.device)
+    load_library("gemm_stream").call(
+        "ll_gemm_stream_gated_scaled", _ptr(act), c_long(act.stride(0)), _ptr(u), c_long(u.stride(0)), _ptr(w_gate_up),
+        c_int(m), c_int(inter), c_int(k), _ptr(sumsq), c_int(sumsq.shape[0]), c_float(eps),
+        c_int(sm_count(u.device)), _ptr(status if status is not None else TIMELINE_STATUS), _stream())
+    return act
+
+
 def qkv_rope_supported(x: torch.Tensor, w_qkv: torch.Tensor, head_dim: int, rot_dim: int) -> bool:
     """Whether the fused projection + bias + rotation + cache write kernel takes this step."""
     return (stream_mode(x, w_qkv) is not None and x.shape[1] % 256 == 0 and head_dim % 16 == 0

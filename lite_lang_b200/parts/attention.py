@@ -22,7 +22,7 @@ import torch
 
 from .. import ops
 from ..config.spec import PartSpec
-from .base import Mixer, PagedKVNeed, TensorDecl, build_part, register_part
+from .base import Mixer, NormSplit, PagedKVNeed, TensorDecl, build_part, register_part
 
 
 class GQAttention(Mixer):
@@ -94,14 +94,20 @@ class GQAttention(Mixer):
 
     # ------------------------------------------------------------------
     accumulates = True
+    splits_norm = True
 
-    def _project_out(self, attn, residual):
+    def _project_out(self, attn, residual, into_norm=None, status=None):
         if residual is not None and ops.accumulate_preferred(attn, self.w_o):
             ops.linear_accumulate(attn, self.w_o, residual)
             return None
+        if (residual is not None and into_norm is not None and into_norm[2] is not None
+                and ops.norm_split_supported(attn, self.w_o, residual, into_norm[2])):
+            # decode: the o projection adds into the residual stream and leaves the norm after it to the next product
+            u, sumsq = ops.gemm_stream_into_norm(attn, self.w_o, residual, into_norm[0], status)
+            return NormSplit(u, sumsq, into_norm[1])
         return ops.linear(attn, self.w_o, partial_ok=True)
 
-    def forward(self, x, step, cache, residual=None):
+    def forward(self, x, step, cache, residual=None, into_norm=None):
         n = x.shape[0]
         slot_map = cache.slot_map if cache.writable else None
         if (self.position is not None and self.position.fuses_with_store
@@ -113,7 +119,7 @@ class GQAttention(Mixer):
                                      cache.page_size, step.status)
             attn = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
             self.attend(attn, q, step, cache)
-            return self._project_out(attn, residual)
+            return self._project_out(attn, residual, into_norm, step.status)
         if (self.position is not None and self.position.fuses_with_store
                 and ops.pair_qkv_supported(x, self.w_qkv, self.head_dim, self.position.fused_table().shape[1])
                 and ops.pair_qkv_preferred(x, self.w_qkv)):
@@ -124,7 +130,7 @@ class GQAttention(Mixer):
                                    cache.page_size, step.status)
             attn = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
             self.attend(attn, q, step, cache)
-            return self._project_out(attn, residual)
+            return self._project_out(attn, residual, into_norm, step.status)
         qkv = ops.linear(x, self.w_qkv)
         if self.position is None or self.position.fuses_with_store:
             table = self.position.fused_table() if self.position is not None else None
@@ -140,7 +146,7 @@ class GQAttention(Mixer):
                                     slot_map, cache.k, cache.v, cache.page_size, step.status, n)
         attn = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
         self.attend(attn, qkv, step, cache)
-        return self._project_out(attn, residual)
+        return self._project_out(attn, residual, into_norm, step.status)
 
     def _plan_mma(self, step, entries, max_kv_len, sms):
         """Row blocks, splits and warps of the decode kernel for ``entries`` single-token entries on a

@@ -20,7 +20,7 @@ their prefix, and receive them in ``load``.  Adding a part is: subclass,
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Mapping, Optional, Sequence, Tuple, Type
+from typing import Any, Callable, Dict, List, Mapping, NamedTuple, Optional, Sequence, Tuple, Type
 
 import torch
 
@@ -90,6 +90,11 @@ class Part:
 class Norm(Part):
     kind_family = "norm"
 
+    def split_params(self) -> Optional[Tuple[torch.Tensor, float]]:
+        """(weight float32 [hidden], eps) if the norm is y = x / sqrt(mean(x^2) + eps) * weight, so that the
+        products around it may split it between them (``NormSplit``); None otherwise."""
+        return None
+
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
@@ -148,6 +153,16 @@ class StepView:
     """
 
 
+class NormSplit(NamedTuple):
+    """A norm's input as the product before the norm left it, for the product after the norm: the residual rows
+    (already summed and written back) times the norm's weight, and the rows' sums of squares in parts.  The product
+    after the norm multiplies ``scaled`` and scales each row of its result by 1 / sqrt(sum / width + eps), so the
+    norm needs no kernel of its own between two products of a decode step."""
+    scaled: torch.Tensor      # [tokens, hidden], the engine's dtype
+    sumsq: torch.Tensor       # float32 [parts, 32]: sums of squares of the rows' values, a part per 16 columns
+    eps: float
+
+
 class Mixer(Part):
     kind_family = "mixer"
 
@@ -161,6 +176,10 @@ class Mixer(Part):
     # True: ``forward`` takes ``residual=h`` and may add its output to the residual stream itself (in its
     # last product's epilogue), returning None instead of the output
     accumulates = False
+    # True: ``forward`` also takes ``into_norm=(norm weight, eps, the matrix that the part after the norm
+    # multiplies first)`` and may, for steps where that pays, add its output to the residual stream and return a
+    # ``NormSplit`` for the part after the norm (which says ``takes_norm_split``) instead
+    splits_norm = False
 
     def forward(self, x: torch.Tensor, step: "StepView", cache: Any) -> torch.Tensor:
         """x [tokens, hidden] -> [tokens, hidden].  ``cache`` is the view of this run-step's plane.
@@ -181,6 +200,12 @@ def whole_output(out: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 class FeedForward(Part):
     kind_family = "feed_forward"
     accumulates = False   # as for a mixer
+    # True: ``forward`` accepts a ``NormSplit`` in place of the normalised rows, and ``first_weight()`` is the
+    # matrix it multiplies them by
+    takes_norm_split = False
+
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return None
 
     def forward(self, x: torch.Tensor, step: "StepView") -> torch.Tensor:
         raise NotImplementedError

@@ -7,7 +7,7 @@ two), which is why a block hands its last, not yet added, output on as ``delta``
 
 from __future__ import annotations
 
-from .base import Block, register_part
+from .base import Block, NormSplit, register_part
 
 
 class PreNormBlock(Block):
@@ -16,10 +16,20 @@ class PreNormBlock(Block):
     def forward(self, h, delta, step, caches):
         cache = caches["mixer"]
         x = self.mixer_norm.add_forward(h, delta)
-        # a part that can add its output to h in its last product (portions of prompts) returns None
-        a = (self.mixer.forward(x, step, cache, residual=h) if self.mixer.accumulates
-             else self.mixer.forward(x, step, cache))
-        x = self.feed_forward_norm.add_forward(h, a)
+        # a part that can add its output to h in its last product (portions of prompts) returns None; one that
+        # can also leave the norm after it to the product that follows (decode steps) returns a NormSplit
+        into = None
+        if self.mixer.splits_norm and self.feed_forward.takes_norm_split:
+            params = self.feed_forward_norm.split_params()
+            if params is not None:
+                into = (params[0], params[1], self.feed_forward.first_weight())
+        if into is not None:
+            a = self.mixer.forward(x, step, cache, residual=h, into_norm=into)
+        elif self.mixer.accumulates:
+            a = self.mixer.forward(x, step, cache, residual=h)
+        else:
+            a = self.mixer.forward(x, step, cache)
+        x = a if isinstance(a, NormSplit) else self.feed_forward_norm.add_forward(h, a)
         f = (self.feed_forward.forward(x, step, residual=h) if self.feed_forward.accumulates
              else self.feed_forward.forward(x, step))
         return h, f

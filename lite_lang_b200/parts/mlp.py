@@ -15,7 +15,7 @@ from typing import Dict
 import torch
 
 from .. import ops
-from .base import FeedForward, TensorDecl, register_part
+from .base import FeedForward, NormSplit, TensorDecl, register_part
 
 
 class GatedMLP(FeedForward):
@@ -51,9 +51,16 @@ class GatedMLP(FeedForward):
         return self.w_gate_up.numel() * self.w_gate_up.element_size() + self.w_down.numel() * self.w_down.element_size()
 
     accumulates = True
+    takes_norm_split = True
+
+    def first_weight(self):
+        return self.w_gate_up
 
     def forward(self, x, step, residual=None):
-        act = ops.gated_linear(x, self.w_gate_up)
+        if isinstance(x, NormSplit):    # the norm before this part, left to its first product
+            act = ops.gemm_stream_gated_scaled(x.scaled, self.w_gate_up, x.sumsq, x.eps, step.status)
+        else:
+            act = ops.gated_linear(x, self.w_gate_up)
         if residual is not None and ops.accumulate_preferred(act, self.w_down):
             ops.linear_accumulate(act, self.w_down, residual)
             return None

@@ -28,6 +28,9 @@ class RMSNorm(Norm):
     def load(self, fetch, dtype, device) -> None:
         self.weight = fetch("weight").to(torch.float32).to(device).contiguous()
 
+    def split_params(self):
+        return self.weight, self.eps
+
     def forward(self, x, out=None):
         if out is None:
             out = torch.empty_like(x)

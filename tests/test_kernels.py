@@ -746,6 +746,46 @@ def test_gemm_stream_split_over_k_and_summed_by_the_norm(mode, m, n, k, parts):
     assert ops.stream_ksplit(1536, 8960, 2, dev()) == 3 and ops.stream_ksplit(2048, 1536, 2, dev()) == 1
 
 
+@pytest.mark.parametrize("m,hidden,k,inter", [(8, 1536, 1536, 8960), (1, 256, 512, 96), (13, 768, 256, 203),
+                                              (32, 2048, 2048, 320), (16, 3584, 3584, 1184)])
+def test_norm_split_between_the_product_before_and_the_gated_product_after(m, hidden, k, inter):
+    """o projection -> residual sum -> RMS norm -> gated feed-forward product as two kernels: against the plain
+    formulas, and the residual rows bit for bit against the three separate kernels."""
+    from lite_lang_b200 import ops
+    d = dev()
+    g = torch.Generator().manual_seed(61)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(d)
+    w1 = (torch.randn(hidden, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(d)
+    res0 = torch.randn(m, hidden, generator=g).to(torch.bfloat16).to(d)
+    wn = (1 + 0.2 * torch.randn(hidden, generator=g)).to(d)
+    w2 = (2 * torch.randn(2 * inter, hidden, generator=g) / hidden ** 0.5).to(torch.bfloat16).to(d)
+    eps = 1e-5
+    status = torch.zeros(1, dtype=torch.int32, device=d)
+    # the separate kernels
+    res_a = res0.clone()
+    delta = ops.gemm_stream(x, w1, torch.empty(m, hidden, dtype=torch.bfloat16, device=d), 2, status)
+    xa = torch.empty_like(res_a)
+    ops.add_rmsnorm(xa, res_a, delta, wn, eps)
+    act_a = ops.gemm_stream(xa, w2, torch.empty(m, inter, dtype=torch.bfloat16, device=d), 1, status)
+    # the two kernels with the norm split between them
+    res_b = res0.clone()
+    u, sumsq = ops.gemm_stream_into_norm(x, w1, res_b, wn, status)
+    act_b = ops.gemm_stream_gated_scaled(u, w2, sumsq, eps, status)
+    assert status.item() == 0
+    assert torch.equal(res_a, res_b), "the residual rows differ from the separate kernels'"
+    total = sumsq[:, :m].sum(0).double().cpu()
+    want = (res_b.double() ** 2).sum(1).cpu()
+    assert float(((total - want).abs() / want).max()) <= 1e-5
+    assert float((u.float() - res_b.float() * wn).abs().max()) <= 2 ** -8 * float((res_b.float() * wn).abs().max())
+    # the plain formulas on the rounded residual rows
+    h = res_b.float().cpu()
+    xn = P.rms_norm(h, wn.cpu(), eps)
+    ref = P.silu_and_mul(P.linear(xn, w2[:inter].float().cpu()), P.linear(xn, w2[inter:].float().cpu()))
+    assert_close(act_b, ref, torch.bfloat16, "gated product after the split norm")
+    assert_close(act_a, ref, torch.bfloat16, "gated product after the norm kernel")
+    assert float((act_a.float() - act_b.float()).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
 @pytest.mark.parametrize("m,inter,k", [(1, 128, 128), (8, 8960, 1536), (20, 203, 384), (32, 320, 256)])
 def test_gemm_stream_gated(m, inter, k):
     from lite_lang_b200 import ops
