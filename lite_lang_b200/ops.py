@@ -586,16 +586,18 @@ NORM_SPLIT = os.environ.get("LITE_LANG_B200_NORM_SPLIT", "1") != "0"   # 0: the 
                                                                         # stays a kernel of its own (for comparisons)
 
 
-def norm_split_supported(x: torch.Tensor, w_before: torch.Tensor, residual: torch.Tensor,
-                         w_after: torch.Tensor) -> bool:
-    """Whether the norm between the product ``x @ w_before.T`` (added to ``residual``) and the gated product with
-    ``w_after`` can be split between the two (``gemm_stream_into_norm``, ``gemm_stream_gated_scaled``): both
-    streaming products of a decode step, the first with units of 16 features and an unsplit k."""
+def into_norm_supported(x: torch.Tensor, w_before: torch.Tensor, residual: torch.Tensor) -> bool:
+    """Whether ``gemm_stream_into_norm`` takes the product ``x @ w_before.T`` added to ``residual``: a streaming
+    product of a decode step with units of 16 features and an unsplit k, bfloat16 residual rows of its shape."""
     n = w_before.shape[0]
     return (NORM_SPLIT and stream_mode(x, w_before) == 2 and n % 16 == 0 and residual.dtype == torch.bfloat16
-            and residual.dim() == 2 and tuple(residual.shape) == (x.shape[0], n) and residual.stride(1) == 1
-            and w_after.dtype == torch.bfloat16 and w_after.shape[1] == n and n % 128 == 0 and w_after.is_contiguous()
-            and w_after.data_ptr() % 16 == 0 and not tc_preferred(residual, w_after, gated=True))
+            and residual.dim() == 2 and tuple(residual.shape) == (x.shape[0], n) and residual.stride(1) == 1)
+
+
+def gated_scaled_supported(rows: torch.Tensor, w_gate_up: torch.Tensor) -> bool:
+    """Whether ``gemm_stream_gated_scaled`` takes rows of this shape: where the streaming gated product runs."""
+    return (NORM_SPLIT and stream_mode(rows, w_gate_up, gated=True) == 1 and w_gate_up.shape[1] == rows.shape[1]
+            and not tc_preferred(rows, w_gate_up, gated=True))
 
 
 def gemm_stream_into_norm(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor,
@@ -607,9 +609,8 @@ def gemm_stream_into_norm(x: torch.Tensor, weight: torch.Tensor, residual: torch
     _need_cuda(x, weight, residual, norm_weight, status)
     m, k = x.shape
     n = weight.shape[0]
-    _need(stream_mode(x, weight) == 2 and n % 16 == 0, "gemm_stream_into_norm: bfloat16, at most 32 tokens, K % 256 == 0, N % 16 == 0")
-    _need(residual.dtype == torch.bfloat16 and tuple(residual.shape) == (m, n) and residual.stride(1) == 1,
-          "gemm_stream_into_norm: residual is bfloat16 [tokens, out]")
+    _need(into_norm_supported(x, weight, residual), "gemm_stream_into_norm: bfloat16, at most 32 tokens, K % 256 == 0, "
+                                                    "N % 16 == 0, residual bfloat16 [tokens, N]")
     _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == n and norm_weight.is_contiguous(),
           "gemm_stream_into_norm: the norm's weight is float32 [out]")
     u = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)

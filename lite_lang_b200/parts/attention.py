@@ -100,11 +100,11 @@ class GQAttention(Mixer):
         if residual is not None and ops.accumulate_preferred(attn, self.w_o):
             ops.linear_accumulate(attn, self.w_o, residual)
             return None
-        if (residual is not None and into_norm is not None and into_norm[2] is not None
-                and ops.norm_split_supported(attn, self.w_o, residual, into_norm[2])):
+        if (residual is not None and into_norm is not None and ops.into_norm_supported(attn, self.w_o, residual)
+                and into_norm.accepts(residual)):
             # decode: the o projection adds into the residual stream and leaves the norm after it to the next product
-            u, sumsq = ops.gemm_stream_into_norm(attn, self.w_o, residual, into_norm[0], status)
-            return NormSplit(u, sumsq, into_norm[1])
+            u, sumsq = ops.gemm_stream_into_norm(attn, self.w_o, residual, into_norm.weight, status)
+            return NormSplit(u, sumsq, into_norm.eps)
         return ops.linear(attn, self.w_o, partial_ok=True)
 
     def forward(self, x, step, cache, residual=None, into_norm=None):

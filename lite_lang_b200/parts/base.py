@@ -153,6 +153,15 @@ class StepView:
     """
 
 
+class NormEntry(NamedTuple):
+    """What the product before a norm has to know to prepare the norm's input for the part after the norm
+    (``NormSplit``): the norm's weight and eps, and whether that part takes such an input for rows shaped like the
+    residual rows it is asked about."""
+    weight: torch.Tensor                          # float32 [hidden]
+    eps: float
+    accepts: Callable[[torch.Tensor], bool]
+
+
 class NormSplit(NamedTuple):
     """A norm's input as the product before the norm left it, for the product after the norm: the residual rows
     (already summed and written back) times the norm's weight, and the rows' sums of squares in parts.  The product
@@ -176,9 +185,9 @@ class Mixer(Part):
     # True: ``forward`` takes ``residual=h`` and may add its output to the residual stream itself (in its
     # last product's epilogue), returning None instead of the output
     accumulates = False
-    # True: ``forward`` also takes ``into_norm=(norm weight, eps, the matrix that the part after the norm
-    # multiplies first)`` and may, for steps where that pays, add its output to the residual stream and return a
-    # ``NormSplit`` for the part after the norm (which says ``takes_norm_split``) instead
+    # True: ``forward`` also takes ``into_norm=NormEntry`` (the norm after this part and what comes after it) and
+    # may, for steps where that pays and the part after the norm accepts it, add its output to the residual stream
+    # and return a ``NormSplit`` instead
     splits_norm = False
 
     def forward(self, x: torch.Tensor, step: "StepView", cache: Any) -> torch.Tensor:
@@ -200,12 +209,12 @@ def whole_output(out: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 class FeedForward(Part):
     kind_family = "feed_forward"
     accumulates = False   # as for a mixer
-    # True: ``forward`` accepts a ``NormSplit`` in place of the normalised rows, and ``first_weight()`` is the
-    # matrix it multiplies them by
+    # True: ``forward`` accepts a ``NormSplit`` in place of the normalised rows where ``accepts_norm_split`` says so
     takes_norm_split = False
 
-    def first_weight(self) -> Optional[torch.Tensor]:
-        return None
+    def accepts_norm_split(self, rows: torch.Tensor) -> bool:
+        """Whether a ``NormSplit`` may stand for normalised rows shaped like ``rows`` (the residual rows) in this step."""
+        return False
 
     def forward(self, x: torch.Tensor, step: "StepView") -> torch.Tensor:
         raise NotImplementedError

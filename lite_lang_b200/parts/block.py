@@ -7,7 +7,7 @@ two), which is why a block hands its last, not yet added, output on as ``delta``
 
 from __future__ import annotations
 
-from .base import Block, NormSplit, register_part
+from .base import Block, NormEntry, NormSplit, register_part
 
 
 class PreNormBlock(Block):
@@ -22,7 +22,7 @@ class PreNormBlock(Block):
         if self.mixer.splits_norm and self.feed_forward.takes_norm_split:
             params = self.feed_forward_norm.split_params()
             if params is not None:
-                into = (params[0], params[1], self.feed_forward.first_weight())
+                into = NormEntry(params[0], params[1], self.feed_forward.accepts_norm_split)
         if into is not None:
             a = self.mixer.forward(x, step, cache, residual=h, into_norm=into)
         elif self.mixer.accumulates:

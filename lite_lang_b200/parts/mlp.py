@@ -53,8 +53,8 @@ class GatedMLP(FeedForward):
     accumulates = True
     takes_norm_split = True
 
-    def first_weight(self):
-        return self.w_gate_up
+    def accepts_norm_split(self, rows) -> bool:
+        return ops.gated_scaled_supported(rows, self.w_gate_up)
 
     def forward(self, x, step, residual=None):
         if isinstance(x, NormSplit):    # the norm before this part, left to its first product

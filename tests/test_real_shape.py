@@ -169,3 +169,64 @@ def test_other_model_sizes_in_bfloat16(size, tmp_path):
         assert rel_err(lg, ref[k:k + 1]) <= TOL["bfloat16"], i
     runner.check_status()
     assert runner.graph_replays == n_dec
+
+
+def test_decode_steps_split_the_norm_after_the_attention_between_two_products(model, monkeypatch):
+    """In bfloat16 decode steps of up to 16 tokens the norm after the attention has no kernel of its own: the o
+    projection leaves its input ready (``ops.gemm_stream_into_norm``) and the gated product applies the rows'
+    factors.  The steps' logits equal the plain ones, and those of the same steps with the norm as a kernel of its
+    own (``ops.NORM_SPLIT`` off) up to bfloat16 rounding; a portion of a prompt in the same step switches it off."""
+    from lite_lang_b200 import ops
+    from lite_lang_b200.cache import CacheManager
+    from lite_lang_b200.config import load_config
+    from lite_lang_b200.engine.batch import StepEntry
+    from lite_lang_b200.engine.model import CausalLM
+    from lite_lang_b200.engine.runner import ModelRunner
+    from lite_lang_b200.weights import load_weights
+
+    folder, toks, ref = model
+    dev = torch.device("cuda:0")
+    m = CausalLM(load_config(folder).model_spec())
+    load_weights(m, folder, torch.bfloat16, dev)
+    calls = {"into_norm": 0, "scaled": 0}
+    real_into, real_scaled = ops.gemm_stream_into_norm, ops.gemm_stream_gated_scaled
+
+    def into(*a, **k):
+        calls["into_norm"] += 1
+        return real_into(*a, **k)
+
+    def scaled(*a, **k):
+        calls["scaled"] += 1
+        return real_scaled(*a, **k)
+
+    monkeypatch.setattr(ops, "gemm_stream_into_norm", into)
+    monkeypatch.setattr(ops, "gemm_stream_gated_scaled", scaled)
+    layers = m.spec.num_layers if hasattr(m.spec, "num_layers") else len(m.blocks)
+
+    def run(split):
+        monkeypatch.setattr(ops, "NORM_SPLIT", split)
+        mgr = CacheManager(m.cache_groups, [32], 16, 8, 256)
+        runner = ModelRunner(m, mgr, dev, 128, cuda_graphs=False)
+        a, b = mgr.open(), mgr.open()
+        assert runner.reserve(a, 40) and runner.reserve(b, 9)
+        first_calls = dict(calls)
+        runner.step([StepEntry(a, toks[:40], ()), StepEntry(b, toks[:9], ())])
+        before = dict(calls)
+        if split:      # (a step with portions of prompts, 49 tokens, keeps the norm's own kernel)
+            assert first_calls == before, (first_calls, before)
+        out = []
+        for i in range(3):     # two requests, a token each: the split path
+            assert runner.reserve(a, 1) and runner.reserve(b, 1)
+            out.append(runner.step([StepEntry(a, [toks[40 + i]], (0,)), StepEntry(b, [toks[9 + i]], (0,))]).float().cpu().numpy())
+        during = {k: calls[k] - before[k] for k in calls}
+        runner.check_status()
+        return np.concatenate(out), during
+
+    got_split, n_split = run(True)
+    got_whole, n_whole = run(False)
+    assert n_split == {"into_norm": 3 * layers, "scaled": 3 * layers}, n_split
+    assert n_whole == {"into_norm": 0, "scaled": 0}
+    want = np.concatenate([np.stack([ref[40 + i], ref[9 + i]]) for i in range(3)])
+    assert rel_err(got_split, want) <= TOL["bfloat16"]
+    assert rel_err(got_whole, want) <= TOL["bfloat16"]
+    assert rel_err(got_split, got_whole) <= TOL["bfloat16"]
