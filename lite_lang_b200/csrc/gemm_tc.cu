@@ -102,6 +102,12 @@ struct TcParams {
   int ksplit;    // > 1: out is float32 [ksplit, M, N] partial sums
   int cpp;       // 64-wide k boxes per part
   int vec_ok;    // the output takes 16-byte pieces (aligned base and stride, N a multiple of the piece)
+  // SCALED (gated, at most 32 tokens): the tokens' rows are only multiplied by the weight of the norm before this
+  // product yet; the rows' sums of squares come in parts [sumsq_units][32] (see gemm_stream.cu: the product before
+  // the norm leaves them), and each row of the result is scaled by 1 / sqrt(sum / K + eps) before the activation
+  const float* sumsq_in;
+  int sumsq_units;
+  float norm_eps;
   int* status;
 };
 
@@ -118,8 +124,8 @@ struct TcShape {
   static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + XCH_BYTES;
 };
 
-// OUT: 0 bfloat16, 1 float32 (also the partial sums)
-template <int MODE, int NT, int OUT>
+// OUT: 0 bfloat16, 1 float32 (also the partial sums); SCALED: see TcParams
+template <int MODE, int NT, int OUT, bool SCALED>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap) {
   using S = TcShape<MODE, NT>;
@@ -255,6 +261,21 @@ gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const
     LL_PDL_WAIT();
     const int ew = warp & 3;               // the 32 tensor-memory lanes this warp may read: 32 ew .. 32 ew + 31
     const int feat_in_unit = 32 * ew + lane;
+    // SCALED: the rows' factors, made while the weights stream and the MMAs run: thread (quarter ew, token lane)
+    // adds the units ew, ew + 4, ... of its token, the quarters meet in shared memory (a fixed order)
+    __shared__ float row_part[SCALED ? 4 : 1][32];
+    __shared__ float row_scale[SCALED ? 32 : 1];
+    if (SCALED) {
+      float part = 0.f;
+#pragma unroll 8
+      for (int un = ew; un < p.sumsq_units; un += 4) part += p.sumsq_in[(size_t)un * 32 + lane];
+      row_part[ew][lane] = part;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ew == 0)
+        row_scale[lane] = 1.0f / sqrtf((row_part[0][lane] + row_part[1][lane] + row_part[2][lane] + row_part[3][lane]) /
+                                           (float)p.K + p.norm_eps);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     int unit_no = 0;
     for (int uu = blockIdx.x; uu < p.units; uu += gridDim.x, ++unit_no) {
       const int u = uu / p.ksplit, kp = uu % p.ksplit;
@@ -285,8 +306,9 @@ gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const
         const float a = stg[fl * (NT + 1) + t];
         if (MODE == TC_MODE_GATED) {
           // gate and up rounded to bfloat16 first, as the unfused path does between product and activation
-          const float gt = __bfloat162float(__float2bfloat16_rn(a));
-          const float uv = __bfloat162float(__float2bfloat16_rn(stg[(64 + fl) * (NT + 1) + t]));
+          const float rs = SCALED ? row_scale[t & 31] : 1.0f;
+          const float gt = __bfloat162float(__float2bfloat16_rn(a * rs));
+          const float uv = __bfloat162float(__float2bfloat16_rn(stg[(64 + fl) * (NT + 1) + t] * rs));
           // (x * rcp(y), not the IEEE division: that is a chain of dependent instructions with a branch an element)
           return __fdividef(gt, 1.0f + __expf(-gt)) * uv;
         }
@@ -369,7 +391,7 @@ static int tc_make_map(CUtensorMap* map, const void* base, long rows, long K, lo
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int MODE, int NT, int OUT>
+template <int MODE, int NT, int OUT, bool SCALED = false>
 static int tc_launch(const TcParams& p, const void* w, const void* x, long x_stride, int sm_count, cudaStream_t stream) {
   constexpr bool GATED = MODE == TC_MODE_GATED;
   CUtensorMap wmap, xmap;
@@ -377,18 +399,21 @@ static int tc_launch(const TcParams& p, const void* w, const void* x, long x_str
   if (rc == 0) rc = tc_make_map(&xmap, x, p.M, p.K, x_stride, NT);
   if (rc != 0) return rc;
   const size_t smem = TcShape<MODE, NT>::SMEM;
-  cudaFuncSetAttribute(gemm_tc_kernel<MODE, NT, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaFuncSetAttribute(gemm_tc_kernel<MODE, NT, OUT, SCALED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const int grid = p.units < sm_count ? p.units : sm_count;
-  ll_launch(gemm_tc_kernel<MODE, NT, OUT>, dim3(grid), dim3(TC_THREADS), smem, stream, p, wmap, xmap);
+  ll_launch(gemm_tc_kernel<MODE, NT, OUT, SCALED>, dim3(grid), dim3(TC_THREADS), smem, stream, p, wmap, xmap);
   return LL_LAUNCH_RESULT();
 }
 
 // x: bfloat16 [M, K] (row stride x_stride, a multiple of 8); w: bfloat16 [N, K] contiguous (gated: [2 N, K],
 // gate rows first); out: bfloat16 [M, N], or float32 with out_f32 = 1; ksplit > 1: out is float32
 // [ksplit, M, N] partial sums (out_stride = N).  33 <= M <= 128 is what it is meant for; any M <= 128 works.
+// sumsq (gated, M <= 32; or null): see TcParams.
 extern "C" int ll_gemm_tc(void* out, long out_stride, int out_f32, const void* x, long x_stride, const void* w, int M,
-                          int N, int K, int gated, int ksplit, int sm_count, int* status, cudaStream_t stream) {
+                          int N, int K, int gated, int ksplit, int sm_count, const float* sumsq, int sumsq_units,
+                          float norm_eps, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  if (sumsq != nullptr && (!gated || M > 32 || sumsq_units <= 0)) return (int)cudaErrorInvalidValue;
   if (M > 128 || K <= 0 || (K % 64) != 0 || (x_stride % 8) != 0 || sm_count <= 0 || ksplit < 1)
     return (int)cudaErrorInvalidValue;
   if ((ksplit > 1 && (!out_f32 || gated)) || (gated && out_f32)) return (int)cudaErrorInvalidValue;
@@ -399,6 +424,9 @@ extern "C" int ll_gemm_tc(void* out, long out_stride, int out_f32, const void* x
   p.N = N;
   p.K = K;
   p.status = status;
+  p.sumsq_in = sumsq;
+  p.sumsq_units = sumsq_units;
+  p.norm_eps = norm_eps;
   p.cpp = (K / 64 + ksplit - 1) / ksplit;
   p.ksplit = (K / 64 + p.cpp - 1) / p.cpp;
   if (p.ksplit != ksplit) return (int)cudaErrorInvalidValue;
@@ -408,6 +436,7 @@ extern "C" int ll_gemm_tc(void* out, long out_stride, int out_f32, const void* x
   }
   p.units = gated ? (N + 63) / 64 : ((N + 127) / 128) * p.ksplit;
   const bool wide = M > 64;
+  if (gated && sumsq != nullptr) return tc_launch<TC_MODE_GATED, 64, 0, true>(p, w, x, x_stride, sm_count, stream);
   if (gated) {
     return wide ? tc_launch<TC_MODE_GATED, 128, 0>(p, w, x, x_stride, sm_count, stream)
                 : tc_launch<TC_MODE_GATED, 64, 0>(p, w, x, x_stride, sm_count, stream);

@@ -596,8 +596,11 @@ def into_norm_supported(x: torch.Tensor, w_before: torch.Tensor, residual: torch
 
 def gated_scaled_supported(rows: torch.Tensor, w_gate_up: torch.Tensor) -> bool:
     """Whether ``gemm_stream_gated_scaled`` takes rows of this shape: where the streaming gated product runs."""
-    return (NORM_SPLIT and stream_mode(rows, w_gate_up, gated=True) == 1 and w_gate_up.shape[1] == rows.shape[1]
-            and not tc_preferred(rows, w_gate_up, gated=True))
+    if not (NORM_SPLIT and w_gate_up.shape[1] == rows.shape[1] and rows.shape[0] <= SUMSQ_ROWS):
+        return False
+    if tc_preferred(rows, w_gate_up, gated=True):      # 17 tokens and more: the tcgen05 kernel has the same epilogue
+        return True
+    return stream_mode(rows, w_gate_up, gated=True) == 1
 
 
 def gemm_stream_into_norm(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor,
@@ -629,10 +632,12 @@ def gemm_stream_gated_scaled(u: torch.Tensor, w_gate_up: torch.Tensor, sumsq: to
     _need_cuda(u, w_gate_up, sumsq, status)
     m, k = u.shape
     inter = w_gate_up.shape[0] // 2
-    _need(stream_mode(u, w_gate_up, gated=True) == 1, "gemm_stream_gated_scaled: bfloat16, at most 32 tokens, K % 128 == 0")
+    _need(gated_scaled_supported(u, w_gate_up), "gemm_stream_gated_scaled: bfloat16, at most 32 tokens, K % 128 == 0")
     _need(sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.shape[1] == SUMSQ_ROWS and sumsq.is_contiguous(),
           "gemm_stream_gated_scaled: sums of squares are float32 [units, 32]")
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=u.device)
+    if tc_preferred(u, w_gate_up, gated=True):
+        return gemm_tc(u, w_gate_up, act, gated=True, status=status, sumsq=sumsq, eps=eps)
     load_library("gemm_stream").call(
         "ll_gemm_stream_gated_scaled", _ptr(act), c_long(act.stride(0)), _ptr(u), c_long(u.stride(0)), _ptr(w_gate_up),
         c_int(m), c_int(inter), c_int(k), _ptr(sumsq), c_int(sumsq.shape[0]), c_float(eps),
@@ -729,7 +734,7 @@ def tc_ksplit(n: int, k: int, device) -> int:
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False,
-            status: Optional[torch.Tensor] = None) -> torch.Tensor:
+            status: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None, eps: float = 0.0) -> torch.Tensor:
     """out = x @ weight.T for up to 128 bfloat16 tokens on the tcgen05 tensor cores (weights streamed
     by TMA, accumulator in tensor memory).  ``gated``: weight is [2 I, K] and out = silu(gate) * up.
     A float32 ``out`` of shape [parts, M, N] receives the partial sums of a k range cut into parts."""
@@ -752,7 +757,8 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: boo
     load_library("gemm_tc").call(
         "ll_gemm_tc", _ptr(out), c_long(out_stride), c_int(1 if out.dtype == torch.float32 else 0), _ptr(x),
         c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(1 if gated else 0), c_int(ksplit),
-        c_int(sm_count(x.device)), _ptr(status), _stream())
+        c_int(sm_count(x.device)), _ptr(sumsq), c_int(0 if sumsq is None else sumsq.shape[0]), c_float(eps),
+        _ptr(status), _stream())
     return out
 
 
