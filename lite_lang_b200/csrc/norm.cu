@@ -95,7 +95,24 @@ add_rmsnorm_bf16x8_kernel(bf16* __restrict__ out, bf16* __restrict__ residual, c
   for (int k = 0; k < 8; ++k) v[k] = 0.f;
   if (active) {
     bf16* res = residual + (size_t)r * hidden + i0;
+    // every load of the row's piece is asked for before the first one is used: the residual values, the delta or
+    // the first four parts of a split product (a chain of a trip to L2 a part otherwise, in the middle of the step's
+    // chain of kernels)
     const uint4 rv = *reinterpret_cast<const uint4*>(res);
+    uint4 dv = make_uint4(0u, 0u, 0u, 0u);
+    float4 pa[4], pb[4];
+    const float* par = partial ? partial + (size_t)r * hidden + i0 : nullptr;
+    if (delta) {
+      dv = *reinterpret_cast<const uint4*>(delta + (size_t)r * hidden + i0);
+    } else if (partial) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (q < parts) {
+          pa[q] = *reinterpret_cast<const float4*>(par + (size_t)q * part_stride);
+          pb[q] = *reinterpret_cast<const float4*>(par + (size_t)q * part_stride + 4);
+        }
+      }
+    }
     const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -105,7 +122,6 @@ add_rmsnorm_bf16x8_kernel(bf16* __restrict__ out, bf16* __restrict__ residual, c
     }
     bool changed = false;
     if (delta) {
-      const uint4 dv = *reinterpret_cast<const uint4*>(delta + (size_t)r * hidden + i0);
       const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -118,8 +134,14 @@ add_rmsnorm_bf16x8_kernel(bf16* __restrict__ out, bf16* __restrict__ residual, c
       float d[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) d[k] = 0.f;
-      const float* par = partial + (size_t)r * hidden + i0;
-      for (int q = 0; q < parts; ++q) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {     // (the same order of additions as a plain loop over the parts)
+        if (q < parts) {
+          d[0] += pa[q].x; d[1] += pa[q].y; d[2] += pa[q].z; d[3] += pa[q].w;
+          d[4] += pb[q].x; d[5] += pb[q].y; d[6] += pb[q].z; d[7] += pb[q].w;
+        }
+      }
+      for (int q = 4; q < parts; ++q) {
         const float4 a = *reinterpret_cast<const float4*>(par + (size_t)q * part_stride);
         const float4 b = *reinterpret_cast<const float4*>(par + (size_t)q * part_stride + 4);
         d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
