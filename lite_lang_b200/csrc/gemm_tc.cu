@@ -165,6 +165,8 @@ gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem = *tmem_slot;
   LL_PDL_TRIGGER();
+  [[maybe_unused]] constexpr int TL_KERNEL = MODE == TC_MODE_GATED ? 3 : 4;   // (the logits, wide and unsplit: 5)
+  LL_TIMELINE_STAMP(p.status, (MODE == TC_MODE_PLAIN && p.ksplit == 1) ? 5 : TL_KERNEL, 0);
 
   bool dead = false;
   const int kboxes = p.K / 64;
@@ -259,6 +261,14 @@ gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const
   } else {
     // ------------------------------ epilogue (warps 2..5) ------------------------------
     LL_PDL_WAIT();
+#ifdef LL_TIMELINE
+    if (tid == 64) {   // (the stamp is thread 0's in the other kernels; here the first epilogue thread's)
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (p.status != nullptr && blockIdx.x < LL_TIMELINE_CTAS)
+        reinterpret_cast<unsigned long long*>(p.status + 4)[((size_t)((MODE == TC_MODE_PLAIN && p.ksplit == 1) ? 5 : TL_KERNEL) * LL_TIMELINE_CTAS + blockIdx.x) * 4 + 1] = t;
+    }
+#endif
     const int ew = warp & 3;               // the 32 tensor-memory lanes this warp may read: 32 ew .. 32 ew + 31
     const int feat_in_unit = 32 * ew + lane;
     // SCALED: the rows' factors, made while the weights stream and the MMAs run: thread (quarter ew, token lane)
@@ -355,6 +365,7 @@ gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const
   // ---- everyone is done: free the tensor memory ----
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  LL_TIMELINE_STAMP(p.status, (MODE == TC_MODE_PLAIN && p.ksplit == 1) ? 5 : TL_KERNEL, 2);
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((unsigned)TMEM_COLS) : "memory");

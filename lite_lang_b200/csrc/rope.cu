@@ -112,7 +112,9 @@ bias_rope_store_bf16x8_kernel(bf16* __restrict__ qkv, long qkv_stride, const flo
                               int nkv, int hd, const int* __restrict__ slot_map, bf16* __restrict__ k_cache,
                               bf16* __restrict__ v_cache, int page_size, long num_slots, int* status) {
   LL_PDL_TRIGGER();
+  LL_TIMELINE_STAMP(status, 0, 0);   // (where the projection is a library product, this kernel stands for q|k|v)
   LL_PDL_WAIT();
+  LL_TIMELINE_STAMP(status, 0, 1);
   const int t = blockIdx.x;
   bf16* row = qkv + (size_t)t * qkv_stride;
   int pos = positions[t];
@@ -190,6 +192,7 @@ bias_rope_store_bf16x8_kernel(bf16* __restrict__ qkv, long qkv_stride, const flo
         *reinterpret_cast<uint4*>(v_cache + (((size_t)page * nkv + h) * page_size + off) * hd + j0) = a;
     }
   }
+  LL_TIMELINE_STAMP(status, 0, 2);
 }
 
 // qkv: [num_tokens, (nh + 2 nkv) * hd] with row stride qkv_stride (elements).

@@ -758,7 +758,7 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: boo
         "ll_gemm_tc", _ptr(out), c_long(out_stride), c_int(1 if out.dtype == torch.float32 else 0), _ptr(x),
         c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(1 if gated else 0), c_int(ksplit),
         c_int(sm_count(x.device)), _ptr(sumsq), c_int(0 if sumsq is None else sumsq.shape[0]), c_float(eps),
-        _ptr(status), _stream())
+        _ptr(status if status is not None else TIMELINE_STATUS), _stream())
     return out
 
 
