@@ -20,7 +20,7 @@
 // its weights: a second tensor map (of x, boxes of 8..32 rows x 64 k) puts them behind the
 // weight boxes of the stage, after griddepcontrol.wait (the weights start before it).
 //
-// Three shapes of work unit:
+// Four shapes of work unit:
 //   WIDE    64 output features x all of K; a stage is 64 rows x 128 k (two boxes); warp w
 //           owns rows 16 w .. 16 w + 15.  For wide products (lm_head).
 //   GATED   32 features of the SiLU-gated feed-forward; W is [2 I, K], gate rows first.
@@ -36,6 +36,13 @@
 //   NARROW  16 features x all of K; a stage is 16 rows x 256 k (four boxes) and warp w takes
 //           one box; the four partial tiles are added through shared memory.  For
 //           products with few output features (q|k|v, o, down), where units, not k, are scarce.
+//
+// Two of them have a variant (template flag SPLIT) that takes over half of an RMS norm that lies between two
+// products of a decode step, so that the norm is no kernel, and no link of the step's chain of dependent
+// launches, of its own: NARROW adds its result to the residual rows, writes them times the norm's weight
+// and leaves each row's sum of squares in parts of 16 columns; GATED multiplies those rows, and a sixth warp
+// adds the parts up into the rows' factors 1 / sqrt(mean + eps) meanwhile, which the epilogue applies before the
+// activation (see GtParams).
 //
 // Every wait on an mbarrier is bounded (about two seconds of clock); a wait that runs out
 // sets LL_ERR_WAIT_TIMEOUT in the status word and the kernel carries on to its end.
