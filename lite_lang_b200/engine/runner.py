@@ -76,10 +76,15 @@ class ModelRunner:
         self.builder = BatchBuilder(manager, max_tokens_per_step, manager.max_requests, device, self.status)
         self.single_builder = BatchBuilder(manager, manager.max_requests, manager.max_requests, device, self.status)
         self.use_graphs = bool(cuda_graphs)
-        self._graphs: Dict[int, tuple] = {}
+        self._graphs: Dict[tuple, tuple] = {}     # (batch bucket, class of context length) -> (graph, logits)
         self._graph_pool = None
         self.graph_kernel_launches: Dict[int, int] = {}   # hand-written kernels inside each captured step
         self._bucket_list = _buckets(manager.max_requests)
+        # A captured step's kernels are planned (splits of the keys, warps) for the longest context that may be
+        # replayed through the graph; so that short contexts are not run with a long one's plan and the other way
+        # round, a batch size has a graph per class of context length: up to 1,024 tokens, 4,096, 16,384, ...
+        self._context_classes = [c for c in (1 << k for k in range(10, 31, 2)) if c < manager.max_model_len]
+        self._context_classes.append(manager.max_model_len)
         self.steps_run = 0
         self.graph_replays = 0
 
@@ -115,9 +120,16 @@ class ModelRunner:
                 return b
         return self._bucket_list[-1]
 
-    def _capture(self, bucket: int):
+    def _context_class(self, longest: int) -> int:
+        for c in self._context_classes:
+            if c >= longest:
+                return c
+        return self._context_classes[-1]
+
+    def _capture(self, bucket: int, context: Optional[int] = None):
+        context = self.manager.max_model_len if context is None else context
         batch = self.single_builder.build([], pad_entries=bucket)
-        batch.max_kv_len = self.manager.max_model_len
+        batch.max_kv_len = context
         batch.captured = True
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
@@ -138,22 +150,25 @@ class ModelRunner:
         self.graph_kernel_launches[bucket] = _build.LAUNCHES - before
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
-        self._graphs[bucket] = (graph, logits)
-        return self._graphs[bucket]
+        self._graphs[(bucket, context)] = (graph, logits)
+        return self._graphs[(bucket, context)]
 
     def capture_all(self) -> None:
-        """Capture every bucket now (largest first, so that the pool is sized once)."""
+        """Capture every bucket and class of context length now (largest first, so that the pool is sized once)."""
         if not self.use_graphs:
             return
         for b in sorted(self._bucket_list, reverse=True):
-            if b not in self._graphs:
-                self._capture(b)
+            for c in sorted(self._context_classes, reverse=True):
+                if (b, c) not in self._graphs:
+                    self._capture(b, c)
 
     def _step_graph(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
         bucket = self._bucket(len(entries))
-        got = self._graphs.get(bucket)
+        m = self.manager
+        context = self._context_class(max(m.length(e.slot) for e in entries) + 1)
+        got = self._graphs.get((bucket, context))
         if got is None:
-            got = self._capture(bucket)
+            got = self._capture(bucket, context)
         graph, logits = got
         batch = self.single_builder.build(entries, pad_entries=bucket, views=False)
         graph.replay()

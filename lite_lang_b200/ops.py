@@ -223,6 +223,22 @@ def attn_mma_scratch_floats(row_blocks: int, num_kv_heads: int, nsplit: int, hea
     return row_blocks * num_kv_heads * nsplit * 16 * (head_dim + 2)
 
 
+_attn_mma_scratch = {}    # per device: (partial results, counters) of attn_mma's splits that meet through memory
+
+
+def attn_mma_scratch(device, row_blocks: int, num_kv_heads: int, nsplit: int, head_dim: int):
+    """Scratch memory and counters (zero, and left zero by the kernel) for ``attn_mma`` with ``nsplit`` parts that
+    meet through memory; kept by this module, grown when needed (a captured step runs twice before its capture,
+    so nothing grows while a graph is recorded)."""
+    floats = attn_mma_scratch_floats(row_blocks, num_kv_heads, nsplit, head_dim)
+    have = _attn_mma_scratch.get(device)
+    if have is None or have[0].numel() < floats or have[1].numel() < row_blocks * num_kv_heads:
+        have = (torch.empty(max(floats, have[0].numel() if have else 0), dtype=torch.float32, device=device),
+                torch.zeros(max(row_blocks * num_kv_heads, 1024), dtype=torch.int32, device=device))
+        _attn_mma_scratch[device] = have
+    return have
+
+
 def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
              block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
              num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,

@@ -152,6 +152,8 @@ class GQAttention(Mixer):
         """Row blocks, splits and warps of the decode kernel for ``entries`` single-token entries on a
         device of ``sms`` SMs."""
         group = self.num_heads // self.num_kv_heads
+        if self.window:
+            max_kv_len = min(max_kv_len, int(self.window) + 16)     # (the keys a token of a windowed layer may see)
         max_tiles = (max_kv_len + 15) // 16
         if group <= 8:
             # attn_decode: one CTA per (entry, kv head, split).  Measured on a B200 (148 SMs; 1.5B sizes, context
@@ -161,13 +163,23 @@ class GQAttention(Mixer):
             # within 1 % of it at context 8k (batch 2 and 8).
             base = entries * self.num_kv_heads
             most = (sms * 7) // 8
+            if base * 8 <= sms // 4 and max_tiles >= 8 * 128:
+                # Very few requests with very long contexts: 8 splits (the most a cluster takes) leave most SMs
+                # without work and every CTA with thousands of keys.  attn_mma cuts the keys into up to 32 parts
+                # that meet through scratch memory instead (context 32k: batch 1 35 -> 20 us a layer, batch 2
+                # 35 -> 21 us; at 8k and below the clusters are ahead: 11 against 13 us).
+                nsplit = 32
+                while nsplit > 8 and (base * nsplit > most or max_tiles // nsplit < 16):
+                    nsplit //= 2
+                if nsplit > 8:
+                    return entries, nsplit, True, 8, "scratch"
             nsplit = 1
             for n in (8, 4, 2):
                 if base * n <= most and n <= max(1, max_tiles // 8):
                     nsplit = n
                     break
             warps = 4 if (nsplit == 8 and base * nsplit > most // 2) else 8
-            return entries, nsplit, True, warps
+            return entries, nsplit, True, warps, "decode"
         blocks = entries * ((group + 15) // 16)
         ctas = blocks * self.num_kv_heads
         # attn_mma: one wave of CTAs at most, and at least 8 tiles (128 keys) a split: with less, merging the
@@ -181,7 +193,7 @@ class GQAttention(Mixer):
         # behind.  Not beyond half the SMs: 8-warp CTAs fit one an SM, and clusters of 8 of them then
         # no longer find room in one wave
         warps = 8 if ctas * nsplit <= sms // 2 and max_tiles >= 16 * nsplit else 4
-        return blocks, nsplit, group <= 16, warps
+        return blocks, nsplit, group <= 16, warps, "cluster"
 
     def attend(self, out, qkv, step, cache) -> None:
         """Attention of the step's tokens over the cache plane; picks the kernels by shape.
@@ -198,8 +210,13 @@ class GQAttention(Mixer):
                 plan = step.scratch.get(key)
                 if plan is None:
                     plan = step.scratch[key] = self._plan_mma(step, n_single, step.max_kv_len, ops.sm_count(qkv.device))
-                blocks, nsplit, single, warps = plan
-                if self.num_heads // self.num_kv_heads <= 8:
+                blocks, nsplit, single, warps, how = plan
+                if how == "scratch":
+                    scratch, counters = ops.attn_mma_scratch(qkv.device, blocks, self.num_kv_heads, nsplit, self.head_dim)
+                    ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q,
+                                 step.ctx_len, step.req_slot, n_single, blocks, *args, nsplit, scratch, counters,
+                                 step.status, all_single=single, cluster=False, warps=warps)
+                elif how == "decode":
                     # keys on the M side, the group's heads on the N side of the MMA: half the work a tile
                     ops.attn_decode(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.ctx_len,
                                     step.req_slot, n_single, *args, nsplit, step.status, warps=warps)

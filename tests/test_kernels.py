@@ -466,10 +466,12 @@ def test_attn_prefill_tc_finds_one_far_key(where):
     assert (float(c["ref"][-1].mean()) > 4.5) == (where != "window_out")
 
 
-@pytest.mark.parametrize("nsplit,cluster", [(1, False), (5, False), (8, True)])
+@pytest.mark.parametrize("nsplit,cluster", [(1, False), (5, False), (8, True), (32, False)])
 @pytest.mark.parametrize("where", ["first", "page_edge", "last_of_page", "window_in", "window_out"])
 def test_attn_mma_finds_one_far_key(where, nsplit, cluster):
     nh, nkv, hd, ps, L, window = 12, 2, 128, 16, 1000, None
+    if nsplit == 32:       # (the plan of one or two requests with very long contexts: 32 parts, 8 warps)
+        L = 9000
     if where == "first":
         peak = lambda l: 0
     elif where == "page_edge":
@@ -480,7 +482,7 @@ def test_attn_mma_finds_one_far_key(where, nsplit, cluster):
         window = 300
         peak = (lambda l: l - 300) if where == "window_in" else (lambda l: l - 301)
     c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, [L], [1], window, seed=16, peak=peak)
-    out = _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster)
+    out = _run_mma(c, nh, nkv, hd, ps, window, nsplit, cluster, warps=8 if nsplit == 32 else 4)
     assert_close(out, c["ref"], torch.bfloat16, where)
     assert (float(c["ref"].mean()) > 4.5) == (where != "window_out")
 

@@ -230,3 +230,76 @@ def test_decode_steps_split_the_norm_after_the_attention_between_two_products(mo
     assert rel_err(got_split, want) <= TOL["bfloat16"]
     assert rel_err(got_whole, want) <= TOL["bfloat16"]
     assert rel_err(got_split, got_whole) <= TOL["bfloat16"]
+
+
+def test_one_and_two_requests_with_a_very_long_context(tmp_path):
+    """A request of 17,000 tokens, decoded alone and beside a short one, in captured steps: with so few requests
+    and so many keys the decode attention is cut into 32 parts that meet through scratch memory (a class of
+    context length of its own has its own graph and plan); the prompt goes in portions of 2,048 tokens, the
+    later ones behind many thousands of cached tokens.  (That no part of the keys goes missing is the kernel test's
+    matter: one far key among 9,000 that outweighs all others.)"""
+    from lite_lang_b200 import ops
+    from lite_lang_b200.cache import CacheManager
+    from lite_lang_b200.config import config_from_dict, load_config
+    from lite_lang_b200.engine.batch import StepEntry
+    from lite_lang_b200.engine.model import CausalLM
+    from lite_lang_b200.engine.runner import ModelRunner
+    from lite_lang_b200.weights import load_weights, write_random_model
+
+    cfg_d = dict(CFG, vocab_size=4099, max_position_embeddings=20000, tie_word_embeddings=False)
+    folder = str(tmp_path / "long")
+    write_random_model(folder, config_from_dict(cfg_d), seed=23, scales={"matrix": 0.03, "bias": 0.05, "norm": 0.05})
+    dev = torch.device("cuda:0")
+    ops.configure_matmul_precision()
+    cfg, w = P.read_model_folder(folder, device=dev)
+    T, head = 17040, 17000
+    toks = random_tokens(T, cfg["vocab_size"], 91)
+    short = random_tokens(40, cfg["vocab_size"], 92)
+    ref = P.forward_logits(cfg, w, toks)[head - 1:].cpu().numpy()
+    ref_short = P.forward_logits(cfg, w, short).cpu().numpy()
+    del w
+    torch.cuda.empty_cache()
+
+    m = CausalLM(load_config(folder).model_spec())
+    load_weights(m, folder, torch.bfloat16, dev)
+    mgr = CacheManager(m.cache_groups, [(T + 64) // 16 + 8], 16, 4, 20000)
+    runner = ModelRunner(m, mgr, dev, 2048, cuda_graphs=True)
+    a = mgr.open()
+    assert runner.reserve(a, head)
+    for c0 in range(0, head, 2048):
+        c1 = min(head, c0 + 2048)
+        lg = runner.step([StepEntry(a, toks[c0:c1], (c1 - c0 - 1,) if c1 == head else ())])
+    assert rel_err(lg.float().cpu().numpy(), ref[:1]) <= TOL["bfloat16"]
+    plans = []
+    real_plan = type(m.blocks[0].mixer)._plan_mma
+
+    def spy(self, step, entries, max_kv_len, sms):
+        plan = real_plan(self, step, entries, max_kv_len, sms)
+        plans.append((entries, max_kv_len, plan[1], plan[4]))
+        return plan
+
+    type(m.blocks[0].mixer)._plan_mma = spy
+    try:
+        b = None
+        for i in range(head, T):
+            entries = [StepEntry(a, [toks[i]], (0,))]
+            want = [ref[i - head + 1:i - head + 2]]
+            assert runner.reserve(a, 1)
+            if i >= head + 10:                      # a short request beside it: prompt whole, then token by token
+                j = i - head - 10
+                if b is None:
+                    b = mgr.open()
+                    assert runner.reserve(b, 8)
+                    runner.step([StepEntry(b, short[:8], ())])
+                assert runner.reserve(b, 1)
+                entries.append(StepEntry(b, [short[8 + j]], (0,)))
+                want.append(ref_short[8 + j:9 + j])
+            got = runner.step(entries).float().cpu().numpy()
+            err = rel_err(got, np.concatenate(want))
+            assert err <= TOL["bfloat16"], (i, err)
+    finally:
+        type(m.blocks[0].mixer)._plan_mma = real_plan
+    runner.check_status()
+    assert runner.graph_replays == T - head
+    assert {(e, how) for e, _, _, how in plans} == {(1, "scratch"), (2, "scratch")}, plans
+    assert all(n == 32 and kv == 20000 for _, kv, n, _ in plans), plans
