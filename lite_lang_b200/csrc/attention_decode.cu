@@ -46,7 +46,14 @@ struct AttnDecodeParams {
   int window;
   float scale_log2;
   int nsplit;
+  // (after `status`:) Few requests with very long contexts: `nouter` clusters a (entry, kv head), each with a range of the keys of its
+  // own; a cluster's CTAs leave their slices of its partial result (unnormalised sums, maximum and sum of every
+  // head) in scratch memory, and the last of the `nouter` CTAs of a slice to arrive (a counter a slice, zero
+  // between launches) adds them up and writes the output.
   int* status;
+  int nouter;
+  float* scratch;     // [entries * nkv * nouter][nsplit][AD_HEADS][HD / nsplit + 2]
+  int* counters;      // [entries * nkv * nsplit]
 };
 
 __device__ __forceinline__ void ad_mma(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
@@ -102,7 +109,9 @@ __device__ __forceinline__ void ad_st_peer4(unsigned addr, float a, float b, flo
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-template <int HD, int NW, int DEPTH>
+// OUTER: several clusters a (entry, kv head) (see AttnDecodeParams; a variant of its own, so that the ordinary
+// kernel carries none of its code: with it in, a decode step at batch 1 to 16 was 3 to 5 % slower)
+template <int HD, int NW, int DEPTH, bool OUTER>
 __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodeParams p) {
   constexpr int KS = HD / 32;   // 16-byte loads per key row and thread for Q K^T
   constexpr int VS = HD / 64;   // 16-byte loads per value row and thread
@@ -118,7 +127,9 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   __shared__ float rx_l[8][AD_HEADS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
-  const int e = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int e = blockIdx.x, kvh = blockIdx.y;
+  const int split = OUTER ? (int)(blockIdx.z % p.nsplit) : (int)blockIdx.z;
+  [[maybe_unused]] const int outer = OUTER ? (int)(blockIdx.z / p.nsplit) : 0;
   if (e >= p.n_entries) return;
   LL_PDL_TRIGGER();   // the kernel after this one may move in and fetch its weights while this one works
   LL_TIMELINE_STAMP(p.status, 1, 0);
@@ -131,9 +142,13 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
   const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
   const int t_first = lo / AD_TILE, t_last = pos / AD_TILE;
   const int ntiles = t_last - t_first + 1;
-  const int tps = (ntiles + p.nsplit - 1) / p.nsplit;
-  const int t_begin = t_first + split * tps;
-  const int t_end = min(t_last + 1, t_begin + tps);
+  // (OUTER: the tiles of this cluster first, then of this CTA among them)
+  const int tpo = OUTER ? (ntiles + p.nouter - 1) / p.nouter : ntiles;
+  const int o_begin = OUTER ? t_first + outer * tpo : t_first;
+  const int o_end = OUTER ? min(t_last + 1, o_begin + tpo) : t_last + 1;
+  const int tps = OUTER ? (max(o_end - o_begin, 0) + p.nsplit - 1) / p.nsplit : (ntiles + p.nsplit - 1) / p.nsplit;
+  const int t_begin = o_begin + split * tps;
+  const int t_end = OUTER ? max(t_begin, min(o_end, t_begin + tps)) : min(t_last + 1, t_begin + tps);
   const int* bt = p.block_table + (size_t)max(slot, 0) * p.bt_stride;
   const int nt_split = t_end - t_begin;
   const bool bt_cached = nt_split <= AD_BT_CACHE;
@@ -212,7 +227,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
     for (int s = 0; s < KS; ++s) qf[s] = hv ? ad_ldg16(qr + 32 * s) : make_uint4(0, 0, 0, 0);
   }
   if (slot < 0) {  // padding entry of a captured step: zeros, no reads (the same for the whole cluster)
-    if (split == 0)
+    if (split == 0 && (!OUTER || outer == 0))
       for (int i = tid; i < p.group * HD; i += (NW * 32))
         p.out[(size_t)e * p.out_stride + (size_t)kvh * p.group * HD + i] = __float2bfloat16_rn(0.f);
     return;
@@ -457,6 +472,54 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
       for (int k = 0; k < 4; ++k)
         if (k < per) fin[k] += rx_o[(sI * AD_HEADS + row2) * slice + dl + k] * ws;
     }
+  if (OUTER) {
+    // ---- several clusters a (entry, kv head): the slice's partial results meet in scratch memory ----
+    __shared__ int sm_last;
+    const int pair = e * p.nkv + kvh;
+    const int rec = AD_HEADS * (slice + 2);     // floats of a slice's record: [head][slice dims, maximum, sum]
+    float* mine = p.scratch + (((size_t)pair * p.nouter + outer) * cs + rank) * rec;
+    if (worker) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (k < per) mine[row2 * (slice + 2) + dl + k] = fin[k];
+      if (dl == 0) {
+        mine[row2 * (slice + 2) + slice] = Mg;
+        mine[row2 * (slice + 2) + slice + 1] = Lg;
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      int* cnt = p.counters + (size_t)pair * cs + rank;
+      const int old = atomicAdd(cnt, 1);
+      sm_last = old == p.nouter - 1;
+      if (sm_last) *cnt = 0;     // ready for the next launch
+    }
+    __syncthreads();
+    if (!sm_last) return;
+    __threadfence();
+    if (worker && row2 < p.group) {
+      const float* base = p.scratch + ((size_t)pair * p.nouter * cs + rank) * rec + row2 * (slice + 2);
+      float Mt = -INFINITY;
+      for (int o = 0; o < p.nouter; ++o) Mt = fmaxf(Mt, __ldcg(base + (size_t)o * cs * rec + slice));
+      const float Mts = (Mt == -INFINITY) ? 0.f : Mt;
+      float Lt = 0.f, tot[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int o = 0; o < p.nouter; ++o) {
+        const float* r = base + (size_t)o * cs * rec;
+        const float wo = ad_exp2(__ldcg(r + slice) - Mts);
+        Lt += __ldcg(r + slice + 1) * wo;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (k < per) tot[k] += __ldcg(r + dl + k) * wo;
+      }
+      bf16* o2 = p.out + (size_t)e * p.out_stride + (size_t)(kvh * p.group + row2) * HD + (int)rank * slice + dl;
+      const float inv = Lt > 0.f ? 1.0f / Lt : 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (k < per) o2[k] = __float2bfloat16_rn(tot[k] * inv);
+    }
+    return;
+  }
   if (worker && row2 < p.group) {
     bf16* o2 = p.out + (size_t)e * p.out_stride + (size_t)(kvh * p.group + row2) * HD + (int)rank * slice + dl;
     const float inv = Lg > 0.f ? 1.0f / Lg : 0.f;
@@ -469,7 +532,9 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
 
 // One new token per entry: q row e (head h at q + e*q_stride + h*hd) attends to the cached keys of
 // the request in req_slot[e] up to position ctx_len[e] (its own key is already in the cache).
-// nsplit in {1, 2, 4, 8}: CTAs per (entry, kv head), launched as one cluster; warps in {4, 8}: warps a CTA
+// nouter clusters a (entry, kv head) (1; more only with nsplit >= 2: scratch is then float32
+// [n_entries * nkv * nouter * nsplit * 8 * (hd / nsplit + 2)], counters int32 [n_entries * nkv * nsplit], zero, left zero).
+// nsplit in {1, 2, 4, 8}: CTAs per (entry, kv head) and cluster, launched as one cluster; warps in {4, 8}: warps a CTA
 // (they take the split's 16-key tiles in turn); depth: tiles of a warp's ring, 2..4 for 4 warps, 2 or 3 for 8
 // (0: 3, but 2 for 8 warps in clusters).  Measured in a decode step at batch 8 (4 warps, 17 tiles a CTA): rings
 // of 3 tiles 1.108 ms, of 2 tiles 1.125-1.157 ms, of 4 tiles (128 KB a CTA, which no longer sits beside the
@@ -477,8 +542,8 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnDecodePa
 extern "C" int ll_attn_decode(void* out, long out_stride, const void* q, long q_stride, const void* k_cache,
                               const void* v_cache, const int* block_table, int bt_stride, const int* ctx_len,
                               const int* req_slot, int n_entries, int nh, int nkv, int hd, int page_size,
-                              int num_pages, int window, float scale, int nsplit, int warps, int depth, int* status,
-                              cudaStream_t stream) {
+                              int num_pages, int window, float scale, int nsplit, int warps, int depth, int nouter,
+                              float* scratch, int* counters, int* status, cudaStream_t stream) {
   if (n_entries <= 0) return 0;
   if ((hd != 64 && hd != 128) || page_size % AD_TILE != 0 || nkv <= 0 || nh % nkv != 0 || nkv > 65535)
     return (int)cudaErrorInvalidValue;
@@ -504,17 +569,22 @@ extern "C" int ll_attn_decode(void* out, long out_stride, const void* q, long q_
   p.num_pages = num_pages;
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
+  if (nouter < 1 || nouter > 64 || (nouter > 1 && (nsplit < 2 || scratch == nullptr || counters == nullptr)))
+    return (int)cudaErrorInvalidValue;
   p.nsplit = nsplit;
+  p.nouter = nouter;
+  p.scratch = scratch;
+  p.counters = counters;
   p.status = status;
-  dim3 grid(n_entries, nkv, nsplit);
+  dim3 grid(n_entries, nkv, nsplit * nouter);
   if (depth == 0) depth = (warps == 4 || nsplit == 1) ? 3 : 2;
   if (!((warps == 4 && depth >= 2 && depth <= 4) || (warps == 8 && (depth == 2 || depth == 3))))
     return (int)cudaErrorInvalidValue;
   const size_t ring = (size_t)warps * depth * 2 * AD_TILE * hd * 2;
 #define AD_LAUNCH(HD_, NW_, DEPTH_)                                                                                  \
   do {                                                                                                               \
-    cudaFuncSetAttribute(attn_decode_kernel<HD_, NW_, DEPTH_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring); \
-    ll_launch_cluster(attn_decode_kernel<HD_, NW_, DEPTH_>, grid, dim3(NW_ * 32), ring, stream, nsplit, p);          \
+    cudaFuncSetAttribute(attn_decode_kernel<HD_, NW_, DEPTH_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring); \
+    ll_launch_cluster(attn_decode_kernel<HD_, NW_, DEPTH_, false>, grid, dim3(NW_ * 32), ring, stream, nsplit, p);          \
   } while (0)
 #define AD_PICK(HD_)                                       \
   do {                                                     \
@@ -524,6 +594,17 @@ extern "C" int ll_attn_decode(void* out, long out_stride, const void* q, long q_
     else if (depth == 2) AD_LAUNCH(HD_, 8, 2);             \
     else AD_LAUNCH(HD_, 8, 3);                             \
   } while (0)
+  if (nouter > 1) {   // (8 warps, rings of two tiles: what the plan of few requests with long contexts uses)
+    if (warps != 8 || depth != 2) return (int)cudaErrorInvalidValue;
+    if (hd == 64) {
+      cudaFuncSetAttribute(attn_decode_kernel<64, 8, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+      ll_launch_cluster(attn_decode_kernel<64, 8, 2, true>, grid, dim3(256), ring, stream, nsplit, p);
+    } else {
+      cudaFuncSetAttribute(attn_decode_kernel<128, 8, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+      ll_launch_cluster(attn_decode_kernel<128, 8, 2, true>, grid, dim3(256), ring, stream, nsplit, p);
+    }
+    return LL_LAUNCH_RESULT();
+  }
   if (hd == 64) AD_PICK(64);
   else AD_PICK(128);
 #undef AD_PICK

@@ -81,9 +81,10 @@ class ModelRunner:
         self.graph_kernel_launches: Dict[int, int] = {}   # hand-written kernels inside each captured step
         self._bucket_list = _buckets(manager.max_requests)
         # A captured step's kernels are planned (splits of the keys, warps) for the longest context that may be
-        # replayed through the graph; so that short contexts are not run with a long one's plan and the other way
-        # round, a batch size has a graph per class of context length: up to 1,024 tokens, 4,096, 16,384, ...
-        self._context_classes = [c for c in (1 << k for k in range(10, 31, 2)) if c < manager.max_model_len]
+        # replayed through the graph; a plan for tens of thousands of keys does not suit a short context and the
+        # other way round, so a batch size has a graph per class of context length: up to 8,192 tokens (where the
+        # plans do not differ), up to 16,384, 32,768, ...
+        self._context_classes = [c for c in (1 << k for k in range(13, 31)) if c < manager.max_model_len]
         self._context_classes.append(manager.max_model_len)
         self.steps_run = 0
         self.graph_replays = 0

@@ -223,22 +223,6 @@ def attn_mma_scratch_floats(row_blocks: int, num_kv_heads: int, nsplit: int, hea
     return row_blocks * num_kv_heads * nsplit * 16 * (head_dim + 2)
 
 
-_attn_mma_scratch = {}    # per device: (partial results, counters) of attn_mma's splits that meet through memory
-
-
-def attn_mma_scratch(device, row_blocks: int, num_kv_heads: int, nsplit: int, head_dim: int):
-    """Scratch memory and counters (zero, and left zero by the kernel) for ``attn_mma`` with ``nsplit`` parts that
-    meet through memory; kept by this module, grown when needed (a captured step runs twice before its capture,
-    so nothing grows while a graph is recorded)."""
-    floats = attn_mma_scratch_floats(row_blocks, num_kv_heads, nsplit, head_dim)
-    have = _attn_mma_scratch.get(device)
-    if have is None or have[0].numel() < floats or have[1].numel() < row_blocks * num_kv_heads:
-        have = (torch.empty(max(floats, have[0].numel() if have else 0), dtype=torch.float32, device=device),
-                torch.zeros(max(row_blocks * num_kv_heads, 1024), dtype=torch.int32, device=device))
-        _attn_mma_scratch[device] = have
-    return have
-
-
 def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
              block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
              num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
@@ -287,14 +271,29 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
         _ptr(status), _stream())
 
 
+_attn_decode_scratch = {}   # per device: (partial results, counters) of attn_decode's clusters that meet through memory
+
+
+def _decode_scratch(device, floats: int, counters: int):
+    have = _attn_decode_scratch.get(device)
+    if have is None or have[0].numel() < floats or have[1].numel() < counters:
+        have = (torch.empty(max(floats, have[0].numel() if have else 0), dtype=torch.float32, device=device),
+                torch.zeros(max(counters, 1024), dtype=torch.int32, device=device))
+        _attn_decode_scratch[device] = have
+    return have
+
+
 def attn_decode(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
                 block_table: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor, num_entries: int,
                 num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
-                scale: float, nsplit: int, status: Optional[torch.Tensor], warps: int = 4, depth: int = 0) -> None:
+                scale: float, nsplit: int, status: Optional[torch.Tensor], warps: int = 4, depth: int = 0,
+                nouter: int = 1) -> None:
     """Tensor-core decode attention (bfloat16), transposed product: one new token per entry, groups of at
     most 8 query heads.  ``nsplit`` in (1, 2, 4, 8) CTAs per (entry, kv head) form a cluster; ``warps`` (4 or 8)
     a CTA take the split's tiles in turn through rings of ``depth`` tiles a warp (0: the kernel's choice; 2 to 4
-    for 4 warps, 2 or 3 for 8)."""
+    for 4 warps, 2 or 3 for 8).  ``nouter`` > 1 (few requests, very long contexts; needs nsplit >= 2): that many
+    clusters a (entry, kv head), each with a range of the keys, which meet through scratch memory kept by this
+    module."""
     _need_cuda(out, q, k_cache, v_cache, block_table, ctx_len, req_slot)
     for t, nm in ((block_table, "block_table"), (ctx_len, "ctx_len"), (req_slot, "req_slot")):
         _i32(t, nm)
@@ -308,11 +307,19 @@ def attn_decode(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torc
     _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache plane must be contiguous")
     _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache plane shape")
     _need(ctx_len.numel() >= num_entries and req_slot.numel() >= num_entries, "attn_decode: entry arrays too short")
+    scratch = counters = None
+    if nouter > 1:
+        _need(nsplit >= 2 and 1 < nouter <= 64 and warps == 8 and depth in (0, 2),
+              "attn_decode: several clusters a (entry, kv head) need nsplit >= 2, 8 warps and rings of two tiles")
+        depth = 2
+        scratch, counters = _decode_scratch(q.device, num_entries * num_kv_heads * nouter * 8 * (head_dim + 2 * nsplit),
+                                            num_entries * num_kv_heads * nsplit)
     load_library("attn_mma").call(
         "ll_attn_decode", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), _ptr(k_cache), _ptr(v_cache),
         _ptr(block_table), c_int(block_table.stride(0)), _ptr(ctx_len), _ptr(req_slot), c_int(num_entries),
         c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size), c_int(k_cache.shape[0]),
-        c_int(window or 0), c_float(scale), c_int(nsplit), c_int(warps), c_int(depth), _ptr(status), _stream())
+        c_int(window or 0), c_float(scale), c_int(nsplit), c_int(warps), c_int(depth), c_int(nouter), _ptr(scratch),
+        _ptr(counters), _ptr(status), _stream())
 
 
 def attn_prefill(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,

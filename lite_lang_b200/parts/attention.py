@@ -163,23 +163,26 @@ class GQAttention(Mixer):
             # within 1 % of it at context 8k (batch 2 and 8).
             base = entries * self.num_kv_heads
             most = (sms * 7) // 8
-            if base * 8 <= sms // 4 and max_tiles >= 8 * 128:
-                # Very few requests with very long contexts: 8 splits (the most a cluster takes) leave most SMs
-                # without work and every CTA with thousands of keys.  attn_mma cuts the keys into up to 32 parts
-                # that meet through scratch memory instead (context 32k: batch 1 35 -> 20 us a layer, batch 2
-                # 35 -> 21 us; at 8k and below the clusters are ahead: 11 against 13 us).
-                nsplit = 32
-                while nsplit > 8 and (base * nsplit > most or max_tiles // nsplit < 16):
-                    nsplit //= 2
-                if nsplit > 8:
-                    return entries, nsplit, True, 8, "scratch"
+            # Few requests with long contexts: a cluster takes 8 splits at most, which leaves most SMs without work
+            # and every CTA with thousands of keys.  Beyond 8,192 tokens a (entry, kv head) gets several clusters of
+            # 4 CTAs instead, each with a range of the keys, which meet through scratch memory: about 7/8 of the
+            # SMs in CTAs again, with at least 16 tiles a CTA at 3/4 of the longest context that the plan is for (a
+            # captured step's plan serves a class of context lengths).  Kernel alone, batch 1: context 8k 12.2 ->
+            # 8.3 us, 16k 20.5 -> 10.8, 32k 37.2 -> 13.5; in a step (CTAs of 128 KB, which the products around
+            # them do not sit beside) it pays from about 8k on: batch 1 at 16k 1.37 -> 1.24 ms, at 30k 1.83 -> 1.29.
+            if max_tiles > (512 if base <= 4 else 1024):     # (four requests: from 16k on; at 9k 1.24 -> 1.25 ms)
+                nouter = 1
+                while base * 4 * (2 * nouter) <= most and (max_tiles * 3 // 4) // (4 * 2 * nouter) >= 16:
+                    nouter *= 2
+                if nouter >= 4:
+                    return entries, 4, True, 8, nouter
             nsplit = 1
             for n in (8, 4, 2):
                 if base * n <= most and n <= max(1, max_tiles // 8):
                     nsplit = n
                     break
             warps = 4 if (nsplit == 8 and base * nsplit > most // 2) else 8
-            return entries, nsplit, True, warps, "decode"
+            return entries, nsplit, True, warps, 1
         blocks = entries * ((group + 15) // 16)
         ctas = blocks * self.num_kv_heads
         # attn_mma: one wave of CTAs at most, and at least 8 tiles (128 keys) a split: with less, merging the
@@ -193,7 +196,7 @@ class GQAttention(Mixer):
         # behind.  Not beyond half the SMs: 8-warp CTAs fit one an SM, and clusters of 8 of them then
         # no longer find room in one wave
         warps = 8 if ctas * nsplit <= sms // 2 and max_tiles >= 16 * nsplit else 4
-        return blocks, nsplit, group <= 16, warps, "cluster"
+        return blocks, nsplit, group <= 16, warps, 0
 
     def attend(self, out, qkv, step, cache) -> None:
         """Attention of the step's tokens over the cache plane; picks the kernels by shape.
@@ -210,16 +213,11 @@ class GQAttention(Mixer):
                 plan = step.scratch.get(key)
                 if plan is None:
                     plan = step.scratch[key] = self._plan_mma(step, n_single, step.max_kv_len, ops.sm_count(qkv.device))
-                blocks, nsplit, single, warps, how = plan
-                if how == "scratch":
-                    scratch, counters = ops.attn_mma_scratch(qkv.device, blocks, self.num_kv_heads, nsplit, self.head_dim)
-                    ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q,
-                                 step.ctx_len, step.req_slot, n_single, blocks, *args, nsplit, scratch, counters,
-                                 step.status, all_single=single, cluster=False, warps=warps)
-                elif how == "decode":
+                blocks, nsplit, single, warps, nouter = plan     # (nouter 0: groups of more than 8 heads, attn_mma)
+                if nouter >= 1:
                     # keys on the M side, the group's heads on the N side of the MMA: half the work a tile
                     ops.attn_decode(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.ctx_len,
-                                    step.req_slot, n_single, *args, nsplit, step.status, warps=warps)
+                                    step.req_slot, n_single, *args, nsplit, step.status, warps=warps, nouter=nouter)
                 else:
                     ops.attn_mma(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.cu_q,
                                  step.ctx_len, step.req_slot, n_single, blocks, *args, nsplit, None, None,

@@ -321,6 +321,26 @@ def test_attn_decode(nh, nkv, hd, ps, lens, window, nsplit):
         assert_close(out, c["ref"], torch.bfloat16, f"attn_decode with {warps} warps, rings of {depth}")
 
 
+@pytest.mark.parametrize("nsplit,nouter,warps", [(8, 4, 8), (2, 7, 8), (4, 16, 8), (8, 2, 8)])
+@pytest.mark.parametrize("nh,nkv,hd,ps,lens,window", [(12, 2, 128, 16, [9000, 33, 1, 2100], None),
+                                                      (8, 1, 64, 32, [5000, 700], None),
+                                                      (14, 2, 64, 16, [3000, 6100], 2500)])
+def test_attn_decode_with_several_clusters_a_request(nh, nkv, hd, ps, lens, window, nsplit, nouter, warps):
+    """Few requests with long contexts: `nouter` clusters a (entry, kv head) that meet through scratch memory (also
+    requests so short that most clusters have no keys); twice, so that the counters must have come back to zero."""
+    from lite_lang_b200 import ops
+    c = _paged_case(torch.bfloat16, nh, nkv, hd, ps, lens, [1] * len(lens), window, seed=33)
+    d = dev()
+    ctx = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=d)
+    status = torch.zeros(1, dtype=torch.int32, device=d)
+    for _ in range(2):
+        out = torch.full_like(c["q"], 3.0)
+        ops.attn_decode(out, c["q"], c["q"].stride(0), c["kc"], c["vc"], c["bt"], ctx, c["req_slot"], len(lens), nh, nkv,
+                        hd, ps, window, hd ** -0.5, nsplit, status, warps=warps, depth=2, nouter=nouter)
+        assert status.item() == 0
+        assert_close(out, c["ref"], torch.bfloat16, f"attn_decode, {nouter} clusters of {nsplit}")
+
+
 @pytest.mark.parametrize("nsplit", [1, 8])
 @pytest.mark.parametrize("where", ["first", "page_edge", "last_of_page", "window_in", "window_out"])
 def test_attn_decode_finds_one_far_key(where, nsplit):

@@ -234,8 +234,8 @@ def test_decode_steps_split_the_norm_after_the_attention_between_two_products(mo
 
 def test_one_and_two_requests_with_a_very_long_context(tmp_path):
     """A request of 17,000 tokens, decoded alone and beside a short one, in captured steps: with so few requests
-    and so many keys the decode attention is cut into 32 parts that meet through scratch memory (a class of
-    context length of its own has its own graph and plan); the prompt goes in portions of 2,048 tokens, the
+    and so many keys the decode attention gives a (request, kv head) eight clusters, each with a range of the keys,
+    that meet through scratch memory (a class of context length of its own has its own graph and plan); the prompt goes in portions of 2,048 tokens, the
     later ones behind many thousands of cached tokens.  (That no part of the keys goes missing is the kernel test's
     matter: one far key among 9,000 that outweighs all others.)"""
     from lite_lang_b200 import ops
@@ -301,5 +301,5 @@ def test_one_and_two_requests_with_a_very_long_context(tmp_path):
         type(m.blocks[0].mixer)._plan_mma = real_plan
     runner.check_status()
     assert runner.graph_replays == T - head
-    assert {(e, how) for e, _, _, how in plans} == {(1, "scratch"), (2, "scratch")}, plans
-    assert all(n == 32 and kv == 20000 for _, kv, n, _ in plans), plans
+    assert {(e, nouter) for e, _, _, nouter in plans} == {(1, 8), (2, 8)}, plans     # 8 clusters of 4 CTAs a kv head
+    assert all(n == 4 and kv == 20000 for _, kv, n, _ in plans), plans
