@@ -157,19 +157,19 @@ struct GtParams {
   // A norm between two products, split between them.  The product before the norm (NARROW to bfloat16, k not
   // split) adds its result to the residual rows, writes them back, writes them times the norm's weight as its
   // output (what the product after the norm multiplies), and leaves the sum of squares of each row's 16 values
-  // of a unit in sumsq_out[unit][32].  The product after the norm (GATED) adds the units' sums of a row in a
+  // of a unit in sumsq_out[unit][64].  The product after the norm (GATED) adds the units' sums of a row in a
   // fixed order and scales the row of its result by 1 / sqrt(sum / hidden + eps): the norm's reduction is off
   // the path between the two, and its kernel, a link of the chain of dependent launches, is gone.
   bf16* res;               // residual rows [M, N], row stride res_stride: read, added to, written
   long res_stride;
   const float* norm_w;     // float32 [N]
-  float* sumsq_out;        // float32 [N / 16][32]
-  const float* sumsq_in;   // float32 [sumsq_units][32]; null: no row factor
+  float* sumsq_out;        // float32 [N / 16][64]
+  const float* sumsq_in;   // float32 [sumsq_units][64]; null: no row factor
   int sumsq_units;
   float norm_eps, norm_inv_n;
   int* status;
 };
-#define GT_SUMSQ_ROWS 32   // rows of a sums-of-squares record: the most tokens the kernel takes
+#define GT_SUMSQ_ROWS 64   // rows of a sums-of-squares record: the most tokens the kernel takes
 
 // What a stage holds and how many there are.  The token rows of the stage's k range travel with the weights
 // (boxes of 8 MT rows x 64 k through a tensor map of x), so the consumers read both operands from shared
@@ -187,7 +187,9 @@ template <int MODE, int MT> struct GtStage {
 
 // SPLIT: the kernel's part of a norm that is split between the products around it (see GtParams): the NARROW product
 // before the norm, or the GATED product after it, which then has a sixth warp that makes the rows' factors.
-template <int MODE, int MT, typename OutT, bool SPLIT>
+// BLOCKS: more than 32 tokens (NARROW and QKV_ROPE, up to 64): the tokens in blocks of 32 along grid.y, each block
+// a set of CTAs of its own that streams the weights again (they are small products; the second read finds L2).
+template <int MODE, int MT, typename OutT, bool SPLIT, bool BLOCKS>
 __global__ void __launch_bounds__(GT_THREADS + ((SPLIT && MODE == GT_MODE_GATED) ? 32 : 0))
 gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap) {
   using S = GtShape<MODE>;
@@ -224,6 +226,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
   LL_TIMELINE_STAMP(p.status, TL_KERNEL, 0);
 
   const int kchunks = p.K / S::KC;
+  const int tok0 = BLOCKS ? (int)blockIdx.y * 8 * MT : 0;   // the first token of this CTA's block
 
   // ---- the rows' factors of the norm before a GATED product (SPLIT): a warp of its own adds the units' sums of
   // squares of each token in a fixed order while the others stream and multiply, and the consumers find
@@ -300,7 +303,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
       auto issue_x = [&](int s, int k) {
 #pragma unroll
         for (int kb = 0; kb < KBOXES; ++kb)
-          gt_tma_load(stage0 + s * STAGE_BYTES + W_BYTES + kb * XBOX_BYTES, &xmap, k * S::KC + kb * 64, 0, full0 + 8 * s);
+          gt_tma_load(stage0 + s * STAGE_BYTES + W_BYTES + kb * XBOX_BYTES, &xmap, k * S::KC + kb * 64, tok0, full0 + 8 * s);
       };
       open_unit();
       int early_kc[STAGES];
@@ -372,14 +375,14 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
         ep_cs[e] = 1.f;
         ep_sn[e] = 0.f;
         ep_slot[e] = -1;
-        if (idx < 8 * 8 * MT && t < p.M) {
+        if (idx < 8 * 8 * MT && tok0 + t < p.M) {
           const int f0 = head * p.hd + i0 + j;
           if (p.bias) {
             ep_b0[e] = p.bias[f0];
             ep_b1[e] = p.bias[f0 + half];
           }
           if (head < p.nh + p.nkv) {
-            int pos = p.positions[t];
+            int pos = p.positions[tok0 + t];
             if (pos < 0 || pos >= p.max_pos) {
               set_status(p.status, LL_ERR_POSITION_RANGE);
               pos = 0;
@@ -387,7 +390,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
             ep_cs[e] = p.cos_sin[(size_t)pos * p.hd + i0 + j];
             ep_sn[e] = p.cos_sin[(size_t)pos * p.hd + half + i0 + j];
           }
-          if (head >= p.nh && p.slot_map) ep_slot[e] = (long)p.slot_map[t];
+          if (head >= p.nh && p.slot_map) ep_slot[e] = (long)p.slot_map[tok0 + t];
         }
       }
     }
@@ -400,8 +403,8 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
       for (int e = 0; e < MT; ++e) {
         const int idx = tid + e * GT_CONSUMERS * 32;
         const int t = idx >> 4, n = u * 16 + (idx & 15);
-        const bool ok = t < p.M && n < p.N;
-        fr_res[e] = ok ? __bfloat162float(p.res[(size_t)t * p.res_stride + n]) : 0.f;
+        const bool ok = tok0 + t < p.M && n < p.N;
+        fr_res[e] = ok ? __bfloat162float(p.res[(size_t)(tok0 + t) * p.res_stride + n]) : 0.f;
         fr_w[e] = ok ? p.norm_w[n] : 0.f;
       }
     }
@@ -492,7 +495,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
         for (int e = 0; e < EP_ITEMS; ++e) {
           const int idx = tid + e * GT_CONSUMERS * 32;
           const int t = idx >> 3, j = idx & 7;
-          if (idx >= 8 * TOK || t >= p.M) continue;
+          if (idx >= 8 * TOK || tok0 + t >= p.M) continue;
           float x0 = 0.f, x1 = 0.f;
 #pragma unroll
           for (int wi = 0; wi < GT_CONSUMERS; ++wi) {
@@ -510,7 +513,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
           }
           const bf16 o0 = __float2bfloat16_rn(x0), o1 = __float2bfloat16_rn(x1);
           if (head < p.nh) {
-            bf16* q = reinterpret_cast<bf16*>(p.out) + (size_t)t * p.out_stride + f0;
+            bf16* q = reinterpret_cast<bf16*>(p.out) + (size_t)(tok0 + t) * p.out_stride + f0;
             q[0] = o0;
             q[half] = o1;
           } else {
@@ -538,31 +541,31 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
         for (int e = 0; e < MT; ++e) {
           const int idx = tid + e * GT_CONSUMERS * 32;
           const int t = idx >> 4, f = idx & 15;
-          const bool ok = t < p.M && u * 16 + f < p.N;
+          const bool ok = tok0 + t < p.M && u * 16 + f < p.N;
           float sum = 0.f;
 #pragma unroll
           for (int wi = 0; wi < GT_CONSUMERS; ++wi) sum += red[((size_t)wi * 16 + f) * TOK + t];
           float hn = 0.f;
           if (ok) {
             hn = __bfloat162float(__float2bfloat16_rn(fr_res[e] + __bfloat162float(__float2bfloat16_rn(sum))));
-            p.res[(size_t)t * p.res_stride + u * 16 + f] = __float2bfloat16_rn(hn);
-            out[(size_t)t * p.out_stride + u * 16 + f] = gt_out<OutT>(hn * fr_w[e]);
+            p.res[(size_t)(tok0 + t) * p.res_stride + u * 16 + f] = __float2bfloat16_rn(hn);
+            out[(size_t)(tok0 + t) * p.out_stride + u * 16 + f] = gt_out<OutT>(hn * fr_w[e]);
           }
           float sq = hn * hn;
           sq += __shfl_xor_sync(0xffffffffu, sq, 1);
           sq += __shfl_xor_sync(0xffffffffu, sq, 2);
           sq += __shfl_xor_sync(0xffffffffu, sq, 4);
           sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-          if (f == 0) p.sumsq_out[(size_t)u * GT_SUMSQ_ROWS + t] = sq;   // (t < 8 MT <= 32; rows beyond M hold 0)
+          if (f == 0) p.sumsq_out[(size_t)u * GT_SUMSQ_ROWS + tok0 + t] = sq;   // (rows beyond M hold 0)
         }
       } else {
         for (int idx = tid; idx < 16 * TOK; idx += GT_CONSUMERS * 32) {
           const int t = idx >> 4, f = idx & 15;
-          if (t < p.M && u * 16 + f < p.N) {
+          if (tok0 + t < p.M && u * 16 + f < p.N) {
             float sum = 0.f;
 #pragma unroll
             for (int wi = 0; wi < GT_CONSUMERS; ++wi) sum += red[((size_t)wi * 16 + f) * TOK + t];
-            out[(size_t)t * p.out_stride + u * 16 + f] = gt_out<OutT>(sum);
+            out[(size_t)(tok0 + t) * p.out_stride + u * 16 + f] = gt_out<OutT>(sum);
           }
         }
       }
@@ -603,7 +606,7 @@ static int gt_make_map(CUtensorMap* map, const void* w, long rows, long K, int b
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int MODE, int MT, typename OutT, bool SPLIT>
+template <int MODE, int MT, typename OutT, bool SPLIT, bool BLOCKS = false>
 static int gt_launch(const GtParams& p, const void* w, int sm_count, cudaStream_t stream) {
   using S = GtShape<MODE>;
   using G = GtStage<MODE, MT>;
@@ -615,11 +618,13 @@ static int gt_launch(const GtParams& p, const void* w, int sm_count, cudaStream_
   if (rc != 0) return rc;
   const size_t smem = 1024 + (size_t)G::STAGES * G::STAGE_BYTES + 2 * G::STAGES * 8 + 8 +   // (+ the row factors' barrier)
                       ((MODE == GT_MODE_NARROW || MODE == GT_MODE_QKV_ROPE) ? sizeof(float) * GT_CONSUMERS * 16 * 8 * MT : 0);
-  cudaFuncSetAttribute(gemm_stream_kernel<MODE, MT, OutT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaFuncSetAttribute(gemm_stream_kernel<MODE, MT, OutT, SPLIT, BLOCKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   // two CTAs an SM (one an SM, so that the next product's CTAs could move in early, was measured slower)
-  const int grid = p.units < 2 * sm_count ? p.units : 2 * sm_count;
+  const int blocks = BLOCKS ? (p.M + 8 * MT - 1) / (8 * MT) : 1;
+  const int room = 2 * sm_count / blocks;
+  const int grid = p.units < room ? p.units : room;
   const int threads = GT_THREADS + ((SPLIT && MODE == GT_MODE_GATED) ? 32 : 0);
-  ll_launch(gemm_stream_kernel<MODE, MT, OutT, SPLIT>, dim3(grid), dim3(threads), smem, stream, p, map, xmap);
+  ll_launch(gemm_stream_kernel<MODE, MT, OutT, SPLIT, BLOCKS>, dim3(grid, blocks), dim3(threads), smem, stream, p, map, xmap);
   return LL_LAUNCH_RESULT();
 }
 
@@ -628,6 +633,9 @@ static int gt_dispatch_m(const GtParams& p, const void* w, int sm_count, cudaStr
   if (p.M <= 8) return gt_launch<MODE, 1, OutT, SPLIT>(p, w, sm_count, stream);
   if (p.M <= 16) return gt_launch<MODE, 2, OutT, SPLIT>(p, w, sm_count, stream);
   if (p.M <= 32) return gt_launch<MODE, 4, OutT, SPLIT>(p, w, sm_count, stream);
+  if constexpr ((MODE == GT_MODE_NARROW || MODE == GT_MODE_QKV_ROPE) && sizeof(OutT) == 2) {
+    if (p.M <= 64 && p.ksplit == 1) return gt_launch<MODE, 4, OutT, SPLIT, true>(p, w, sm_count, stream);
+  }
   return (int)cudaErrorInvalidValue;
 }
 
@@ -641,7 +649,9 @@ extern "C" int ll_gemm_stream(void* out, long out_stride, int out_f32, const voi
                               int M, int N, int K, int mode, int ksplit, int sm_count, int* status,
                               cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 32 || K <= 0 || (x_stride % 8) != 0 || sm_count <= 0 || ksplit < 1) return (int)cudaErrorInvalidValue;
+  if (M > 64 || K <= 0 || (x_stride % 8) != 0 || sm_count <= 0 || ksplit < 1) return (int)cudaErrorInvalidValue;
+  // (33 to 64 tokens: units of 16 features to bfloat16 only, in two blocks of tokens)
+  if (M > 32 && (mode != GT_MODE_NARROW || out_f32 || ksplit != 1)) return (int)cudaErrorInvalidValue;
   if (ksplit > 1 && (!out_f32 || mode == GT_MODE_GATED)) return (int)cudaErrorInvalidValue;
   GtParams p = {};
   p.x = (const bf16*)x;
@@ -682,14 +692,14 @@ extern "C" int ll_gemm_stream(void* out, long out_stride, int out_f32, const voi
 
 // The product before a norm and the product after it, with the norm split between them (see GtParams).
 // ll_gemm_stream_into_norm: res[M, N] += x W^T (bfloat16, rounded as a separate product and sum would be), out[M, N] =
-// res * norm_w, sumsq[N / 16][32] = the sums of squares of each row's 16 values of a unit.  K % 256 == 0, N % 16 == 0.
+// res * norm_w, sumsq[N / 16][64] = the sums of squares of each row's 16 values of a unit.  K % 256 == 0, N % 16 == 0.
 // ll_gemm_stream_gated_scaled: the gated product of rows that are only multiplied by the norm's weight yet; each
 // row of the result is scaled by 1 / sqrt(sum over units of sumsq[unit][row] / hidden + eps) before the activation.
 extern "C" int ll_gemm_stream_into_norm(void* out, long out_stride, void* res, long res_stride, const float* norm_w,
                                         float* sumsq, const void* x, long x_stride, const void* w, int M, int N, int K,
                                         int sm_count, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 32 || K <= 0 || (K % 256) != 0 || (N % 16) != 0 || (x_stride % 8) != 0 || sm_count <= 0 || res == nullptr ||
+  if (M > 64 || K <= 0 || (K % 256) != 0 || (N % 16) != 0 || (x_stride % 8) != 0 || sm_count <= 0 || res == nullptr ||
       norm_w == nullptr || sumsq == nullptr)
     return (int)cudaErrorInvalidValue;
   GtParams p = {};
@@ -739,14 +749,14 @@ extern "C" int ll_gemm_stream_gated_scaled(void* out, long out_stride, const voi
 // The fused q|k|v projection of an attention layer (mode QKV_ROPE): qkv = x W^T (+ bias), q and k
 // rotated by the token's position (half-split pairs over the whole head), q written to
 // out[t, head * hd + i] (out: bfloat16 [M, >= nh * hd], row stride out_stride), k and v written into the
-// cache plane at slot_map[t].  w: bfloat16 [(nh + 2 nkv) hd, K]; K % 256 == 0; hd % 16 == 0; M <= 32.
+// cache plane at slot_map[t].  w: bfloat16 [(nh + 2 nkv) hd, K]; K % 256 == 0; hd % 16 == 0; M <= 64 (more than 32: two blocks of tokens).
 extern "C" int ll_gemm_stream_qkv_rope(void* out, long out_stride, const void* x, long x_stride, const void* w, int M,
                                        int K, const float* bias, const int* positions, const float* cos_sin,
                                        int max_pos, int nh, int nkv, int hd, const int* slot_map, void* k_cache,
                                        void* v_cache, int page_size, long num_slots, int sm_count, int* status,
                                        cudaStream_t stream) {
   if (M <= 0) return 0;
-  if (M > 32 || K <= 0 || (K % 256) != 0 || (x_stride % 8) != 0 || sm_count <= 0 || hd <= 0 || (hd % 16) != 0 ||
+  if (M > 64 || K <= 0 || (K % 256) != 0 || (x_stride % 8) != 0 || sm_count <= 0 || hd <= 0 || (hd % 16) != 0 ||
       nh <= 0 || nkv <= 0 || positions == nullptr || cos_sin == nullptr)
     return (int)cudaErrorInvalidValue;
   GtParams p = {};

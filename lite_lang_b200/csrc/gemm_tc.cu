@@ -102,8 +102,8 @@ struct TcParams {
   int ksplit;    // > 1: out is float32 [ksplit, M, N] partial sums
   int cpp;       // 64-wide k boxes per part
   int vec_ok;    // the output takes 16-byte pieces (aligned base and stride, N a multiple of the piece)
-  // SCALED (gated, at most 32 tokens): the tokens' rows are only multiplied by the weight of the norm before this
-  // product yet; the rows' sums of squares come in parts [sumsq_units][32] (see gemm_stream.cu: the product before
+  // SCALED (gated, at most 64 tokens): the tokens' rows are only multiplied by the weight of the norm before this
+  // product yet; the rows' sums of squares come in parts [sumsq_units][64] (see gemm_stream.cu: the product before
   // the norm leaves them), and each row of the result is scaled by 1 / sqrt(sum / K + eps) before the activation
   const float* sumsq_in;
   int sumsq_units;
@@ -273,17 +273,23 @@ gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const
     const int feat_in_unit = 32 * ew + lane;
     // SCALED: the rows' factors, made while the weights stream and the MMAs run: thread (quarter ew, token lane)
     // adds the units ew, ew + 4, ... of its token, the quarters meet in shared memory (a fixed order)
-    __shared__ float row_part[SCALED ? 4 : 1][32];
-    __shared__ float row_scale[SCALED ? 32 : 1];
+    __shared__ float row_part[SCALED ? 4 : 1][64];
+    __shared__ float row_scale[SCALED ? 64 : 1];
     if (SCALED) {
-      float part = 0.f;
+      float part0 = 0.f, part1 = 0.f;     // tokens lane and lane + 32
 #pragma unroll 8
-      for (int un = ew; un < p.sumsq_units; un += 4) part += p.sumsq_in[(size_t)un * 32 + lane];
-      row_part[ew][lane] = part;
+      for (int un = ew; un < p.sumsq_units; un += 4) {
+        part0 += p.sumsq_in[(size_t)un * 64 + lane];
+        part1 += p.sumsq_in[(size_t)un * 64 + 32 + lane];
+      }
+      row_part[ew][lane] = part0;
+      row_part[ew][32 + lane] = part1;
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (ew == 0)
-        row_scale[lane] = 1.0f / sqrtf((row_part[0][lane] + row_part[1][lane] + row_part[2][lane] + row_part[3][lane]) /
-                                           (float)p.K + p.norm_eps);
+      if (ew < 2) {
+        const int t = 32 * ew + lane;
+        row_scale[t] = 1.0f / sqrtf((row_part[0][t] + row_part[1][t] + row_part[2][t] + row_part[3][t]) / (float)p.K +
+                                    p.norm_eps);
+      }
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
     int unit_no = 0;
@@ -316,7 +322,7 @@ gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const
         const float a = stg[fl * (NT + 1) + t];
         if (MODE == TC_MODE_GATED) {
           // gate and up rounded to bfloat16 first, as the unfused path does between product and activation
-          const float rs = SCALED ? row_scale[t & 31] : 1.0f;
+          const float rs = SCALED ? row_scale[t & 63] : 1.0f;
           const float gt = __bfloat162float(__float2bfloat16_rn(a * rs));
           const float uv = __bfloat162float(__float2bfloat16_rn(stg[(64 + fl) * (NT + 1) + t] * rs));
           // (x * rcp(y), not the IEEE division: that is a chain of dependent instructions with a branch an element)
@@ -419,12 +425,12 @@ static int tc_launch(const TcParams& p, const void* w, const void* x, long x_str
 // x: bfloat16 [M, K] (row stride x_stride, a multiple of 8); w: bfloat16 [N, K] contiguous (gated: [2 N, K],
 // gate rows first); out: bfloat16 [M, N], or float32 with out_f32 = 1; ksplit > 1: out is float32
 // [ksplit, M, N] partial sums (out_stride = N).  33 <= M <= 128 is what it is meant for; any M <= 128 works.
-// sumsq (gated, M <= 32; or null): see TcParams.
+// sumsq (gated, M <= 64; or null): see TcParams.
 extern "C" int ll_gemm_tc(void* out, long out_stride, int out_f32, const void* x, long x_stride, const void* w, int M,
                           int N, int K, int gated, int ksplit, int sm_count, const float* sumsq, int sumsq_units,
                           float norm_eps, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (sumsq != nullptr && (!gated || M > 32 || sumsq_units <= 0)) return (int)cudaErrorInvalidValue;
+  if (sumsq != nullptr && (!gated || M > 64 || sumsq_units <= 0)) return (int)cudaErrorInvalidValue;
   if (M > 128 || K <= 0 || (K % 64) != 0 || (x_stride % 8) != 0 || sm_count <= 0 || ksplit < 1)
     return (int)cudaErrorInvalidValue;
   if ((ksplit > 1 && (!out_f32 || gated)) || (gated && out_f32)) return (int)cudaErrorInvalidValue;

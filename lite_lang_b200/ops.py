@@ -531,6 +531,7 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated:
 
 
 STREAM_M = 32         # the most tokens the bulk-copy streaming kernel takes
+STREAM_M_NARROW = 64  # ... for its units of 16 features (q|k|v, o): the tokens then go in two blocks of 32
 _sm_count = {}
 
 
@@ -545,10 +546,12 @@ def sm_count(device) -> int:
 def stream_mode(x: torch.Tensor, weight: torch.Tensor, gated: bool = False) -> Optional[int]:
     """Work-unit shape of ``gemm_stream`` for this product (0 wide, 1 gated, 2 narrow), or None."""
     if not (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
-            and 0 < x.shape[0] <= STREAM_M and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and 0 < x.shape[0] <= STREAM_M_NARROW and x.stride(1) == 1 and x.stride(0) % 8 == 0
             and weight.is_contiguous() and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
         return None
     k = x.shape[1]
+    if x.shape[0] > STREAM_M:      # 33 to 64 tokens: small products with units of 16 features only (bfloat16 out, k whole)
+        return 2 if (not gated and k % 256 == 0 and weight.shape[0] < 8192) else None
     if gated:
         return 1 if k % 128 == 0 else None
     n = weight.shape[0]
@@ -574,7 +577,8 @@ def stream_ksplit(n: int, k: int, mode: int, device) -> int:
 
 def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: int,
                 status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out = x @ weight.T for up to 32 bfloat16 tokens with the TMA weight-streaming kernel.
+    """out = x @ weight.T for up to 32 bfloat16 tokens (64 for mode 2 to bfloat16 with k whole) with the TMA
+    weight-streaming kernel.
 
     mode 0: units of 64 output features; 1: SiLU-gated (weight [2 I, K], out [M, I]);
     2: units of 16 features with k split over the warps.  A float32 ``out`` of shape
@@ -584,7 +588,7 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: 
     m, k = x.shape
     gated = mode == 1
     n = weight.shape[0] // 2 if gated else weight.shape[0]
-    _need(stream_mode(x, weight, gated) is not None, "gemm_stream: bfloat16, at most 32 tokens, K % 128 == 0")
+    _need(stream_mode(x, weight, gated) is not None, "gemm_stream: bfloat16, at most 32 tokens (64 for mode 2), K % 128 == 0")
     _need(mode in (0, 1, 2) and k % (256 if mode == 2 else 128) == 0, "gemm_stream: K does not fit the mode")
     _need(weight.shape[1] == k, "gemm_stream: weight shape")
     ksplit = 1
@@ -604,7 +608,7 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: 
     return out
 
 
-SUMSQ_ROWS = 32     # rows of a sums-of-squares record (the most tokens ``gemm_stream`` takes)
+SUMSQ_ROWS = 64     # rows of a sums-of-squares record (the most tokens ``gemm_stream`` takes)
 NORM_SPLIT = os.environ.get("LITE_LANG_B200_NORM_SPLIT", "1") != "0"   # 0: the norm between two streaming products
                                                                         # stays a kernel of its own (for comparisons)
 
@@ -629,13 +633,13 @@ def gated_scaled_supported(rows: torch.Tensor, w_gate_up: torch.Tensor) -> bool:
 def gemm_stream_into_norm(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor,
                           status: Optional[torch.Tensor] = None):
     """residual += x @ weight.T (rounded as the separate product and sum would be); returns (u, sumsq): u = the new
-    residual rows times ``norm_weight`` (bfloat16), sumsq float32 [out / 16, 32] = the sums of squares of each
+    residual rows times ``norm_weight`` (bfloat16), sumsq float32 [out / 16, 64] = the sums of squares of each
     row's 16 values of a unit.  With ``gemm_stream_gated_scaled`` after it, this is the residual sum, the RMS norm
     and the two products around them in two kernels instead of three."""
     _need_cuda(x, weight, residual, norm_weight, status)
     m, k = x.shape
     n = weight.shape[0]
-    _need(into_norm_supported(x, weight, residual), "gemm_stream_into_norm: bfloat16, at most 32 tokens, K % 256 == 0, "
+    _need(into_norm_supported(x, weight, residual), "gemm_stream_into_norm: bfloat16, at most 64 tokens, K % 256 == 0, "
                                                     "N % 16 == 0, residual bfloat16 [tokens, N]")
     _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == n and norm_weight.is_contiguous(),
           "gemm_stream_into_norm: the norm's weight is float32 [out]")
@@ -651,13 +655,13 @@ def gemm_stream_into_norm(x: torch.Tensor, weight: torch.Tensor, residual: torch
 def gemm_stream_gated_scaled(u: torch.Tensor, w_gate_up: torch.Tensor, sumsq: torch.Tensor, eps: float,
                              status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """silu(g) * up of the rows x = u / sqrt(mean of squares + eps), where u is already multiplied by the norm's
-    weight and ``sumsq`` [units, 32] holds the rows' sums of squares in parts (``gemm_stream_into_norm``)."""
+    weight and ``sumsq`` [units, 64] holds the rows' sums of squares in parts (``gemm_stream_into_norm``)."""
     _need_cuda(u, w_gate_up, sumsq, status)
     m, k = u.shape
     inter = w_gate_up.shape[0] // 2
-    _need(gated_scaled_supported(u, w_gate_up), "gemm_stream_gated_scaled: bfloat16, at most 32 tokens, K % 128 == 0")
+    _need(gated_scaled_supported(u, w_gate_up), "gemm_stream_gated_scaled: bfloat16, K % 128 == 0, at most 32 tokens (64 where the tcgen05 kernel takes the product)")
     _need(sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.shape[1] == SUMSQ_ROWS and sumsq.is_contiguous(),
-          "gemm_stream_gated_scaled: sums of squares are float32 [units, 32]")
+          "gemm_stream_gated_scaled: sums of squares are float32 [units, 64]")
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=u.device)
     if tc_preferred(u, w_gate_up, gated=True):
         return gemm_tc(u, w_gate_up, act, gated=True, status=status, sumsq=sumsq, eps=eps)
@@ -918,10 +922,14 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
         out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
         return gemm_tc(x, weight, out)
     mode = stream_mode(x, weight) if (out is None or out.stride(1) == 1) else None
+    many = x.shape[0] > STREAM_M       # 33 to 64 tokens: bfloat16 out, k whole
+    if mode is not None and many and ((out_dtype or x.dtype) != torch.bfloat16 or (out is not None and out.dtype != torch.bfloat16)):
+        mode = None
     if mode is not None:
         dt = out_dtype or x.dtype
         if out is None:
-            parts = stream_ksplit(weight.shape[0], x.shape[1], mode, x.device) if (partial_ok and dt == x.dtype) else 1
+            parts = (stream_ksplit(weight.shape[0], x.shape[1], mode, x.device)
+                     if (partial_ok and dt == x.dtype and not many) else 1)
             if parts > 1:
                 out = torch.empty((parts, x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
                 return gemm_stream(x, weight, out, mode)

@@ -727,7 +727,8 @@ def test_gemm_smallm_gated_equals_product_then_activation(m, inter, k):
 
 @pytest.mark.parametrize("mode,m,n,k", [(2, 1, 48, 256), (2, 8, 2048, 1536), (2, 5, 1536, 8960), (2, 13, 100, 512),
                                         (0, 8, 9000, 1536), (0, 3, 331, 128), (0, 32, 151936, 256), (2, 32, 272, 1024),
-                                        (0, 16, 64, 384), (2, 16, 17, 768)])
+                                        (0, 16, 64, 384), (2, 16, 17, 768), (2, 33, 1536, 1536), (2, 64, 2048, 512),
+                                        (2, 47, 100, 256)])
 def test_gemm_stream(mode, m, n, k):
     from lite_lang_b200 import ops
     g = torch.Generator().manual_seed(24)
@@ -736,6 +737,8 @@ def test_gemm_stream(mode, m, n, k):
     ref = x.double() @ w.double().t()
     status = torch.zeros(1, dtype=torch.int32, device=dev())
     for dt in (torch.bfloat16, torch.float32):
+        if m > 32 and dt == torch.float32:       # (33 to 64 tokens: two blocks of tokens, to bfloat16 only)
+            continue
         out = torch.full((m, n), 7.0, dtype=dt, device=dev())
         for _ in range(2):
             ops.gemm_stream(x.to(dev()), w.to(dev()), out, mode, status)
@@ -769,7 +772,8 @@ def test_gemm_stream_split_over_k_and_summed_by_the_norm(mode, m, n, k, parts):
 
 
 @pytest.mark.parametrize("m,hidden,k,inter", [(8, 1536, 1536, 8960), (1, 256, 512, 96), (13, 768, 256, 203),
-                                              (32, 2048, 2048, 320), (16, 3584, 3584, 1184)])
+                                              (32, 2048, 2048, 320), (16, 3584, 3584, 1184), (40, 1536, 1536, 8960),
+                                              (64, 2048, 2048, 11008), (33, 768, 512, 640)])
 def test_norm_split_between_the_product_before_and_the_gated_product_after(m, hidden, k, inter):
     """o projection -> residual sum -> RMS norm -> gated feed-forward product as two kernels: against the plain
     formulas, and the residual rows bit for bit against the three separate kernels."""
@@ -788,7 +792,7 @@ def test_norm_split_between_the_product_before_and_the_gated_product_after(m, hi
     delta = ops.gemm_stream(x, w1, torch.empty(m, hidden, dtype=torch.bfloat16, device=d), 2, status)
     xa = torch.empty_like(res_a)
     ops.add_rmsnorm(xa, res_a, delta, wn, eps)
-    act_a = ops.gemm_stream(xa, w2, torch.empty(m, inter, dtype=torch.bfloat16, device=d), 1, status)
+    act_a = ops.gated_linear(xa, w2)      # (the streaming kernel, or from 17 tokens on the tcgen05 one)
     # the two kernels with the norm split between them
     res_b = res0.clone()
     u, sumsq = ops.gemm_stream_into_norm(x, w1, res_b, wn, status)
@@ -974,7 +978,8 @@ def _assert_qkv_equals_the_plain_formulas(x, w, bias, pos, slots, q, kc, vc, nh,
 
 
 @pytest.mark.parametrize("m,hidden,nh,nkv,hd,ps", [(8, 1536, 12, 2, 128, 16), (1, 256, 3, 1, 64, 32), (19, 512, 4, 4, 32, 16),
-                                                   (32, 768, 6, 2, 128, 64)])
+                                                   (32, 768, 6, 2, 128, 64), (50, 1536, 12, 2, 128, 16), (64, 512, 4, 2, 64, 16),
+                                                   (33, 256, 2, 2, 128, 32)])
 def test_gemm_stream_qkv_rope_equals_the_plain_formulas_and_the_three_kernels_it_replaces(m, hidden, nh, nkv, hd, ps):
     from lite_lang_b200 import ops
     from lite_lang_b200.parts.rope import rope_table

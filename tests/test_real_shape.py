@@ -172,10 +172,10 @@ def test_other_model_sizes_in_bfloat16(size, tmp_path):
 
 
 def test_decode_steps_split_the_norm_after_the_attention_between_two_products(model, monkeypatch):
-    """In bfloat16 decode steps of up to 16 tokens the norm after the attention has no kernel of its own: the o
+    """In bfloat16 steps of up to 64 tokens the norm after the attention has no kernel of its own: the o
     projection leaves its input ready (``ops.gemm_stream_into_norm``) and the gated product applies the rows'
     factors.  The steps' logits equal the plain ones, and those of the same steps with the norm as a kernel of its
-    own (``ops.NORM_SPLIT`` off) up to bfloat16 rounding; a portion of a prompt in the same step switches it off."""
+    own (``ops.NORM_SPLIT`` off) up to bfloat16 rounding; a larger step keeps the norm's kernel."""
     from lite_lang_b200 import ops
     from lite_lang_b200.cache import CacheManager
     from lite_lang_b200.config import load_config
@@ -207,12 +207,13 @@ def test_decode_steps_split_the_norm_after_the_attention_between_two_products(mo
         monkeypatch.setattr(ops, "NORM_SPLIT", split)
         mgr = CacheManager(m.cache_groups, [32], 16, 8, 256)
         runner = ModelRunner(m, mgr, dev, 128, cuda_graphs=False)
-        a, b = mgr.open(), mgr.open()
-        assert runner.reserve(a, 40) and runner.reserve(b, 9)
+        a, b, c = mgr.open(), mgr.open(), mgr.open()
+        assert runner.reserve(a, 40) and runner.reserve(b, 9) and runner.reserve(c, 30)
         first_calls = dict(calls)
-        runner.step([StepEntry(a, toks[:40], ()), StepEntry(b, toks[:9], ())])
+        runner.step([StepEntry(a, toks[:40], ()), StepEntry(b, toks[:9], ()), StepEntry(c, toks[:30], ())])
+        mgr.close(c)
         before = dict(calls)
-        if split:      # (a step with portions of prompts, 49 tokens, keeps the norm's own kernel)
+        if split:      # (a step of more than 64 tokens, here 79 of three prompts, keeps the norm's own kernel)
             assert first_calls == before, (first_calls, before)
         out = []
         for i in range(3):     # two requests, a token each: the split path
