@@ -403,3 +403,33 @@ def test_a_portion_shrinks_to_what_every_cache_group_can_take():
     assert counts[0] == [20]                      # the windowed group's 5 pages, not the budget of 32
     assert sum(c[0] for c in counts[:-2]) == 50 and a.finish_reason == "length" and len(a.output) == 3
     assert m.num_free_pages(0) == 16 and m.num_free_pages(1) == 5
+
+
+def test_decode_attention_plan_follows_requests_and_context():
+    """The host's plan of the decode attention (CPU: arithmetic only): CTAs for about 7/8 of the SMs, as splits of a
+    cluster; several clusters a (request, kv head) for one to four requests with more than 8k tokens; a windowed
+    layer is planned for its window, not for the context."""
+    from lite_lang_b200.parts.attention import GQAttention
+
+    def attn(nh, nkv, window=None):
+        a = GQAttention.__new__(GQAttention)
+        a.num_heads, a.num_kv_heads, a.window = nh, nkv, window
+        return a
+
+    plan = GQAttention._plan_mma
+    a = attn(12, 2)
+    # (row blocks, splits, one token an entry, warps, clusters a (entry, kv head))
+    assert plan(a, None, 8, 4096, 148) == (8, 8, True, 4, 1)        # 8 x 2 x 8 = 128 CTAs of 4 warps
+    assert plan(a, None, 1, 4096, 148) == (1, 8, True, 8, 1)
+    assert plan(a, None, 16, 4096, 148) == (16, 4, True, 8, 1)
+    assert plan(a, None, 64, 4096, 148) == (64, 1, True, 8, 1)
+    assert plan(a, None, 8, 100, 148)[1] == 1                       # fewer than 8 tiles a split: no splits
+    for entries, kv, nouter in ((1, 8192, 1), (1, 16384, 8), (1, 65536, 16), (2, 16384, 8), (4, 16384, 1),
+                                (4, 32768, 4), (8, 65536, 1)):
+        got = plan(a, None, entries, kv, 148)
+        assert got[4] == nouter, (entries, kv, got)
+        if nouter > 1:
+            assert got[1] == 4 and got[3] == 8 and entries * 2 * 4 * nouter <= 148
+    assert plan(attn(12, 2, window=1000), None, 1, 65536, 148) == plan(a, None, 1, 1016, 148)
+    # more than 8 query heads a kv head: the other kernel (clusters = 0)
+    assert plan(attn(32, 2), None, 4, 4096, 148)[4] == 0
