@@ -550,8 +550,14 @@ def stream_mode(x: torch.Tensor, weight: torch.Tensor, gated: bool = False) -> O
             and weight.is_contiguous() and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
         return None
     k = x.shape[1]
-    if x.shape[0] > STREAM_M:      # 33 to 64 tokens: small products with units of 16 features only (bfloat16 out, k whole)
-        return 2 if (not gated and k % 256 == 0 and weight.shape[0] < 8192) else None
+    if x.shape[0] > STREAM_M:
+        # 33 to 64 tokens: only small products with units of 16 features (bfloat16 out, k whole), a unit a CTA in
+        # both blocks of tokens at once and k up to 1,536: a CTA re-reads its 32 token rows (twice its weights' bytes)
+        # with every unit, which a larger product pays for (Qwen2-7B sizes at batch 64: 4.33 -> 4.85 ms a step;
+        # 2.5-3B sizes 3.27 -> 3.43, and 3.32 with the o projection, k = 2,048, alone) and the 1.5B sizes gain from
+        # (2.06 -> 2.00)
+        units = (weight.shape[0] + 15) // 16
+        return 2 if (not gated and k % 256 == 0 and k <= 1536 and 2 * units <= 2 * sm_count(x.device)) else None
     if gated:
         return 1 if k % 128 == 0 else None
     n = weight.shape[0]
