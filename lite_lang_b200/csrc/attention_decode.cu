@@ -21,6 +21,9 @@
 // finishes a slice of the head dimensions, which the others send to it with stores into its shared memory
 // before the cluster's one barrier.  No scratch memory, no counters, nothing spins (the cluster
 // barrier is the hardware's; every CTA of a cluster reaches it, early exits are the same for all of them).
+// A variant (OUTER) for very few requests with very long contexts gives an (entry, kv head) several such clusters,
+// each with a range of the keys; their slices of the result meet in scratch memory, where the last CTA of a
+// slice to arrive (a counter, no spinning) adds them up.
 //
 // Head sizes 64 and 128, groups of at most 8 query heads, pages of a multiple of 16 tokens.
 #include "common.cuh"
