@@ -632,6 +632,14 @@ template <int MODE, typename OutT, bool SPLIT = false>
 static int gt_dispatch_m(const GtParams& p, const void* w, int sm_count, cudaStream_t stream) {
   if (p.M <= 8) return gt_launch<MODE, 1, OutT, SPLIT>(p, w, sm_count, stream);
   if (p.M <= 16) return gt_launch<MODE, 2, OutT, SPLIT>(p, w, sm_count, stream);
+  if constexpr ((MODE == GT_MODE_NARROW || MODE == GT_MODE_QKV_ROPE) && sizeof(OutT) == 2) {
+    // 17 to 32 tokens of a small product (a unit a CTA in both blocks at once): two blocks of 16 tokens, which
+    // stream the weights twice (the second time from L2) but keep six stages in the ring where tiles of 32 tokens
+    // leave four (a decode step at batch 17 1.62 -> 1.55 ms, 24 1.61 -> 1.52, 32 1.66 -> 1.56; two blocks of 8 for
+    // 9 to 16 tokens: no difference; with k = 2,048, the o projection of the 3B sizes: none either, or 1 % worse)
+    if (p.M > 16 && p.M <= 32 && p.ksplit == 1 && 2 * p.units <= 2 * sm_count && p.K <= 1536)
+      return gt_launch<MODE, 2, OutT, SPLIT, true>(p, w, sm_count, stream);
+  }
   if (p.M <= 32) return gt_launch<MODE, 4, OutT, SPLIT>(p, w, sm_count, stream);
   if constexpr ((MODE == GT_MODE_NARROW || MODE == GT_MODE_QKV_ROPE) && sizeof(OutT) == 2) {
     if (p.M <= 64 && p.ksplit == 1) return gt_launch<MODE, 4, OutT, SPLIT, true>(p, w, sm_count, stream);

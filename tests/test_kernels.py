@@ -773,7 +773,7 @@ def test_gemm_stream_split_over_k_and_summed_by_the_norm(mode, m, n, k, parts):
 
 @pytest.mark.parametrize("m,hidden,k,inter", [(8, 1536, 1536, 8960), (1, 256, 512, 96), (13, 768, 256, 203),
                                               (32, 2048, 2048, 320), (16, 3584, 3584, 1184), (40, 1536, 1536, 8960),
-                                              (64, 1536, 1024, 11008), (33, 768, 512, 640)])
+                                              (64, 1536, 1024, 11008), (33, 768, 512, 640), (24, 1536, 1536, 640), (17, 256, 256, 96)])
 def test_norm_split_between_the_product_before_and_the_gated_product_after(m, hidden, k, inter):
     """o projection -> residual sum -> RMS norm -> gated feed-forward product as two kernels: against the plain
     formulas, and the residual rows bit for bit against the three separate kernels."""
