@@ -272,13 +272,18 @@ def attn_mma(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: torch.T
 
 
 _attn_decode_scratch = {}   # per device: (partial results, counters) of attn_decode's clusters that meet through memory
+_DECODE_SCRATCH_FLOATS = 1 << 19    # 2 MB; a plan's need is (CTAs / 4) * 8 * (head size + 2 splits) floats: far less
+_DECODE_SCRATCH_COUNTERS = 4096
 
 
 def _decode_scratch(device, floats: int, counters: int):
+    """One buffer a device, of a fixed size and never replaced: captured steps keep its address."""
+    _need(floats <= _DECODE_SCRATCH_FLOATS and counters <= _DECODE_SCRATCH_COUNTERS,
+          "attn_decode: too many clusters for the scratch memory of their partial results")
     have = _attn_decode_scratch.get(device)
-    if have is None or have[0].numel() < floats or have[1].numel() < counters:
-        have = (torch.empty(max(floats, have[0].numel() if have else 0), dtype=torch.float32, device=device),
-                torch.zeros(max(counters, 1024), dtype=torch.int32, device=device))
+    if have is None:
+        have = (torch.empty(_DECODE_SCRATCH_FLOATS, dtype=torch.float32, device=device),
+                torch.zeros(_DECODE_SCRATCH_COUNTERS, dtype=torch.int32, device=device))
         _attn_decode_scratch[device] = have
     return have
 
